@@ -1,0 +1,230 @@
+// Memory-bound kernels of the step: embedding gather, (residual add +) RMSNorm, rotary
+// position encoding fused with the paged KV append, and the SwiGLU gate.
+//
+// The residual stream is float32 in every mode; normalisation, rotation angles and the
+// residual sum are computed in float32 (the reference computes its norm in float32,
+// mini_hisparse/model.py:49-51, and its angles in float32, model.py:141-147).
+//
+// Inputs that come from a split-K matrix product arrive as `nsplit` float32 partial
+// matrices `split_stride` elements apart; they are summed here in a fixed order, so the
+// result does not depend on timing.
+#include "common.cuh"
+
+using namespace mhb;
+
+MHB_EXPORT const char* mhb_last_error() { return error_buffer(); }
+
+// ---- load helpers -----------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float load_split(const T* p, size_t idx, int nsplit, size_t split_stride) {
+    float v = to_float(p[idx]);
+    for (int s = 1; s < nsplit; ++s) v += to_float(p[idx + (size_t)s * split_stride]);
+    return v;
+}
+
+// ---- embedding ---------------------------------------------------------------------------
+// out[t, :] = table[tokens[t], :]   (mini_hisparse/model.py:166: plain lookup, no scaling)
+template <typename WT>
+__global__ void embed_kernel(const WT* __restrict__ table, const int* __restrict__ tokens,
+                             float* __restrict__ out, int H, int V, int* __restrict__ status) {
+    const int t = blockIdx.x;
+    const int tok = tokens[t];
+    float* o = out + (size_t)t * H;
+    if (tok < 0 || tok >= V) {  // the host validates ids; never read outside the table
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.f;
+        if (threadIdx.x == 0 && status) atomicOr(status, 1);
+        return;
+    }
+    const WT* row = table + (size_t)tok * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_float(row[i]);
+}
+
+MHB_EXPORT int mhb_embed(const void* table, int table_dtype, const int* tokens, float* out, int T,
+                         int H, int V, int* status, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    MHB_DISPATCH_DTYPE(table_dtype, WT,
+        embed_kernel<WT><<<T, threads, 0, stream>>>((const WT*)table, tokens, out, H, V, status));
+    return check_launch("embed");
+}
+
+// ---- (add +) RMSNorm -----------------------------------------------------------------------
+// For output row r (source row s = rows ? rows[r] : r):
+//   v = x[s] (+ delta[s]);  if delta and !rows: x[s] = v  (residual updated in place)
+//   out[r] = (v * rsqrt(mean(v^2) + eps)) * weight        (mini_hisparse/model.py:49-51)
+template <typename DT, typename OT>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const DT* __restrict__ delta, int nsplit,
+                                   size_t split_stride, const float* __restrict__ weight,
+                                   float eps, const int* __restrict__ rows, OT* __restrict__ out,
+                                   int H) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    float* xr = x + (size_t)s * H;
+    const bool write_back = (delta != nullptr) && (rows == nullptr);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = xr[i];
+        if (delta) {
+            v += load_split(delta, (size_t)s * H + i, nsplit, split_stride);
+            if (write_back) xr[i] = v;
+        }
+        ss += v * v;
+    }
+    const float total = block_sum(ss, scratch);
+    const float rstd = rsqrtf(total / (float)H + eps);
+    OT* o = out + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = xr[i];
+        if (delta && !write_back) v += load_split(delta, (size_t)s * H + i, nsplit, split_stride);
+        const float n = v * rstd;
+        o[i] = from_float<OT>(n * weight[i]);
+    }
+}
+
+// Residual add alone (the last feed-forward's output when no norm follows on all rows).
+template <typename DT>
+__global__ void residual_add_kernel(float* __restrict__ x, const DT* __restrict__ delta, int nsplit,
+                                    size_t split_stride, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += load_split(delta, i, nsplit, split_stride);
+}
+
+MHB_EXPORT int mhb_add_rmsnorm(float* x, const void* delta, int delta_dtype, int nsplit,
+                               long long split_stride, const float* weight, float eps,
+                               const int* rows, void* out, int out_dtype, int R, int H,
+                               cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (nsplit > 1 && delta_dtype != MHB_F32) return fail("add_rmsnorm: split partials must be float32");
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    MHB_DISPATCH_DTYPE(delta_dtype, DT, MHB_DISPATCH_DTYPE(out_dtype, OT,
+        add_rmsnorm_kernel<DT, OT><<<R, threads, 0, stream>>>(
+            x, (const DT*)delta, nsplit, (size_t)split_stride, weight, eps, rows, (OT*)out, H)));
+    return check_launch("add_rmsnorm");
+}
+
+MHB_EXPORT int mhb_residual_add(float* x, const void* delta, int delta_dtype, int nsplit,
+                                long long split_stride, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (nsplit > 1 && delta_dtype != MHB_F32) return fail("residual_add: split partials must be float32");
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+    MHB_DISPATCH_DTYPE(delta_dtype, DT,
+        residual_add_kernel<DT><<<blocks, threads, 0, stream>>>(x, (const DT*)delta, nsplit,
+                                                                 (size_t)split_stride, (size_t)n));
+    return check_launch("residual_add");
+}
+
+// ---- rotary positions + paged KV append -----------------------------------------------------
+// qkv[t] = [q heads | k heads | v heads], each head `d` wide, plus an optional float32 bias.
+// q and k are rotated by the half-split rule of mini_hisparse/model.py:141-151:
+//   angle = float(position) * inv_freq[i],  out[j] = t[j]*cos + (j < d/2 ? -t[j+d/2] : t[j-d/2])*sin
+// Rotated q goes to q_out [T, nq*d]; rotated k and plain v go into the cache page of the
+// token's position (the append happens before attention, model.py:169-170, 201):
+//   cache[page][0 or 1][kv head][position % P][d],  page = block_table[seg][position / P].
+// With write_kv == 0 nothing is appended (a layer that reads another layer's cache).
+template <typename IT, typename QT, typename CT>
+__global__ void rope_append_kernel(const IT* __restrict__ qkv, int nsplit, size_t split_stride,
+                                   const float* __restrict__ bias, const int* __restrict__ positions,
+                                   const int* __restrict__ tok_seg, const int* __restrict__ block_table,
+                                   int table_width, const float* __restrict__ inv_freq,
+                                   QT* __restrict__ q_out, CT* __restrict__ cache, int nq, int nkv,
+                                   int d, int P, int num_pages, int write_kv, int rotate_q_k,
+                                   int* __restrict__ status) {
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = d >> 1;
+    const int width = (nq + 2 * nkv) * d;
+    const IT* in = qkv;
+    const size_t base = (size_t)t * width;
+    int page = -1;
+    if (write_kv) {
+        page = block_table[(size_t)tok_seg[t] * table_width + pos / P];
+        if (page < 0 || page >= num_pages) {  // never write outside the pool
+            if (threadIdx.x == 0 && status) atomicOr(status, 2);
+            page = -1;
+        }
+    }
+    const int within = pos % P;
+    // q and k heads: one thread per (head, i < d/2) pair
+    const int pairs = (nq + nkv) * half;
+    for (int idx = threadIdx.x; idx < pairs; idx += blockDim.x) {
+        const int head = idx / half, i = idx - head * half;
+        const int col = head * d + i;
+        float a = load_split(in, base + col, nsplit, split_stride);
+        float b = load_split(in, base + col + half, nsplit, split_stride);
+        if (bias) { a += bias[col]; b += bias[col + half]; }
+        float oa = a, ob = b;
+        if (rotate_q_k) {
+            const float angle = (float)pos * inv_freq[i];
+            float sn, cs;
+            sincosf(angle, &sn, &cs);
+            oa = a * cs - b * sn;
+            ob = b * cs + a * sn;
+        }
+        if (head < nq) {
+            q_out[(size_t)t * nq * d + col] = from_float<QT>(oa);
+            q_out[(size_t)t * nq * d + col + half] = from_float<QT>(ob);
+        } else if (page >= 0) {
+            const int kh = head - nq;
+            CT* dst = cache + ((((size_t)page * 2 + 0) * nkv + kh) * P + within) * d;
+            dst[i] = from_float<CT>(oa);
+            dst[i + half] = from_float<CT>(ob);
+        }
+    }
+    if (page >= 0) {
+        const int vbase = (nq + nkv) * d;
+        for (int idx = threadIdx.x; idx < nkv * d; idx += blockDim.x) {
+            const int kh = idx / d, e = idx - kh * d;
+            float v = load_split(in, base + vbase + idx, nsplit, split_stride);
+            if (bias) v += bias[vbase + idx];
+            cache[((((size_t)page * 2 + 1) * nkv + kh) * P + within) * d + e] = from_float<CT>(v);
+        }
+    }
+}
+
+MHB_EXPORT int mhb_rope_append(const void* qkv, int in_dtype, int nsplit, long long split_stride,
+                               const float* bias, const int* positions, const int* tok_seg,
+                               const int* block_table, int table_width, const float* inv_freq,
+                               void* q_out, void* cache, int act_dtype, int T, int nq, int nkv,
+                               int d, int P, int num_pages, int write_kv, int rotate,
+                               int* status, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (d % 2) return fail("rope_append: head_dim %d must be even", d);
+    if (nsplit > 1 && in_dtype != MHB_F32) return fail("rope_append: split partials must be float32");
+    const int threads = 256;
+    MHB_DISPATCH_DTYPE(in_dtype, IT, MHB_DISPATCH_DTYPE(act_dtype, AT,
+        rope_append_kernel<IT, AT, AT><<<T, threads, 0, stream>>>(
+            (const IT*)qkv, nsplit, (size_t)split_stride, bias, positions, tok_seg, block_table,
+            table_width, inv_freq, (AT*)q_out, (AT*)cache, nq, nkv, d, P, num_pages, write_kv,
+            rotate, status)));
+    return check_launch("rope_append");
+}
+
+// ---- SwiGLU gate ------------------------------------------------------------------------------
+// gu[t] = [gate (I) | up (I)]  ->  out[t, i] = silu(gate_i) * up_i   (mini_hisparse/model.py:70-71)
+template <typename IT, typename OT>
+__global__ void swiglu_kernel(const IT* __restrict__ gu, int nsplit, size_t split_stride,
+                              OT* __restrict__ out, int I, size_t total) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t t = idx / I;
+    const int i = (int)(idx - t * I);
+    const float g = load_split(gu, t * 2 * I + i, nsplit, split_stride);
+    const float u = load_split(gu, t * 2 * I + I + i, nsplit, split_stride);
+    const float s = g / (1.f + expf(-g));
+    out[idx] = from_float<OT>(s * u);
+}
+
+MHB_EXPORT int mhb_swiglu(const void* gu, int in_dtype, int nsplit, long long split_stride,
+                          void* out, int out_dtype, int T, int I, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (nsplit > 1 && in_dtype != MHB_F32) return fail("swiglu: split partials must be float32");
+    const size_t total = (size_t)T * I;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    MHB_DISPATCH_DTYPE(in_dtype, IT, MHB_DISPATCH_DTYPE(out_dtype, OT,
+        swiglu_kernel<IT, OT><<<blocks, threads, 0, stream>>>((const IT*)gu, nsplit,
+                                                            (size_t)split_stride, (OT*)out, I, total)));
+    return check_launch("swiglu");
+}

@@ -1,0 +1,96 @@
+// C[M,N] = A[M,K] * W[N,K]^T (+ bias) on the CUDA cores with float32 accumulation.
+//
+// This is the matrix product of the true 32-bit path (plain FFMA: no TF32, no tensor core,
+// no reduced-precision intermediate) and the any-shape product of the bfloat16 path for sizes
+// the tensor-core kernel refuses.  A and W are row-major with K contiguous, the layout of
+// nn.Linear (mini_hisparse/model.py:57-60: y = x W^T + b).
+//
+// With nsplit > 1 the K range is cut into nsplit parts; part z writes a float32 partial
+// matrix at C + z*split_stride and the consumer sums the parts in order.
+#include "common.cuh"
+
+using namespace mhb;
+
+MHB_EXPORT const char* mhb_last_error() { return error_buffer(); }
+
+namespace {
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4, THREADS = 256;
+
+template <typename AT, typename WT, typename OT>
+__global__ void __launch_bounds__(THREADS)
+gemm_simt_kernel(const AT* __restrict__ A, const WT* __restrict__ W, OT* __restrict__ C,
+                 const float* __restrict__ bias, int M, int N, int K, long long lda, long long ldw,
+                 long long ldc, int k_per_split, long long split_stride) {
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int k_begin = blockIdx.z * k_per_split;
+    const int k_end = min(K, k_begin + k_per_split);
+    const int tx = tid % 16, ty = tid / 16;  // 16 x 16 threads, 4 x 4 outputs each
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+
+    const int lrow = tid / 4;        // 0..63
+    const int lk = (tid % 4) * 4;    // 0,4,8,12
+    for (int k0 = k_begin; k0 < k_end; k0 += BK) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int k = k0 + lk + j;
+            const int am = m0 + lrow, wn = n0 + lrow;
+            As[lk + j][lrow] = (am < M && k < k_end) ? to_float(A[(size_t)am * lda + k]) : 0.f;
+            Ws[lk + j][lrow] = (wn < N && k < k_end) ? to_float(W[(size_t)wn * ldw + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float a[TM], w[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = As[k][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) w[j] = Ws[k][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    OT* Cz = C + (size_t)blockIdx.z * split_stride;
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int m = m0 + ty * TM + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + tx * TN + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (bias && blockIdx.z == 0) v += bias[n];
+            Cz[(size_t)m * ldc + n] = from_float<OT>(v);
+        }
+    }
+}
+}  // namespace
+
+MHB_EXPORT int mhb_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* C,
+                             int c_dtype, const float* bias, int M, int N, int K, long long lda,
+                             long long ldw, long long ldc, int nsplit, long long split_stride,
+                             cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0) return fail("gemm: K must be positive");
+    if (nsplit < 1) nsplit = 1;
+    if (nsplit > 1 && c_dtype != MHB_F32) return fail("gemm: split-K partials must be float32");
+    int k_per_split = (K + nsplit - 1) / nsplit;
+    k_per_split = (k_per_split + BK - 1) / BK * BK;
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, nsplit);
+    if (grid.y > 65535) return fail("gemm: M %d too large for one launch", M);
+    MHB_DISPATCH_DTYPE(a_dtype, AT, MHB_DISPATCH_DTYPE(w_dtype, WT, MHB_DISPATCH_DTYPE(c_dtype, OT,
+        gemm_simt_kernel<AT, WT, OT><<<grid, THREADS, 0, stream>>>(
+            (const AT*)A, (const WT*)W, (OT*)C, bias, M, N, K, lda, ldw, ldc, k_per_split,
+            split_stride))));
+    return check_launch("gemm_simt");
+}

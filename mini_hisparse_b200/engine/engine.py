@@ -1,0 +1,127 @@
+"""The Python entry point: load a model folder, add requests, step, run.
+
+In the reference's manner (mini_hisparse/engine.py:24-146; examples/long_context_chat.py:58-81):
+``Engine.add_request(request_id, prompt, max_new_tokens)``, ``step() -> [(id, token)]``,
+``run() -> {id: tokens}``, ``cancel(id)``; ``load_model`` stands where
+``MiniModel.from_pretrained(name, device, dtype)`` does (mini_hisparse/model.py:98-125).
+"""
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+from ..cache.manager import CacheConfig, CacheManager
+from ..config.registry import resolve
+from ..models.decoder import DecoderModel
+from ..parts.base import Runtime
+from ..sampling.sampler import Sampler, SamplingParams
+from ..weights.loader import init_random, load_weights
+from .scheduler import Request, Scheduler, SchedulerConfig
+from .step import ModelRunner, StepEntry
+
+_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "fp32": torch.float32,
+           "bf16": torch.bfloat16, torch.float32: torch.float32, torch.bfloat16: torch.bfloat16}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise ValueError(f"dtype must be float32 or bfloat16, not {dtype!r}") from None
+
+
+def make_runtime(device="cuda:0", dtype="bfloat16") -> Runtime:
+    from ..kernels.runtime import make_runtime as _make
+
+    return _make(device, parse_dtype(dtype))
+
+
+def load_model(source, device="cuda:0", dtype="bfloat16", random_seed: int | None = None) -> DecoderModel:
+    """Build the model that ``source`` (a folder with config.json, a config file, or a config
+    mapping) names in its "architectures", and load its safetensors weights; with
+    ``random_seed`` the weights are drawn on the device instead and no file is read."""
+    cfg, spec = resolve(source)
+    rt = make_runtime(device, dtype)
+    model = DecoderModel(spec, rt, config=cfg)
+    if random_seed is not None:
+        init_random(model, random_seed)
+    else:
+        load_weights(model, Path(source))
+    return model
+
+
+class Engine:
+    def __init__(self, model: DecoderModel, cache_config: CacheConfig | None = None, *,
+                 num_pages: int | None = None, page_size: int = 16, max_requests: int = 8,
+                 max_tokens_per_step: int = 2048, eos_token_id: int | None = None,
+                 use_graphs: bool = True):
+        self.model = model
+        if cache_config is None:
+            if num_pages is None:
+                raise ValueError("give a CacheConfig or num_pages")
+            cache_config = CacheConfig(num_pages=num_pages, page_size=page_size,
+                                       max_requests=max_requests, dtype=model.rt.dtype,
+                                       device=str(model.rt.device))
+        if cache_config.dtype != model.rt.dtype or torch.device(cache_config.device) != model.rt.device:
+            raise ValueError("model/cache dtype or device differ")   # mini_hisparse/engine.py:36-38
+        self.cache = CacheManager(model.cache_needs, cache_config)
+        self.runner = ModelRunner(model, self.cache, use_graphs=use_graphs)
+        eos = eos_token_id if eos_token_id is not None else model.spec.eos_token_id
+        self.scheduler = Scheduler(self.cache, SchedulerConfig(max_tokens_per_step),
+                                   model.spec.vocab_size, model.spec.max_positions, eos)
+        self.sampler = Sampler(model.rt.device, max_rows=cache_config.max_requests)
+        self.timeline: list[dict] = []
+
+    # ---- the reference's five calls ------------------------------------------------------------
+    @property
+    def requests(self) -> dict:
+        return self.scheduler.requests
+
+    @property
+    def waiting(self):
+        return self.scheduler.waiting
+
+    @property
+    def running(self):
+        return self.scheduler.running
+
+    def add_request(self, request_id, prompt, max_new_tokens: int = 16, temperature: float = 0.0,
+                    seed: int = 0, eos_token_id: int | None = None) -> Request:
+        params = SamplingParams(max_new_tokens=max_new_tokens, temperature=temperature, seed=seed,
+                                eos_token_id=eos_token_id)
+        return self.scheduler.add(request_id, prompt, params)
+
+    def step(self) -> list[tuple[object, int]]:
+        planned = self.scheduler.plan()
+        if not planned:
+            return []
+        entries = [StepEntry(p.request.request_id, p.tokens, [len(p.tokens) - 1] if p.sample else [])
+                   for p in planned]
+        logits = self.runner.step(entries)
+        sampled: list[int] = []
+        if logits is not None:
+            rs = [p.request for p in planned if p.sample]
+            sampled = self.sampler.sample(
+                logits,
+                [r.params.temperature for r in rs],
+                [r.params.seed for r in rs],
+                [len(r.generated) for r in rs],
+            )
+        self.runner.check_status()
+        emitted = self.scheduler.commit(planned, sampled)
+        self.timeline.append({"active": len(self.scheduler.running), "waiting": len(self.scheduler.waiting),
+                              "tokens": sum(len(p.tokens) for p in planned)})
+        return emitted
+
+    def run(self) -> dict:
+        while not self.scheduler.idle:
+            self.step()
+        return {name: r.generated for name, r in self.scheduler.requests.items()}
+
+    def cancel(self, request_id) -> None:
+        self.scheduler.cancel(request_id)
+
+    def snapshot(self) -> dict:
+        return {"cache": self.cache.snapshot(), "scheduler": dict(self.scheduler.stats),
+                "runner": dict(self.runner.stats)}

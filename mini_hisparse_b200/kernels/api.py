@@ -1,0 +1,163 @@
+"""Python face of the CUDA kernels: torch tensors in, a launch on the current stream out.
+
+There is no CPU or library fallback here: every function launches a kernel of ``csrc/``
+and raises :class:`KernelError` if the library is missing, the tensors are not on a CUDA
+device, or a size is outside what the kernel takes.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import build
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DT[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 and bfloat16, not {dtype}") from None
+
+
+def _ptr(t: torch.Tensor | None):
+    if t is None:
+        return c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError(
+            "a tensor on the CPU reached a CUDA kernel: this engine has no CPU path"
+        )
+    return c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(lib, code: int, what: str):
+    if code != 0:
+        raise KernelError(f"{what}: {lib.mhb_last_error().decode()}")
+
+
+def _contig(t: torch.Tensor, name: str):
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+# ---------------------------------------------------------------------------------------
+def embed(table, tokens, out, status=None):
+    """out[t] = table[tokens[t]] as float32; ids outside the table give zeros and set status bit 0."""
+    lib = build.load("elementwise")
+    T, H = out.shape
+    _check(lib, lib.mhb_embed(_ptr(table), c_int(dtype_code(table.dtype)), _ptr(tokens), _ptr(out),
+                              c_int(T), c_int(H), c_int(table.shape[0]), _ptr(status), _stream()),
+           "embed")
+
+
+def add_rmsnorm(x, weight, eps, out, delta=None, nsplit=1, split_stride=0, rows=None):
+    """out[r] = rmsnorm(x[s] + delta[s]) * weight with s = rows[r] if rows is given else r.
+
+    Without ``rows`` and with ``delta`` the sum is written back to ``x`` (the residual).
+    ``delta`` may be ``nsplit`` float32 partial matrices ``split_stride`` elements apart.
+    """
+    lib = build.load("elementwise")
+    R, H = out.shape
+    ddt = dtype_code(delta.dtype) if delta is not None else F32
+    _check(lib, lib.mhb_add_rmsnorm(_ptr(x), _ptr(delta), c_int(ddt), c_int(nsplit),
+                                    c_longlong(split_stride), _ptr(weight), c_float(eps),
+                                    _ptr(rows), _ptr(out), c_int(dtype_code(out.dtype)),
+                                    c_int(R), c_int(H), _stream()), "add_rmsnorm")
+
+
+def residual_add(x, delta, nsplit=1, split_stride=0):
+    lib = build.load("elementwise")
+    _check(lib, lib.mhb_residual_add(_ptr(x), _ptr(delta), c_int(dtype_code(delta.dtype)),
+                                     c_int(nsplit), c_longlong(split_stride),
+                                     c_longlong(x.numel()), _stream()), "residual_add")
+
+
+def rope_append(qkv, bias, positions, tok_seg, block_table, inv_freq, q_out, cache, *, nq, nkv, d,
+                page_size, write_kv=True, rotate=True, nsplit=1, split_stride=0, status=None):
+    """Bias + rotary encoding of q and k, q to ``q_out``, k and v into the cache pages.
+
+    ``cache`` is one layer's pool [pages, 2, nkv, page_size, d]; ``block_table`` [S, width]
+    holds the page ids of each segment of the batch, ``tok_seg`` [T] the segment of a token.
+    """
+    lib = build.load("elementwise")
+    T = q_out.shape[0]
+    if cache.dtype != q_out.dtype:
+        raise KernelError("rope_append: cache and activations must have one dtype")
+    _check(lib, lib.mhb_rope_append(
+        _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_int(nsplit), c_longlong(split_stride),
+        _ptr(bias), _ptr(positions), _ptr(tok_seg), _ptr(block_table),
+        c_int(block_table.shape[-1]), _ptr(inv_freq), _ptr(q_out), _ptr(cache),
+        c_int(dtype_code(q_out.dtype)), c_int(T), c_int(nq), c_int(nkv), c_int(d),
+        c_int(page_size), c_int(cache.shape[0]), c_int(1 if write_kv else 0),
+        c_int(1 if rotate else 0), _ptr(status), _stream()), "rope_append")
+
+
+def swiglu(gate_up, out, nsplit=1, split_stride=0):
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    lib = build.load("elementwise")
+    T, I = out.shape
+    _check(lib, lib.mhb_swiglu(_ptr(gate_up), c_int(dtype_code(gate_up.dtype)), c_int(nsplit),
+                               c_longlong(split_stride), _ptr(out), c_int(dtype_code(out.dtype)),
+                               c_int(T), c_int(I), _stream()), "swiglu")
+
+
+def gemm_simt(a, w, out, bias=None, nsplit=1, split_stride=0):
+    """out[M, N] = a[M, K] @ w[N, K]^T (+ bias) with float32 accumulation on the CUDA cores."""
+    lib = build.load("gemm_simt")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"gemm: a is [{M},{K}] but w is {list(w.shape)}")
+    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(-1) != 1:
+        raise KernelError("gemm: the last dimension must be contiguous")
+    _check(lib, lib.mhb_gemm_simt(
+        _ptr(a), c_int(dtype_code(a.dtype)), _ptr(w), c_int(dtype_code(w.dtype)), _ptr(out),
+        c_int(dtype_code(out.dtype)), _ptr(bias), c_int(M), c_int(N), c_int(K),
+        c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(-2)),
+        c_int(nsplit), c_longlong(split_stride), _stream()), "gemm_simt")
+
+
+def attention_simt(q, cache, out, part_acc, part_ml, items, num_items, max_items, positions,
+                   block_table, tok_part_row, *, nq, nkv, d, page_size, window=0, scale=None):
+    lib = build.load("attention_simt")
+    if scale is None:
+        scale = float(d) ** -0.5
+    _check(lib, lib.mhb_attention_simt(
+        _ptr(q), _ptr(cache), _ptr(out), c_int(dtype_code(q.dtype)), _ptr(part_acc), _ptr(part_ml),
+        _ptr(items), c_int(num_items), c_int(max_items), _ptr(positions), _ptr(block_table),
+        c_int(block_table.shape[-1]), _ptr(tok_part_row), c_int(nq), c_int(nkv), c_int(d),
+        c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_float(scale), _stream()),
+        "attention")
+
+
+def attention_combine(part_acc, part_ml, tok_part_row, tok_nsplit, out, *, nq, d):
+    lib = build.load("attention_simt")
+    T = out.shape[0]
+    _check(lib, lib.mhb_attention_combine(_ptr(part_acc), _ptr(part_ml), _ptr(tok_part_row),
+                                          _ptr(tok_nsplit), _ptr(out), c_int(dtype_code(out.dtype)),
+                                          c_int(T), c_int(nq), c_int(d), _stream()),
+           "attention_combine")
+
+
+def sample(logits, temperature, seed, counter, out):
+    """out[r] = argmax(logits[r]) where temperature[r] <= 0, else a draw from softmax(logits/T)."""
+    lib = build.load("sampling")
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 with a contiguous last dimension")
+    _check(lib, lib.mhb_sample(_ptr(logits), c_longlong(logits.stride(0)), c_int(R), c_int(V),
+                               _ptr(temperature), _ptr(seed), _ptr(counter), _ptr(out), _stream()),
+           "sample")

@@ -1,0 +1,185 @@
+"""Grouped-query attention over the paged cache, and the plan of its work for one step."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from ..kernels import api as K
+from .base import CacheView, Mixer, Product, StepContext
+from .registry import POSITIONS, register_mixer
+from .spec import PagedKVNeed, ParamSpec, PartSpec
+
+ROW_TILE = 16          # query rows (tokens x heads of one group) per CTA of the attention kernel
+KEY_TILE = 32          # keys per inner tile; split boundaries are multiples of it
+ITEM_INTS = 8
+MIN_KEYS_PER_SPLIT = 256
+SPLIT_MAX_TOKENS = 16  # only short segments (decode tokens, tiny portions) are split along the keys
+MAX_SPLITS = 64
+
+
+@dataclass
+class AttentionPlan:
+    """Host arrays of one page group for one step (see csrc/attention_simt.cu for the item layout)."""
+
+    items: np.ndarray          # [n_items, 8] int32
+    tok_part_row: np.ndarray   # [T] int32
+    tok_nsplit: np.ndarray     # [T] int32: 0 = written directly
+    part_rows: int
+
+
+def plan_attention(need: PagedKVNeed, segments, T: int, sm_count: int = 148,
+                   fixed_nsplit: int | None = None) -> AttentionPlan:
+    """Cut the step's attention into items of at most ROW_TILE query rows.
+
+    A tile is a run of tokens of one segment times the heads of one KV group (or a chunk of
+    them, if a group has more heads than a tile has rows).  Its keys are [kv_begin, kv_end):
+    everything up to its last token, minus what a window has passed.  Short segments with long
+    histories are split along the keys so that a small batch still fills the GPU; with
+    ``fixed_nsplit`` every short segment gets exactly that many splits (a captured graph needs
+    a fixed launch size), empty ones included.
+    """
+    groups = need.q_heads // need.kv_heads
+    if groups <= ROW_TILE:
+        head_chunks = [(0, groups)]
+        tok_per_tile = ROW_TILE // groups
+    else:
+        head_chunks = [(h, min(ROW_TILE, groups - h)) for h in range(0, groups, ROW_TILE)]
+        tok_per_tile = 1
+    window = need.window or 0
+    tiles = []
+    for si, seg in enumerate(segments):
+        for a in range(0, seg.count, tok_per_tile):
+            nt = min(tok_per_tile, seg.count - a)
+            first_pos = seg.start + a
+            kv_end = first_pos + nt
+            kv_begin = max(0, first_pos - window + 1) if window else 0
+            tiles.append((si, seg.offset + a, nt, kv_begin, kv_end, seg.count))
+    base_ctas = len(tiles) * len(head_chunks) * need.kv_heads
+    items = []
+    tok_part_row = np.zeros(T, np.int32)
+    tok_nsplit = np.zeros(T, np.int32)
+    part_rows = 0
+    for si, tok0, nt, kv_begin, kv_end, seg_count in tiles:
+        nsplit = 1
+        if seg_count <= SPLIT_MAX_TOKENS:
+            if fixed_nsplit is not None:
+                nsplit = fixed_nsplit
+            elif base_ctas < 2 * sm_count:
+                want = -(-2 * sm_count // max(base_ctas, 1))
+                fit = max(1, (kv_end - kv_begin) // MIN_KEYS_PER_SPLIT)
+                nsplit = max(1, min(want, fit, MAX_SPLITS))
+        if nsplit == 1:
+            for h0, nh in head_chunks:
+                items.append((si, tok0, nt, h0, nh, kv_begin, kv_end, -1))
+            continue
+        span = kv_end - kv_begin
+        chunk = -(-span // nsplit)
+        chunk = -(-chunk // KEY_TILE) * KEY_TILE
+        for t in range(tok0, tok0 + nt):
+            tok_part_row[t] = part_rows
+            tok_nsplit[t] = nsplit
+            part_rows += nsplit
+        for s in range(nsplit):
+            b = min(kv_end, kv_begin + s * chunk)
+            e = min(kv_end, b + chunk)
+            for h0, nh in head_chunks:
+                items.append((si, tok0, nt, h0, nh, b, e, s))
+    arr = np.asarray(items, np.int32).reshape(-1, ITEM_INTS)
+    return AttentionPlan(arr, tok_part_row, tok_nsplit, part_rows)
+
+
+def plan_capacity(need: PagedKVNeed, max_tokens: int, max_segments: int,
+                  fixed_nsplit: int | None = None) -> tuple[int, int]:
+    """Upper bounds (items, partial rows) for a step of at most max_tokens / max_segments."""
+    groups = need.q_heads // need.kv_heads
+    chunks = 1 if groups <= ROW_TILE else -(-groups // ROW_TILE)
+    tok_per_tile = max(1, ROW_TILE // groups)
+    splits = fixed_nsplit or MAX_SPLITS
+    # every segment may end with a ragged tile; short segments may be split
+    tiles = max_tokens // tok_per_tile + max_segments
+    short_tiles = min(tiles, max_segments * -(-SPLIT_MAX_TOKENS // tok_per_tile))
+    items = (tiles + short_tiles * (splits - 1)) * chunks
+    part_rows = min(max_tokens, max_segments * SPLIT_MAX_TOKENS) * splits
+    return items, part_rows
+
+
+@register_mixer("gq_attention")
+class GQAttention(Mixer):
+    """q/k/v projections (with bias), position encoding on q and k, append to the cache, causal
+    grouped-query attention over the cache, output projection without bias
+    (mini_hisparse/model.py:54-60, 135-153, 169-179, 157).
+
+    Sizes are parameters: hidden_size, q_heads, kv_heads, head_dim, qkv_bias, window, and the
+    position encoding's own spec.  Query head h reads KV head h // (q_heads // kv_heads).
+    """
+
+    def __init__(self, spec: PartSpec, rt=None):
+        super().__init__(spec, rt)
+        self.hidden = int(spec["hidden_size"])
+        self.nq = int(spec["q_heads"])
+        self.nkv = int(spec["kv_heads"])
+        self.d = int(spec["head_dim"])
+        self.qkv_bias = bool(spec.get("qkv_bias", True))
+        self.window = spec.get("window")
+        if self.nq % self.nkv:
+            raise ValueError(f"{self.nq} query heads cannot be grouped over {self.nkv} KV heads")
+        if self.d % 16 or not 16 <= self.d <= 256:
+            raise ValueError(f"head_dim {self.d} is not supported: kernels take 16..256 in steps of 16")
+        self.position = POSITIONS.build(spec["position"], rt=rt)
+        self.scale = float(self.d) ** -0.5
+        self.qkv_weight = self.qkv_bias_vec = self.o_weight = None
+
+    def cache_need(self):
+        return PagedKVNeed(kv_heads=self.nkv, head_dim=self.d, q_heads=self.nq, window=self.window)
+
+    def parameters(self):
+        q, kv = self.nq * self.d, self.nkv * self.d
+        p = {
+            "q_proj.weight": ParamSpec((q, self.hidden)),
+            "k_proj.weight": ParamSpec((kv, self.hidden)),
+            "v_proj.weight": ParamSpec((kv, self.hidden)),
+            "o_proj.weight": ParamSpec((self.hidden, q)),
+        }
+        if self.qkv_bias:
+            p["q_proj.bias"] = ParamSpec((q,), role="vector")
+            p["k_proj.bias"] = ParamSpec((kv,), role="vector")
+            p["v_proj.bias"] = ParamSpec((kv,), role="vector")
+        return p
+
+    def load(self, tensors):
+        self.qkv_weight = torch.cat(
+            (tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]), 0
+        ).contiguous()
+        if self.qkv_bias:
+            self.qkv_bias_vec = torch.cat(
+                (tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]), 0
+            ).contiguous()
+        self.o_weight = tensors["o_proj.weight"].contiguous()
+
+    def forward(self, h, ctx: StepContext, cache: CacheView) -> Product:
+        rt, ws, T = ctx.rt, ctx.ws, h.shape[0]
+        meta = cache.meta
+        qkv = rt.linear(h, self.qkv_weight, ws, "qkv", out_dtype=torch.float32)
+        q = ws.get("q", (T, self.nq * self.d), rt.dtype)
+        K.rope_append(
+            qkv.tensor, self.qkv_bias_vec, ctx.positions, ctx.tok_seg, meta["block_table"],
+            self.position.inv_freq, q, cache.storage, nq=self.nq, nkv=self.nkv, d=self.d,
+            page_size=cache.page_size, write_kv=cache.writable, rotate=self.position.rotates,
+            nsplit=qkv.nsplit, split_stride=qkv.split_stride, status=ctx.status,
+        )
+        attn = ws.get("attn", (T, self.nq * self.d), rt.dtype)
+        part_rows = max(1, meta["part_rows_cap"])
+        part_acc = ws.get("attn_part_acc", (part_rows, self.nq, self.d), torch.float32)
+        part_ml = ws.get("attn_part_ml", (part_rows, self.nq, 2), torch.float32)
+        K.attention_simt(
+            q, cache.storage, attn, part_acc, part_ml, meta["items"], meta["num_items"],
+            meta["launch_items"], ctx.positions, meta["block_table"], meta["tok_part_row"],
+            nq=self.nq, nkv=self.nkv, d=self.d, page_size=cache.page_size,
+            window=self.window or 0, scale=self.scale,
+        )
+        if meta["any_split"]:
+            K.attention_combine(part_acc, part_ml, meta["tok_part_row"], meta["tok_nsplit"], attn,
+                                nq=self.nq, d=self.d)
+        return rt.linear(attn, self.o_weight, ws, "mix_out")

@@ -1,0 +1,185 @@
+"""What every part sees: the runtime (device, compute dtype, matrix products), the workspace,
+and the step context (the batch's tokens, segments and cache views).
+
+Interfaces, in short:
+
+* ``Part.parameters()`` -> {local name: ParamSpec}; ``Part.load(tensors)`` receives them on the
+  device in the dtype their role asks for and may fuse or re-lay them out.
+* ``Norm.forward(x, ctx, delta=None, rows=None)``: x is the float32 residual [T, H]; with
+  ``delta`` the sum x + delta is written back to x first; returns the normalised rows in the
+  compute dtype.
+* ``Mixer.cache_need()`` -> CacheNeed | None;
+  ``Mixer.forward(h, ctx, cache)`` -> Product [T, H]; ``cache`` is a view of the entry's cache
+  (``cache.writable`` is False when the entry only reads another entry's cache).
+* ``FeedForward.forward(h, ctx)`` -> Product [T, H].
+* ``Block.forward(x, pending, ctx, cache)`` -> pending: the block adds ``pending`` (the previous
+  block's last output) into x where it normalises, and returns its own last output unadded.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+
+from ..kernels import api as K
+from .spec import CacheNeed, ParamSpec, PartSpec
+
+
+# ---------------------------------------------------------------------------------------
+@dataclass
+class Product:
+    """The result of a matrix product: one matrix, or ``nsplit`` float32 partial matrices
+    [nsplit, M, N] that the consumer sums in order (split-K)."""
+
+    tensor: torch.Tensor
+    nsplit: int = 1
+
+    @property
+    def split_stride(self) -> int:
+        return self.tensor.stride(0) if self.nsplit > 1 else 0
+
+    @property
+    def matrix(self) -> torch.Tensor:
+        if self.nsplit > 1:
+            raise ValueError("split product has not been reduced")
+        return self.tensor
+
+
+class Workspace:
+    """Named scratch buffers, reused layer after layer.  ``frozen`` forbids growth (a captured
+    CUDA graph holds the addresses)."""
+
+    def __init__(self, device):
+        self.device = device
+        self._buffers: dict[str, torch.Tensor] = {}
+        self.frozen = False
+
+    def get(self, name: str, shape, dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * dtype.itemsize
+        buf = self._buffers.get(name)
+        if buf is None or buf.numel() < nbytes:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer {name!r} would grow after it was frozen")
+            cap = max(nbytes, 256)
+            buf = torch.empty(cap, dtype=torch.uint8, device=self.device)
+            self._buffers[name] = buf
+        return buf[:nbytes].view(dtype).view(*shape)
+
+    def nbytes(self) -> int:
+        return sum(b.numel() for b in self._buffers.values())
+
+
+class Runtime:
+    """Device, compute dtype and the matrix product for that dtype."""
+
+    def __init__(self, device="cuda:0", dtype=torch.bfloat16):
+        self.device = torch.device(device)
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"compute dtype must be float32 or bfloat16, not {dtype}")
+        self.dtype = dtype
+        if self.device.type != "cuda":
+            raise K.KernelError(
+                f"device {self.device} is not a CUDA device: this engine runs its own sm_100a "
+                "kernels only and has no CPU path"
+            )
+
+    def kernel_modules(self) -> tuple[str, ...]:
+        return ("elementwise", "gemm_simt", "attention_simt", "sampling")
+
+    def linear(self, x: torch.Tensor, weight: torch.Tensor, ws: Workspace, name: str,
+               out_dtype: torch.dtype | None = None, bias: torch.Tensor | None = None) -> Product:
+        """x [M, K] times weight [N, K] transposed, float32 accumulation."""
+        M, N = x.shape[0], weight.shape[0]
+        out = ws.get(name, (M, N), out_dtype or self.dtype)
+        K.gemm_simt(x, weight, out, bias=bias)
+        return Product(out)
+
+
+# ---------------------------------------------------------------------------------------
+@dataclass
+class Segment:
+    """Consecutive tokens of one request inside a step's batch."""
+
+    request: Any          # the request's id
+    slot: int             # its state slot
+    start: int            # position of the first token
+    count: int            # tokens in this step
+    offset: int           # index of the first token in the batch
+
+
+@dataclass
+class CacheView:
+    """What a mixer gets for its cache entry in one step."""
+
+    need: CacheNeed | None
+    group: int
+    index: int                      # layer index inside the group
+    writable: bool
+    storage: torch.Tensor | None    # pages: [pages, 2, nkv, P, d]; state: [max_requests, *shape]
+    page_size: int = 0
+    meta: dict = field(default_factory=dict)   # device views of the group's per-step arrays
+
+
+@dataclass
+class StepContext:
+    rt: Runtime
+    ws: Workspace
+    T: int
+    segments: list[Segment]
+    tokens: torch.Tensor            # [T] int32
+    positions: torch.Tensor         # [T] int32
+    tok_seg: torch.Tensor           # [T] int32: segment of each token
+    seg_slot: torch.Tensor          # [S] int32: state slot of each segment
+    status: torch.Tensor            # [1] int32 error bits set by kernels
+    extras: dict = field(default_factory=dict)
+
+
+# ---------------------------------------------------------------------------------------
+class Part:
+    """Base of all parts: a spec, stored tensors, nothing about the model around it."""
+
+    def __init__(self, spec: PartSpec, rt: Runtime | None = None):
+        self.spec = spec
+        self.rt = rt
+
+    def parameters(self) -> dict[str, ParamSpec]:
+        return {}
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        for k, v in tensors.items():
+            setattr(self, k.replace(".", "_"), v)
+
+    def nbytes(self) -> int:
+        total = 0
+        for v in vars(self).values():
+            if isinstance(v, torch.Tensor):
+                total += v.numel() * v.element_size()
+        return total
+
+
+class Mixer(Part):
+    def cache_need(self) -> CacheNeed | None:
+        return None
+
+    def forward(self, h: torch.Tensor, ctx: StepContext, cache: CacheView | None) -> Product:
+        raise NotImplementedError
+
+    #: False if forward() does host-side work that depends on the batch (no CUDA graph then)
+    graph_safe = True
+
+
+class FeedForward(Part):
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> Product:
+        raise NotImplementedError
+
+    graph_safe = True
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, ctx: StepContext, delta: Product | None = None,
+                rows: torch.Tensor | None = None, name: str = "h") -> torch.Tensor:
+        raise NotImplementedError
