@@ -99,7 +99,8 @@ class PageAllocator:
         for p in pages:
             self._owner[p] = None
             self._free.append(p)
-        self._held[owner] -= len(pages)
+        if pages:
+            self._held[owner] -= len(pages)
 
     def release_owner(self, owner) -> None:
         """Drop the owner's reservation; it must hold no pages any more."""

@@ -57,8 +57,11 @@ class PageGroup:
     def __init__(self, gid: int, need: PagedKVNeed, entries: list[int], cfg: CacheConfig):
         self.gid, self.need, self.entries, self.cfg = gid, need, entries, cfg
         self.allocator = PageAllocator(cfg.num_pages)
+        # the table is indexed by logical page: a full group never needs more entries than the
+        # pool has pages; a windowed group gives pages back and can run far past the pool's size
         self.width = cfg.max_pages_per_request or cfg.num_pages
-        self.width = min(self.width, cfg.num_pages)
+        if need.window is None:
+            self.width = min(self.width, cfg.num_pages)
         self.tables: dict[int, _RequestPages] = {}       # slot -> pages
         shape = (len(entries), cfg.num_pages, 2, need.kv_heads, cfg.page_size, need.head_dim)
         self.storage = (
@@ -133,7 +136,8 @@ class CacheManager:
     # ---- requests -------------------------------------------------------------------------
     def can_ever_fit(self, total_tokens: int, max_step_tokens: int | None = None) -> bool:
         return all(
-            g.pages_for(total_tokens, max_step_tokens) <= min(g.cfg.num_pages, g.width)
+            g.pages_for(total_tokens, max_step_tokens) <= g.cfg.num_pages
+            and -(-total_tokens // g.cfg.page_size) <= g.width
             for g in self.page_groups
         )
 

@@ -100,40 +100,35 @@ class _Staging:
 
 
 class _DecodeGraph:
-    """A captured step for exactly B single-token segments."""
+    """A captured step for exactly B single-token segments whose block tables are ``width`` wide."""
 
-    def __init__(self, runner: "ModelRunner", B: int):
+    def __init__(self, runner: "ModelRunner", B: int, width: int):
         self.B = B
         self.ws = Workspace(runner.device)
-        self.nsplit = [runner.decode_splits(g.need, B) for g in runner.cache.page_groups]
+        self.nsplit = [runner.batch.decode_splits(g.need, B) for g in runner.cache.page_groups]
         caps = []
         for g, ns in zip(runner.cache.page_groups, self.nsplit):
             groups = g.need.q_heads // g.need.kv_heads
             chunks = 1 if groups <= ROW_TILE else -(-groups // ROW_TILE)
-            caps.append((B * ns * chunks, g.width))
+            caps.append((B * ns * chunks, min(width, g.width)))
         self.layout = _Layout(B, B, B, caps)
         self.meta = torch.zeros(self.layout.total, dtype=torch.int32, device=runner.device)
         self.graph = None
         self.logits = None
 
 
-class ModelRunner:
-    def __init__(self, model, cache: CacheManager, use_graphs: bool = True, sm_count: int | None = None):
-        self.model, self.cache = model, cache
-        self.rt = model.rt
-        self.device = self.rt.device
+class BatchBuilder:
+    """Turns a step's entries into the device arrays the kernels read.  It knows the cache
+    manager, not the model: tests use it to run a single part."""
+
+    def __init__(self, cache: CacheManager, device, sm_count: int | None = None):
+        self.cache = cache
+        self.device = torch.device(device)
         if sm_count is None:
             sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.sm_count = sm_count
-        self.ws = Workspace(self.device)
         self.meta = None
         self.staging = _Staging()
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.use_graphs = use_graphs and model.graph_safe
-        self.graphs: dict[int, _DecodeGraph] = {}
-        self.observer = None
-        self.stats = {"steps": 0, "tokens": 0, "graph_steps": 0, "kernel_launches": 0}
-        build.build_all(self.rt.kernel_modules())
 
     # ---- planning ----------------------------------------------------------------------------
     def decode_splits(self, need: PagedKVNeed, B: int) -> int:
@@ -145,7 +140,7 @@ class ModelRunner:
         ctas = B * need.kv_heads * chunks
         return max(1, min(MAX_SPLITS, -(-2 * self.sm_count // ctas)))
 
-    def _segments(self, entries: list[StepEntry]) -> tuple[list[Segment], int]:
+    def segments(self, entries: list[StepEntry]) -> tuple[list[Segment], int]:
         segments, offset = [], 0
         seen = set()
         for e in entries:
@@ -231,22 +226,64 @@ class ModelRunner:
             "groups": group_meta,
         }
 
+    def eager(self, entries, segments):
+        """Pack and send the arrays of an eagerly launched step; returns the device views."""
+        T = sum(s.count for s in segments)
+        S = len(segments)
+        R = sum(len(e.want) for e in entries)
+        caps = []
+        for g in self.cache.page_groups:
+            items, _ = plan_capacity(g.need, T, S)
+            width = max(1, max(-(-(s.start + s.count) // self.cache.cfg.page_size) for s in segments))
+            caps.append((items, min(width, g.width)))
+        layout = _Layout(T, S, R, caps)
+        stage, turn = self.staging.next(layout.total)
+        _, facts = self._fill(stage.numpy(), layout, entries, segments)
+        if self.meta is None or self.meta.numel() < layout.total:
+            self.meta = torch.empty(max(layout.total, 4096) * 2, dtype=torch.int32, device=self.device)
+        self.meta[: layout.total].copy_(stage[: layout.total], non_blocking=True)
+        self.staging.mark(turn)
+        return self._views(self.meta, layout, T, S, R, facts)
+
+    def context(self, rt, ws, status, views, segments) -> StepContext:
+        return StepContext(
+            rt=rt, ws=ws, T=sum(s.count for s in segments), segments=segments,
+            tokens=views["tokens"], positions=views["positions"], tok_seg=views["tok_seg"],
+            seg_slot=views["seg_slot"], status=status,
+        )
+
+    def cache_view(self, entry: int, group_meta, writable: bool = True) -> CacheView | None:
+        """The view of cache entry ``entry`` for one step."""
+        where = self.cache.entry_group[entry]
+        if where is None:
+            return None
+        kind, g, storage = self.cache.entry_storage(entry)
+        if kind == "pages":
+            return CacheView(g.need, g.gid, where[2], writable, storage,
+                             page_size=self.cache.cfg.page_size, meta=group_meta[g.gid])
+        return CacheView(g.need, g.gid, where[2], writable, storage)
+
+
+class ModelRunner:
+    def __init__(self, model, cache: CacheManager, use_graphs: bool = True, sm_count: int | None = None):
+        self.model, self.cache = model, cache
+        self.rt = model.rt
+        self.device = self.rt.device
+        self.batch = BatchBuilder(cache, self.device, sm_count)
+        self.sm_count = self.batch.sm_count
+        self.ws = Workspace(self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.use_graphs = use_graphs and model.graph_safe
+        self.graphs: dict[tuple[int, int], _DecodeGraph] = {}
+        self.observer = None
+        self.stats = {"steps": 0, "tokens": 0, "graph_steps": 0}
+        build.build_all(self.rt.kernel_modules())
+
     def _cache_views(self, group_meta) -> list[CacheView | None]:
-        views = []
-        for i, entry in enumerate(self.model.spec.order):
-            ce = self.model.entry_cache[i]
-            where = self.cache.entry_group[ce]
-            if where is None:
-                views.append(None)
-                continue
-            kind, g, storage = self.cache.entry_storage(ce)
-            writable = entry.cache_of is None
-            if kind == "pages":
-                views.append(CacheView(g.need, g.gid, where[2], writable, storage,
-                                       page_size=self.cache.cfg.page_size, meta=group_meta[g.gid]))
-            else:
-                views.append(CacheView(g.need, g.gid, where[2], writable, storage))
-        return views
+        return [
+            self.batch.cache_view(self.model.entry_cache[i], group_meta, writable=entry.cache_of is None)
+            for i, entry in enumerate(self.model.spec.order)
+        ]
 
     # ---- the step -----------------------------------------------------------------------------
     @torch.inference_mode()
@@ -261,7 +298,7 @@ class ModelRunner:
             for t in e.tokens:
                 if not 0 <= t < vocab:
                     raise StepError(f"request {e.request!r}: token {t} is outside the vocabulary of {vocab}")
-        segments, T = self._segments(entries)
+        segments, T = self.batch.segments(entries)
         maxpos = self.model.spec.max_positions
         for s in segments:
             if maxpos is not None and s.start + s.count > maxpos:
@@ -283,49 +320,36 @@ class ModelRunner:
         return logits
 
     def _step_eager(self, entries, segments, T):
-        S = len(segments)
-        R = sum(len(e.want) for e in entries)
-        caps = []
-        for g in self.cache.page_groups:
-            items, _ = plan_capacity(g.need, T, S)
-            width = max(1, max(-(-(s.start + s.count) // self.cache.cfg.page_size) for s in segments))
-            caps.append((items, min(width, g.width)))
-        layout = _Layout(T, S, R, caps)
-        stage, turn = self.staging.next(layout.total)
-        R_, facts = self._fill(stage.numpy(), layout, entries, segments)
-        if self.meta is None or self.meta.numel() < layout.total:
-            self.meta = torch.empty(max(layout.total, 4096) * 2, dtype=torch.int32, device=self.device)
-        self.meta[: layout.total].copy_(stage[: layout.total], non_blocking=True)
-        self.staging.mark(turn)
-        views = self._views(self.meta, layout, T, S, R, facts)
+        views = self.batch.eager(entries, segments)
         return self._forward(self.ws, views, segments, T)
 
     def _forward(self, ws, views, segments, T):
-        ctx = StepContext(
-            rt=self.rt, ws=ws, T=T, segments=segments, tokens=views["tokens"],
-            positions=views["positions"], tok_seg=views["tok_seg"], seg_slot=views["seg_slot"],
-            status=self.status,
-        )
+        ctx = self.batch.context(self.rt, ws, self.status, views, segments)
         caches = self._cache_views(views["groups"])
         return self.model.forward(ctx, caches, views["rows"], observer=self.observer)
 
     def _step_graph(self, entries, segments):
         B = len(segments)
-        g = self.graphs.get(B)
+        # block-table width in powers of two: a graph is re-captured only when contexts double
+        pages = max(-(-(s.start + 1) // self.cache.cfg.page_size) for s in segments)
+        width = 16
+        while width < pages:
+            width *= 2
+        g = self.graphs.get((B, width))
         if g is None:
-            g = self.graphs[B] = _DecodeGraph(self, B)
+            g = self.graphs[(B, width)] = _DecodeGraph(self, B, width)
         layout = g.layout
-        stage, turn = self.staging.next(layout.total)
-        _, facts = self._fill(stage.numpy(), layout, entries, segments, fixed_nsplit=g.nsplit)
+        stage, turn = self.batch.staging.next(layout.total)
+        _, facts = self.batch._fill(stage.numpy(), layout, entries, segments, fixed_nsplit=g.nsplit)
         g.meta.copy_(stage[: layout.total], non_blocking=True)
-        self.staging.mark(turn)
+        self.batch.staging.mark(turn)
         if g.graph is None:
             # fixed facts for the capture: every item slot is launched, splits are constant
             fixed = []
             for gi, pg in enumerate(self.cache.page_groups):
                 fixed.append({"num_items": layout.groups[gi][0], "part_rows": B * g.nsplit[gi],
                               "any_split": g.nsplit[gi] > 1})
-            views = self._views(g.meta, layout, B, B, B, fixed, launch_items=True)
+            views = self.batch._views(g.meta, layout, B, B, B, fixed, launch_items=True)
             # one eager run sizes the workspace and warms the kernels up, then the capture
             g.logits = self._forward(g.ws, views, segments, B)
             g.ws.frozen = True

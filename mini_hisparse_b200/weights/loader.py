@@ -85,10 +85,12 @@ def _tensor_seed(seed: int, name: str) -> int:
     return int.from_bytes(h[:8], "little") & ((1 << 63) - 1)
 
 
-def draw(name: str, ps, seed: int, device="cpu") -> torch.Tensor:
+def draw(name: str, ps, seed: int, device="cpu", matrix_std: float | None = None) -> torch.Tensor:
     """One tensor of the random-weights mode: its own generator, seeded by (seed, name), so the
     values do not depend on the order in which tensors are drawn.  float32 values."""
     kind, mean, std = ps.init
+    if matrix_std is not None and ps.role == "matrix":
+        std = matrix_std
     if kind != "normal":
         raise ValueError(f"unknown init {ps.init!r} for {name}")
     gen = torch.Generator(device=device)
@@ -110,11 +112,13 @@ def init_random(model, seed: int) -> None:
     _deliver(model, fetch)
 
 
-def write_random_model(config: dict, seed: int, folder, dtype: torch.dtype = torch.bfloat16) -> Path:
+def write_random_model(config: dict, seed: int, folder, dtype: torch.dtype = torch.bfloat16,
+                       matrix_std: float | None = None) -> Path:
     """Write a model folder (config.json, model.safetensors) for a configuration and a seed.
 
     Weights and biases are normal(0, 0.02), norm weights 1 + normal(0, 0.1); matrices are stored
-    in ``dtype``, vectors in float32.
+    in ``dtype``, vectors in float32.  ``matrix_std`` replaces the 0.02 of the matrices (tests use
+    a larger one, so that attention is not near-uniform and a wrong key shows).
     """
     from ..config.registry import resolve
     from ..parts.spec import ParamSpec  # noqa: F401  (documents what expected_tensors returns)
@@ -127,7 +131,7 @@ def write_random_model(config: dict, seed: int, folder, dtype: torch.dtype = tor
     for name, ps in expected_tensors_of_spec(spec).items():
         if ps.optional:
             continue
-        t = draw(name, ps, seed)
+        t = draw(name, ps, seed, matrix_std=matrix_std)
         tensors[name] = t.to(_target_dtype(ps.role, dtype))
     (folder / "config.json").write_text(json.dumps(config, indent=2) + "\n")
     write_safetensors(folder / "model.safetensors", tensors, metadata={"format": "pt", "seed": str(seed)})

@@ -1,0 +1,172 @@
+"""Generation through the Python entry point and the command line, against the plain
+implementation: greedy, temperature, long decoding, the first tokens of a sequence, and what
+happens when pages run out."""
+import json
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from conftest import ROOT, TINY, random_tokens
+from plain import qwen2_plain as P
+
+pytestmark = pytest.mark.gpu
+
+
+def load(folder, dtype):
+    from mini_hisparse_b200 import load_model
+
+    return load_model(folder, device="cuda:0", dtype=dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_equals_plain(folders, name, dtype):
+    from mini_hisparse_b200 import Engine
+
+    cfg, page = TINY[name]
+    pc, w = P.load_folder(folders[name])
+    model = load(folders[name], dtype)
+    engine = Engine(model, num_pages=64, page_size=page, max_requests=4, max_tokens_per_step=48)
+    prompts = {str(n): random_tokens(cfg["vocab_size"], n, seed=n) for n in (7, 33, 64)}
+    for rid, prompt in prompts.items():
+        engine.add_request(rid, prompt, max_new_tokens=16)
+    out = engine.run()
+    for rid, prompt in prompts.items():
+        want = P.generate(pc, w, prompt, 16)
+        if dtype == "float32":
+            assert out[rid] == want
+        else:
+            # bfloat16 may flip a near-tie; up to there the tokens are equal, and the flip is a near-tie
+            same = next((i for i, (a, b) in enumerate(zip(out[rid], want)) if a != b), 16)
+            if same < 16:
+                logits = P.forward_logits(pc, w, prompt + want[:same])[-1]
+                top = logits.topk(2).values
+                assert float(top[0] - top[1]) < 0.05 * float(logits.abs().max()), (rid, same)
+        r = engine.requests[rid]
+        assert r.prefill_count == 1 and r.decode_count == 15 and r.finished
+    assert engine.runner.stats["graph_steps"] > 0        # decoding went through captured graphs
+    engine.cache.assert_invariants()
+    assert not engine.cache.requests
+    assert engine.cache.page_groups[0].allocator.free_pages == 64
+
+
+def test_temperature_sampling_equals_plain_chain(folders):
+    """Tiny B, portions of 48 tokens mixed with decoding, 24 steps at temperature 0.8, fixed seeds."""
+    from mini_hisparse_b200 import Engine
+
+    cfg, page = TINY["B"]
+    pc, w = P.load_folder(folders["B"])
+    model = load(folders["B"], "float32")
+    engine = Engine(model, num_pages=32, page_size=page, max_requests=4, max_tokens_per_step=48)
+    prompts = {str(n): random_tokens(cfg["vocab_size"], n, seed=n) for n in (1, 31, 100, 257)}
+    for i, (rid, prompt) in enumerate(prompts.items()):
+        engine.add_request(rid, prompt, max_new_tokens=24, temperature=0.8, seed=1234 + i)
+    out = engine.run()
+    for i, (rid, prompt) in enumerate(prompts.items()):
+        history = list(prompt)
+        for step, token in enumerate(out[rid]):
+            logits = P.forward_logits(pc, w, history)[-1]
+            want, margin = P.sample_temperature(logits, 0.8, 1234 + i, step)
+            assert token == want or margin < 1e-4, (rid, step, token, want, margin)
+            history.append(token)
+        assert len(out[rid]) == 24
+    assert len({tuple(v) for v in out.values()}) == 4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(folders, dtype):
+    """A one-token prompt (positions 0, 1, 2, ... are all decoded) run far past several pages."""
+    from mini_hisparse_b200 import Engine
+
+    pc, w = P.load_folder(folders["A"])
+    model = load(folders["A"], dtype)
+    engine = Engine(model, num_pages=16, page_size=16, max_requests=2)
+    engine.add_request("long", [5], max_new_tokens=200)
+    out = engine.run()["long"]
+    assert len(out) == 200
+    logits = P.forward_logits(pc, w, [5] + out)
+    picks = logits.argmax(-1)[:-1].tolist()
+    if dtype == "float32":
+        assert picks == out
+    else:
+        agree = sum(a == b for a, b in zip(picks, out)) / len(out)
+        assert agree > 0.9
+
+
+def test_few_pages_requests_wait_and_pages_are_used_again(folders):
+    from mini_hisparse_b200 import CapacityError, Engine
+
+    cfg, page = TINY["A"]
+    pc, w = P.load_folder(folders["A"])
+    model = load(folders["A"], "float32")
+    # 6 pages of 16: one request of 40 + 8 tokens (3 pages) fits twice, never three times
+    engine = Engine(model, num_pages=6, page_size=page, max_requests=4, max_tokens_per_step=64)
+    prompts = {str(i): random_tokens(cfg["vocab_size"], 40, seed=i) for i in range(5)}
+    for rid, p in prompts.items():
+        engine.add_request(rid, p, max_new_tokens=8)
+    with pytest.raises(CapacityError):
+        engine.add_request("huge", [1] * 100, max_new_tokens=8)
+    engine.step()
+    assert len(engine.waiting) == 3 and len(engine.running) == 2
+    out = engine.run()
+    for rid, p in prompts.items():
+        assert out[rid] == P.generate(pc, w, p, 8)
+        assert engine.requests[rid].prefill_count == 1
+    snap = engine.snapshot()
+    assert snap["cache"]["page_groups"][0]["pages_reused"] > 0
+    assert snap["scheduler"]["admissions_deferred"] > 0
+    engine.cache.assert_invariants()
+
+
+def test_cancel_and_eos(folders):
+    from mini_hisparse_b200 import Engine
+
+    cfg, page = TINY["A"]
+    pc, w = P.load_folder(folders["A"])
+    model = load(folders["A"], "float32")
+    prompt = random_tokens(cfg["vocab_size"], 20, seed=3)
+    want = P.generate(pc, w, prompt, 10)
+    engine = Engine(model, num_pages=16, page_size=page, eos_token_id=want[4])
+    engine.add_request("a", prompt, max_new_tokens=10)
+    engine.add_request("b", prompt, max_new_tokens=10)
+    engine.step()
+    engine.cancel("b")
+    out = engine.run()
+    stop = want.index(want[4])
+    assert out["a"] == want[: stop + 1]                   # the EOS token is kept
+    assert engine.requests["b"].cancelled and not engine.cache.requests
+
+
+def test_bad_weights_fail_with_one_clear_error(folders, tmp_path):
+    from mini_hisparse_b200 import WeightError
+    from mini_hisparse_b200.weights import write_safetensors
+
+    w = P.read_safetensors(folders["B"] / "model.safetensors")
+    del w["model.layers.2.mlp.up_proj.weight"]
+    w["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(7)
+    w["model.layers.7.ghost"] = torch.zeros(2)
+    bad = tmp_path / "bad"
+    bad.mkdir()
+    (bad / "config.json").write_text((folders["B"] / "config.json").read_text())
+    write_safetensors(bad / "model.safetensors", w)
+    with pytest.raises(WeightError) as e:
+        load(bad, "float32")
+    msg = str(e.value)
+    assert "up_proj" in msg and "ghost" in msg and "q_proj.bias" in msg and "[7]" in msg
+
+
+def test_command_line_generate(folders, tmp_path):
+    out_file = tmp_path / "report.json"
+    prompt = random_tokens(512, 9, seed=2)
+    cmd = [sys.executable, "-m", "mini_hisparse_b200", "generate", "--model", str(folders["A"]),
+           "--dtype", "float32", "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "6",
+           "--gpu-pages", "8", "--output", str(out_file)]
+    res = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    report = json.loads(out_file.read_text())
+    pc, w = P.load_folder(folders["A"])
+    assert report["outputs"]["0"] == P.generate(pc, w, prompt, 6)
+    assert report["requests"]["0"] == {"prefill_count": 1, "decode_count": 5, "generated_tokens": 6}
+    assert json.loads(res.stdout)["outputs"] == report["outputs"]

@@ -1,0 +1,352 @@
+"""Each CUDA kernel alone against a plain PyTorch float32 reference of the same operation, at
+sizes other than the engine's test models (widths and vocabularies that are no power of two,
+head sizes in steps of 16, odd group counts)."""
+import math
+
+import pytest
+import torch
+
+from plain import qwen2_plain as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def K():
+    from mini_hisparse_b200.kernels import api
+
+    return api
+
+
+def tol(dtype, scale=1.0):
+    if dtype == torch.float32:
+        return dict(atol=2e-5 * scale, rtol=2e-5)
+    return dict(atol=1.6e-2 * scale, rtol=1.6e-2)
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+# ---- embedding -----------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(dtype):
+    V, H = 777, 200
+    table = rnd(V, H, dtype=dtype)
+    tokens = torch.tensor([0, 776, 5, 5, 300], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, H, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K().embed(table, tokens, out, status)
+    assert torch.equal(out, table.float()[tokens.long()]) and int(status) == 0
+    bad = torch.tensor([3, 777, -1], dtype=torch.int32, device=DEV)
+    out3 = torch.ones(3, H, device=DEV)
+    K().embed(table, bad, out3, status)
+    assert int(status) == 1 and torch.equal(out3[1:], torch.zeros(2, H, device=DEV))
+    assert torch.equal(out3[0], table.float()[3])
+
+
+# ---- RMSNorm ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [80, 1000, 3584])
+def test_rmsnorm_plain_add_rows_and_splits(dtype, H):
+    R, eps = 7, 3e-6
+    x = rnd(R, H, seed=1, scale=2.0)
+    w = rnd(H, seed=2) * 0.1 + 1
+    ref = P.rms_norm(x, w, eps)
+    out = torch.empty(R, H, dtype=dtype, device=DEV)
+    K().add_rmsnorm(x.clone(), w, eps, out)
+    torch.testing.assert_close(out.float(), ref, **tol(dtype, 4))
+    # with a delta: the residual is updated in place
+    delta = rnd(R, H, dtype=dtype, seed=3)
+    xr = x.clone()
+    K().add_rmsnorm(xr, w, eps, out, delta=delta)
+    torch.testing.assert_close(xr, x + delta.float(), atol=1e-6, rtol=1e-6)
+    torch.testing.assert_close(out.float(), P.rms_norm(x + delta.float(), w, eps), **tol(dtype, 4))
+    # split partials, summed in order
+    parts = rnd(3, R, H, seed=4)
+    xr = x.clone()
+    K().add_rmsnorm(xr, w, eps, out, delta=parts, nsplit=3, split_stride=parts.stride(0))
+    want = x + parts[0] + parts[1] + parts[2]
+    torch.testing.assert_close(xr, want, atol=1e-6, rtol=1e-6)
+    # selected rows: nothing is written back
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    xr = x.clone()
+    out3 = torch.empty(3, H, dtype=dtype, device=DEV)
+    K().add_rmsnorm(xr, w, eps, out3, delta=delta, rows=rows)
+    assert torch.equal(xr, x)
+    torch.testing.assert_close(out3.float(), P.rms_norm((x + delta.float())[rows.long()], w, eps), **tol(dtype, 4))
+
+
+def test_residual_add():
+    x = rnd(5, 33, seed=1)
+    parts = rnd(2, 5, 33, seed=2)
+    xr = x.clone()
+    K().residual_add(xr, parts, nsplit=2, split_stride=parts.stride(0))
+    torch.testing.assert_close(xr, x + parts[0] + parts[1], atol=1e-6, rtol=1e-6)
+
+
+# ---- matrix product --------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K_", [(1, 50, 24), (7, 1000, 96), (130, 67, 333), (65, 64, 16), (3, 129, 1)])
+def test_gemm_simt(dtype, M, N, K_):
+    a = rnd(M, K_, dtype=dtype, seed=1)
+    w = rnd(N, K_, dtype=dtype, seed=2)
+    bias = rnd(N, seed=3)
+    ref = a.float() @ w.float().T
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    K().gemm_simt(a, w, out)
+    torch.testing.assert_close(out, ref, atol=2e-5 * math.sqrt(K_), rtol=2e-5)
+    K().gemm_simt(a, w, out, bias=bias)
+    torch.testing.assert_close(out, ref + bias, atol=2e-5 * math.sqrt(K_), rtol=2e-5)
+    out_d = torch.empty(M, N, dtype=dtype, device=DEV)
+    K().gemm_simt(a, w, out_d)
+    torch.testing.assert_close(out_d.float(), ref, **tol(dtype, math.sqrt(K_)))
+    parts = torch.full((3, M, N), float("nan"), device=DEV)
+    K().gemm_simt(a, w, parts, nsplit=3, split_stride=parts.stride(0))
+    torch.testing.assert_close(parts.sum(0), ref, atol=2e-5 * math.sqrt(K_), rtol=2e-5)
+
+
+def test_gemm_is_true_float32():
+    """A product that TF32 or bfloat16 inputs would get wrong by 1e-3 comes out to 1e-6."""
+    a = torch.full((4, 64), 1.0 + 2 ** -12, device=DEV)
+    w = torch.full((8, 64), 1.0 + 2 ** -12, device=DEV)
+    out = torch.empty(4, 8, device=DEV)
+    K().gemm_simt(a, w, out)
+    exact = 64 * (1.0 + 2 ** -12) ** 2
+    assert abs(float(out[0, 0]) - exact) < 1e-4
+
+
+# ---- rotary + append -----------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,P_", [(4, 2, 16, 16), (3, 1, 32, 32), (10, 2, 48, 16), (7, 7, 128, 8)])
+def test_rope_append(dtype, nq, nkv, d, P_):
+    theta = 50000.0
+    T, pages = 21, 9
+    width = (nq + 2 * nkv) * d
+    qkv = rnd(T, width, seed=1)
+    bias = rnd(width, seed=2) * 0.1
+    # two segments: one starts at position 37 (inside a page), one at 0
+    positions = torch.tensor(list(range(37, 37 + 13)) + list(range(0, 8)), dtype=torch.int32, device=DEV)
+    tok_seg = torch.tensor([0] * 13 + [1] * 8, dtype=torch.int32, device=DEV)
+    w_pages = -(-(37 + 13) // P_)
+    table = torch.full((2, max(w_pages, 2)), -1, dtype=torch.int32)
+    perm = torch.randperm(64, generator=torch.Generator().manual_seed(5)).tolist()
+    table[0, :w_pages] = torch.tensor(perm[:w_pages])
+    table[1, : -(-8 // P_)] = torch.tensor(perm[w_pages : w_pages + -(-8 // P_)])
+    table = table.to(DEV)
+    cache = torch.zeros(64, 2, nkv, P_, d, dtype=dtype, device=DEV)
+    q_out = torch.empty(T, nq * d, dtype=dtype, device=DEV)
+    inv = (theta ** (-torch.arange(0, d, 2).float() / d)).to(DEV)
+    K().rope_append(qkv, bias, positions, tok_seg, table, inv, q_out, cache, nq=nq, nkv=nkv, d=d, page_size=P_)
+    full = qkv + bias
+    q = full[:, : nq * d].view(T, nq, d)
+    k = full[:, nq * d : (nq + nkv) * d].view(T, nkv, d)
+    v = full[:, (nq + nkv) * d :].view(T, nkv, d)
+    cos, sin = P.rope_tables(positions, d, theta, torch.float32)
+    torch.testing.assert_close(q_out.float().view(T, nq, d), P.rotate(q, cos, sin), **tol(dtype, 4))
+    kr = P.rotate(k, cos, sin)
+    for t in range(T):
+        pos, seg = int(positions[t]), int(tok_seg[t])
+        page = int(table[seg, pos // P_])
+        torch.testing.assert_close(cache[page, 0, :, pos % P_].float(), kr[t], **tol(dtype, 4))
+        torch.testing.assert_close(cache[page, 1, :, pos % P_].float(), v[t], **tol(dtype, 4))
+    # nothing else was touched
+    touched = torch.zeros(64, P_, dtype=torch.bool)
+    for t in range(T):
+        pos, seg = int(positions[t]), int(tok_seg[t])
+        touched[int(table[seg, pos // P_]), pos % P_] = True
+    untouched = cache.float().abs().sum((1, 2, 4)).cpu()[~touched]
+    assert float(untouched.sum()) == 0.0
+
+
+def test_rope_append_refuses_a_page_outside_the_pool():
+    nq, nkv, d, P_ = 2, 1, 16, 16
+    qkv = rnd(1, 4 * d)
+    pos = torch.tensor([3], dtype=torch.int32, device=DEV)
+    seg = torch.zeros(1, dtype=torch.int32, device=DEV)
+    table = torch.tensor([[99]], dtype=torch.int32, device=DEV)
+    cache = torch.zeros(4, 2, nkv, P_, d, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    inv = torch.ones(d // 2, device=DEV)
+    q_out = torch.empty(1, nq * d, device=DEV)
+    K().rope_append(qkv, None, pos, seg, table, inv, q_out, cache, nq=nq, nkv=nkv, d=d, page_size=P_, status=status)
+    assert int(status) == 2 and float(cache.abs().sum()) == 0.0
+
+
+# ---- SwiGLU -------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    T, I = 5, 176
+    gu = rnd(T, 2 * I, dtype=dtype, seed=1, scale=3)
+    out = torch.empty(T, I, dtype=dtype, device=DEV)
+    K().swiglu(gu, out)
+    g, u = gu.float()[:, :I], gu.float()[:, I:]
+    torch.testing.assert_close(out.float(), g * torch.sigmoid(g) * u, **tol(dtype, 8))
+    parts = rnd(2, T, 2 * I, seed=2)
+    K().swiglu(parts, out, nsplit=2, split_stride=parts.stride(0))
+    s = parts.sum(0)
+    torch.testing.assert_close(out.float(), s[:, :I] * torch.sigmoid(s[:, :I]) * s[:, I:], **tol(dtype, 8))
+
+
+# ---- attention -------------------------------------------------------------------------------------
+def paged_case(nq, nkv, d, P_, seg_specs, dtype, seed=0, pool=96):
+    """Segments (history, new tokens): K/V of the history AND the new tokens are in shuffled pages
+    (the engine appends before it attends)."""
+    from mini_hisparse_b200.parts.base import Segment
+
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(pool, generator=g).tolist()
+    cache = torch.zeros(pool, 2, nkv, P_, d, dtype=dtype, device=DEV)
+    cache.normal_(generator=torch.Generator(device=DEV).manual_seed(seed))   # stale junk everywhere
+    segments, ks, vs, qs, positions = [], [], [], [], []
+    width = max(-(-(h + n) // P_) for h, n in seg_specs)
+    table = torch.full((len(seg_specs), width), -1, dtype=torch.int32)
+    off = 0
+    for si, (hist, n) in enumerate(seg_specs):
+        total = hist + n
+        k = torch.randn(total, nkv, d, generator=g).to(dtype)
+        v = torch.randn(total, nkv, d, generator=g).to(dtype)
+        q = torch.randn(total, nq, d, generator=g).to(dtype)
+        npg = -(-total // P_)
+        pages = [perm.pop() for _ in range(npg)]
+        table[si, :npg] = torch.tensor(pages)
+        for t in range(total):
+            cache[pages[t // P_], 0, :, t % P_] = k[t].to(DEV)
+            cache[pages[t // P_], 1, :, t % P_] = v[t].to(DEV)
+        segments.append(Segment(si, si, hist, n, off))
+        ks.append(k), vs.append(v), qs.append(q)
+        positions += list(range(hist, total))
+        off += n
+    return cache, table.to(DEV), segments, qs, ks, vs, torch.tensor(positions, dtype=torch.int32, device=DEV)
+
+
+def run_attention(nq, nkv, d, P_, seg_specs, dtype, window=None, fixed_nsplit=None, seed=0, edit=None):
+    from mini_hisparse_b200.parts.attention import plan_attention
+    from mini_hisparse_b200.parts.spec import PagedKVNeed
+
+    cache, table, segments, qs, ks, vs, positions = paged_case(nq, nkv, d, P_, seg_specs, dtype, seed)
+    if edit:
+        edit(qs, ks, vs, cache, table)
+    T = sum(n for _, n in seg_specs)
+    need = PagedKVNeed(nkv, d, nq, window)
+    plan = plan_attention(need, segments, T, 148, fixed_nsplit=fixed_nsplit)
+    q = torch.cat([qq[h:] for qq, (h, n) in zip(qs, seg_specs)]).reshape(T, nq * d).to(DEV)
+    out = torch.full((T, nq * d), float("nan"), dtype=dtype, device=DEV)
+    rows = max(1, plan.part_rows)
+    part_acc = torch.full((rows, nq, d), float("nan"), device=DEV)
+    part_ml = torch.full((rows, nq, 2), float("nan"), device=DEV)
+    items = torch.from_numpy(plan.items).to(DEV).reshape(-1)
+    tpr = torch.from_numpy(plan.tok_part_row).to(DEV)
+    tns = torch.from_numpy(plan.tok_nsplit).to(DEV)
+    n_items = plan.items.shape[0]
+    K().attention_simt(q, cache, out, part_acc, part_ml, items, n_items, n_items, positions, table, tpr,
+                       nq=nq, nkv=nkv, d=d, page_size=P_, window=window or 0)
+    if plan.part_rows:
+        K().attention_combine(part_acc, part_ml, tpr, tns, out, nq=nq, d=d)
+    ref = torch.cat([
+        P.causal_attention(qq.float(), kk.float(), vv.float(), window=window)[h:]
+        for qq, kk, vv, (h, n) in zip(qs, ks, vs, seg_specs)
+    ]).reshape(T, nq * d)
+    return out.float().cpu(), ref, plan
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,P_", [(4, 2, 16, 16), (3, 1, 32, 32), (10, 2, 48, 16), (28, 4, 128, 16),
+                                          (20, 1, 80, 8), (2, 2, 256, 16), (6, 3, 112, 7)])
+def test_attention_prefill_portions_and_decode_mixed(dtype, nq, nkv, d, P_):
+    # a whole prompt, a portion at an offset inside a page, a single token, a 2-token portion
+    specs = [(0, 37), (45, 19), (130, 1), (63, 2)]
+    out, ref, plan = run_attention(nq, nkv, d, P_, specs, dtype)
+    torch.testing.assert_close(out, ref, **tol(dtype, 2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_split_keys_and_combine(dtype):
+    specs = [(700, 1), (33, 1), (1023, 1), (0, 1)]
+    out, ref, plan = run_attention(28, 4, 128, 16, specs, dtype, fixed_nsplit=5)
+    assert plan.part_rows == 20 and (plan.items[:, 7] >= 0).all()
+    torch.testing.assert_close(out, ref, **tol(dtype, 2))
+    out, ref, plan = run_attention(8, 2, 64, 16, [(2000, 1)], dtype)      # the planner splits by itself
+    assert plan.part_rows > 1
+    torch.testing.assert_close(out, ref, **tol(dtype, 2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key_among_hundreds(dtype):
+    """Random keys give near-uniform weights, which would hide a missed page.  Here the query of
+    the last token matches key 3 (first page) with a large score: the output must be V[3]."""
+    def edit(qs, ks, vs, cache, table):
+        d = qs[0].shape[-1]
+        direction = torch.zeros(d)
+        direction[5] = 1.0
+        for h in range(qs[0].shape[1]):
+            qs[0][-1, h] = direction * 60.0
+        ks[0][3, :] = (direction * 8.0).to(ks[0].dtype)
+        page = int(table[0, 0])
+        cache[page, 0, :, 3] = ks[0][3].to(cache.device)
+    out, ref, _ = run_attention(4, 2, 64, 16, [(640, 1)], dtype, edit=edit)
+    torch.testing.assert_close(out, ref, **tol(dtype, 2))
+    # and the reference itself is V[3] there, up to the tail of the softmax
+    out2, ref2, _ = run_attention(4, 2, 64, 16, [(0, 641)], dtype, edit=edit)
+    torch.testing.assert_close(out2[-1], ref2[-1], **tol(dtype, 2))
+    torch.testing.assert_close(out[-1], out2[-1], **tol(dtype, 2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 5, 16, 40])
+def test_attention_window_edge(dtype, window):
+    """Keys exactly at the window's edge: position - window + 1 is the first key kept."""
+    specs = [(0, 50), (77, 3), (100, 1)]
+    out, ref, _ = run_attention(4, 2, 32, 16, specs, dtype, window=window)
+    torch.testing.assert_close(out, ref, **tol(dtype, 2))
+
+
+def test_attention_refuses_what_it_cannot_do():
+    from mini_hisparse_b200.kernels.api import KernelError
+    from mini_hisparse_b200.parts.attention import GQAttention
+    from mini_hisparse_b200.parts.spec import PartSpec
+
+    pos = PartSpec.make("rotary", head_dim=40, theta=1e4)
+    with pytest.raises(ValueError, match="head_dim 40"):
+        GQAttention(PartSpec.make("gq_attention", hidden_size=80, q_heads=2, kv_heads=2, head_dim=40, position=pos))
+    with pytest.raises(KernelError, match="CPU"):
+        K().embed(torch.zeros(4, 4), torch.zeros(1, dtype=torch.int32), torch.zeros(1, 4))
+
+
+# ---- sampling -------------------------------------------------------------------------------------
+def test_sample_greedy_lowest_index_wins():
+    V = 152064 // 8 + 3
+    logits = rnd(5, V, seed=3)
+    logits[1, 100] = logits[1, 17000] = 50.0
+    logits[2, V - 1] = 60.0
+    logits[3, 0] = 60.0
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    K().sample(logits, None, None, None, out)
+    assert out.tolist() == logits.argmax(-1).tolist()
+    assert out[1] == 100 and out[2] == V - 1 and out[3] == 0
+
+
+def test_sample_temperature_equals_the_plain_draw():
+    V, R = 1000, 64
+    logits = rnd(R, V, seed=4, scale=2.0)
+    temps = torch.tensor([0.8] * (R - 2) + [0.0, 1.5], device=DEV)
+    seeds = torch.arange(R, dtype=torch.int64, device=DEV) + 11
+    counters = torch.arange(R, dtype=torch.int64, device=DEV) * 3
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    K().sample(logits, temps, seeds, counters, out)
+    cpu = logits.cpu()
+    for r in range(R):
+        if float(temps[r]) == 0:
+            assert int(out[r]) == int(cpu[r].argmax())
+            continue
+        token, margin = P.sample_temperature(cpu[r], float(temps[r]), int(seeds[r]), int(counters[r]))
+        assert int(out[r]) == token or margin < 1e-5, (r, int(out[r]), token, margin)
+    # the same request draws the same token whatever else is in the batch
+    again = torch.empty(3, dtype=torch.int32, device=DEV)
+    sel = [5, 40, 9]
+    K().sample(logits[sel].contiguous(), temps[sel].contiguous(), seeds[sel].contiguous(),
+               counters[sel].contiguous(), again)
+    assert again.tolist() == [int(out[i]) for i in sel]

@@ -1,0 +1,171 @@
+"""Generality of the parts: a toy model defined HERE, with a mixer that keeps a state of its own,
+a layer that runs twice, a layer that reads another layer's cache and a layer without position
+encoding, is registered, built from a model folder and stepped in portions, without a change to
+the framework's files.  It is compared with a whole-sequence computation written here."""
+import json
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+from conftest import random_tokens
+from plain import qwen2_plain as P
+
+pytestmark = pytest.mark.gpu
+
+TOY = dict(architectures=["ToyForCausalLM"], vocab_size=130, hidden_size=48, intermediate_size=72,
+           q_heads=3, kv_heads=1, head_dim=16, eps=1e-5, theta=777.0)
+
+
+def register_toy():
+    from mini_hisparse_b200 import register_architecture
+    from mini_hisparse_b200.parts import (LayerSpec, Mixer, ModelSpec, ParamSpec, PartSpec, Product,
+                                          RunEntry, StateNeed, register_mixer)
+
+    @register_mixer("toy_running_mean", replace=True)
+    class RunningMean(Mixer):
+        """out[t] = W . mean(h[0..t]); the state is the running sum, carried across steps."""
+
+        graph_safe = False
+
+        def __init__(self, spec, rt=None):
+            super().__init__(spec, rt)
+            self.width = spec["hidden_size"]
+
+        def cache_need(self):
+            return StateNeed(shape=(self.width,), dtype="float32")
+
+        def parameters(self):
+            return {"mix.weight": ParamSpec((self.width, self.width))}
+
+        def load(self, tensors):
+            self.w = tensors["mix.weight"]
+
+        def forward(self, h, ctx, cache):
+            out = ctx.ws.get("toy_out", (h.shape[0], self.width), ctx.rt.dtype)
+            for seg in ctx.segments:
+                rows = slice(seg.offset, seg.offset + seg.count)
+                csum = h[rows].float().cumsum(0) + cache.storage[seg.slot]
+                counts = torch.arange(seg.start + 1, seg.start + seg.count + 1, device=h.device)
+                if cache.writable:
+                    cache.storage[seg.slot] = csum[-1]
+                out[rows] = ((csum / counts[:, None]) @ self.w.float().T).to(out.dtype)
+            return Product(out)
+
+    @dataclass(frozen=True)
+    class ToyConfig:
+        raw: tuple
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(tuple(sorted((k, v) for k, v in d.items() if k != "architectures")))
+
+        def __getitem__(self, k):
+            return dict(self.raw)[k]
+
+    def toy_spec(c):
+        H = c["hidden_size"]
+        norm = PartSpec.make("rmsnorm", width=H, eps=c["eps"])
+        ff = PartSpec.make("swiglu", hidden_size=H, intermediate_size=c["intermediate_size"])
+
+        def attn(position):
+            return PartSpec.make("gq_attention", hidden_size=H, q_heads=c["q_heads"], kv_heads=c["kv_heads"],
+                                 head_dim=c["head_dim"], qkv_bias=False, window=None, position=position)
+
+        rotary = PartSpec.make("rotary", head_dim=c["head_dim"], theta=c["theta"])
+        mixers = [attn(rotary), PartSpec.make("toy_running_mean", hidden_size=H), attn(PartSpec.make("none"))]
+        layers = tuple(LayerSpec(f"toy.layers.{i}", "pre_norm", m, norm, ff, norm) for i, m in enumerate(mixers))
+        order = (RunEntry(0), RunEntry(1), RunEntry(2), RunEntry(1), RunEntry(2, cache_of=2))
+        return ModelSpec("ToyForCausalLM", c["vocab_size"], H,
+                         PartSpec.make("token_embedding", vocab_size=c["vocab_size"], hidden_size=H), "toy.embed",
+                         layers, order, norm, "toy.norm",
+                         PartSpec.make("lm_head", vocab_size=c["vocab_size"], hidden_size=H, tied=True), "toy.head")
+
+    register_architecture("ToyForCausalLM", ToyConfig, toy_spec, replace=True)
+
+
+def toy_reference(w, tokens):
+    """The whole sequence at once, from the formulas above."""
+    c = TOY
+    T = len(tokens)
+    x = w["toy.embed.weight"][torch.tensor(tokens)]
+    pos = torch.arange(T)
+    shared_kv = {}
+
+    def attention(i, h, rotate, entry, reuse=None):
+        p = f"toy.layers.{i}.self_attn."
+        q = (h @ w[p + "q_proj.weight"].T).view(T, c["q_heads"], c["head_dim"])
+        k = (h @ w[p + "k_proj.weight"].T).view(T, c["kv_heads"], c["head_dim"])
+        v = (h @ w[p + "v_proj.weight"].T).view(T, c["kv_heads"], c["head_dim"])
+        if rotate:
+            cos, sin = P.rope_tables(pos, c["head_dim"], c["theta"], torch.float32)
+            q, k = P.rotate(q, cos, sin), P.rotate(k, cos, sin)
+        if reuse is not None:
+            k, v = shared_kv[reuse]
+        shared_kv[entry] = (k, v)
+        return P.causal_attention(q, k, v).reshape(T, -1) @ w[p + "o_proj.weight"].T
+
+    def running_mean(i, h):
+        mean = h.cumsum(0) / torch.arange(1, T + 1)[:, None]
+        return mean @ w[f"toy.layers.{i}.self_attn.mix.weight"].T
+
+    def block(i, x, mix):
+        p = f"toy.layers.{i}."
+        x = x + mix(P.rms_norm(x, w[p + "input_layernorm.weight"], c["eps"]))
+        h = P.rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"])
+        return x + P.swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+
+    x = block(0, x, lambda h: attention(0, h, True, 0))
+    x = block(1, x, lambda h: running_mean(1, h))
+    x = block(2, x, lambda h: attention(2, h, False, 2))
+    x = block(1, x, lambda h: running_mean(1, h))
+    x = block(2, x, lambda h: attention(2, h, False, 4, reuse=2))
+    return P.rms_norm(x, w["toy.norm.weight"], c["eps"]) @ w["toy.embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_model_registers_builds_and_steps(tmp_path, dtype):
+    from mini_hisparse_b200 import CacheConfig, CacheManager, load_model, write_random_model
+    from mini_hisparse_b200.engine import ModelRunner, StepEntry
+
+    register_toy()
+    write_random_model(TOY, 5, tmp_path, dtype=torch.bfloat16, matrix_std=0.15)
+    w = {k: v.float() for k, v in P.read_safetensors(tmp_path / "model.safetensors").items()}
+    model = load_model(tmp_path, dtype=dtype)
+    assert len(model.cache_needs) == 4            # five run entries, one of them reads another's cache
+    cache = CacheManager(model.cache_needs, CacheConfig(num_pages=12, page_size=16, max_requests=3,
+                                                        dtype=model.rt.dtype))
+    assert len(cache.page_groups) == 1 and len(cache.state_groups) == 1
+    assert len(cache.page_groups[0].entries) == 2 and len(cache.state_groups[0].entries) == 2
+    runner = ModelRunner(model, cache)
+    assert not runner.use_graphs                  # the toy mixer works on the host: no captured graph
+    reqs = {"a": random_tokens(130, 70, 1), "b": random_tokens(130, 41, 2)}
+    refs = {k: toy_reference(w, t) for k, t in reqs.items()}
+    got = {k: [] for k in reqs}
+    done = {k: 0 for k in reqs}
+    cuts = {"a": [30, 2, 1, 17, 1, 19], "b": [5, 1, 1, 30, 2, 2]}
+    for k in reqs:
+        cache.open(k)
+    for step in range(6):
+        entries = []
+        for k in reqs:
+            n = cuts[k][step]
+            entries.append(StepEntry(k, reqs[k][done[k]: done[k] + n], list(range(n))))
+        logits = runner.step(entries).cpu()
+        runner.check_status()
+        row = 0
+        for e in entries:
+            n = len(e.tokens)
+            got[e.request].append(logits[row: row + n].clone())
+            row += n
+            done[e.request] += n
+    for k in reqs:
+        out = torch.cat(got[k])
+        tol = dict(atol=3e-5, rtol=3e-5) if dtype == "float32" else dict(atol=0.03 * float(refs[k].abs().max()), rtol=0.03)
+        torch.testing.assert_close(out, refs[k], **tol)
+    # a slot that is used again starts from a zero state
+    cache.close("a")
+    cache.open("c")
+    logits = runner.step([StepEntry("c", reqs["b"][:9], list(range(9)))]).cpu()
+    torch.testing.assert_close(logits, refs["b"][:9], **tol)
+    cache.assert_invariants()
