@@ -192,11 +192,12 @@ def test_swiglu(dtype):
 
 
 # ---- attention -------------------------------------------------------------------------------------
-def paged_case(nq, nkv, d, P_, seg_specs, dtype, seed=0, pool=96):
+def paged_case(nq, nkv, d, P_, seg_specs, dtype, seed=0):
     """Segments (history, new tokens): K/V of the history AND the new tokens are in shuffled pages
     (the engine appends before it attends)."""
     from mini_hisparse_b200.parts.base import Segment
 
+    pool = sum(-(-(h + n) // P_) for h, n in seg_specs) + 13
     g = torch.Generator().manual_seed(seed)
     perm = torch.randperm(pool, generator=g).tolist()
     cache = torch.zeros(pool, 2, nkv, P_, d, dtype=dtype, device=DEV)
