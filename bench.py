@@ -1,0 +1,189 @@
+#!/usr/bin/env python3
+"""Decode throughput of the engine at Qwen2.5-7B shape with random weights, on one GPU.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens a second at batch 8 with about 4,096 tokens of
+context per request, timed on the device around K decode steps of the step function;
+``e2e`` is the same through ``Engine.step()`` with host token ids in and sampled host tokens
+out (its prompts are really prefilled); ``prefill`` times a 2,048-token prompt; ``roofline``
+relates the decode step to the bytes it has to read; ``points`` holds batch 1 and 64.
+For --gpus > 1 it prints one line that says so and exits with 2: this engine is single-GPU.
+"""
+from __future__ import annotations
+
+import argparse
+import gc
+import json
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# BASELINE.json configs[2]: Qwen2.5-7B shape
+CONFIG_7B = dict(
+    architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=152064, hidden_size=3584,
+    intermediate_size=18944, num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4,
+    rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False,
+    max_position_embeddings=32768, hidden_act="silu", use_sliding_window=False,
+)
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+PAGE = 16
+
+
+def reference_arm(args) -> int:
+    from baseline.reference_arm import run_reference
+
+    print(json.dumps(run_reference(CONFIG_7B, CONTEXT, args)))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the 28 of the config")
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.impl == "reference":
+        return reference_arm(args)
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+
+    from mini_hisparse_b200 import measure
+    from mini_hisparse_b200.config import Qwen2Config
+    from mini_hisparse_b200.engine.engine import Engine, load_model
+    from mini_hisparse_b200.engine.step import StepEntry
+    from mini_hisparse_b200.kernels import api as K
+
+    cfg_dict = dict(CONFIG_7B)
+    layers = args.layers or cfg_dict["num_hidden_layers"]
+    cfg_dict["num_hidden_layers"] = layers
+    cfg = Qwen2Config.from_dict(cfg_dict)
+    model = load_model(cfg_dict, device="cuda:0", dtype="bfloat16", random_seed=0)
+    peaks = measure.peaks()
+    vocab = cfg.vocab_size
+    steps, warmup = args.steps, args.warmup
+    start_ctx = CONTEXT - steps - warmup - 1      # the timed steps end at the context length
+
+    def decode_point(batch: int) -> dict:
+        engine = Engine(model, num_pages=batch * (CONTEXT // PAGE + 1), page_size=PAGE, max_requests=batch)
+        names = measure.synthetic_context(engine, batch, start_ctx)
+        r = measure.time_decode(engine, names, steps, warmup, vocab)
+        live = batch * (start_ctx + warmup + steps // 2)
+        r["bytes"] = measure.decode_bytes(model, engine.cache, live)
+        del engine
+        gc.collect()
+        torch.cuda.empty_cache()
+        return r
+
+    main_pt = decode_point(args.batch)
+    gbs = main_pt["bytes"] / (main_pt["ms_per_step"] / 1e3) / 1e9
+
+    # ---- end to end through Engine.step(): host tokens in, host tokens out -------------------
+    e2e = None
+    if not args.no_e2e:
+        engine = Engine(model, num_pages=args.batch * (CONTEXT // PAGE + 1), page_size=PAGE,
+                        max_requests=args.batch, max_tokens_per_step=4096)
+        g = torch.Generator().manual_seed(3)
+        for i in range(args.batch):
+            prompt = torch.randint(0, vocab, (start_ctx,), generator=g).tolist()
+            engine.add_request(f"e{i}", prompt, max_new_tokens=steps + warmup + 1)
+        while not all(r.decoding for r in engine.requests.values()):
+            engine.step()                           # real prefill, untimed
+        torch.cuda.synchronize()
+        done = 0
+        for i in range(warmup + steps):
+            if i == warmup:
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+            n = len(engine.step())
+            if i >= warmup:
+                done += n
+        torch.cuda.synchronize()
+        sec = time.perf_counter() - t0
+        # per step: the packed index arrays go up from pinned memory, the sampled ids come down
+        words = engine.runner.graphs[next(iter(engine.runner.graphs))].layout.total if engine.runner.graphs else 0
+        e2e = {"value": done / sec, "unit": "tokens/s", "h2d_bytes_per_step": words * 4,
+               "d2h_bytes_per_step": 4 * args.batch + 4, "ms_per_step": sec / steps * 1e3}
+        del engine
+        gc.collect()
+        torch.cuda.empty_cache()
+
+    # ---- prefill of one 2,048-token prompt -----------------------------------------------------
+    engine = Engine(model, num_pages=PREFILL_TOKENS // PAGE + 8, page_size=PAGE, max_requests=2,
+                    max_tokens_per_step=PREFILL_TOKENS)
+    g = torch.Generator().manual_seed(5)
+    times = []
+    for i in range(4):
+        name = f"p{i}"
+        engine.cache.open(name)
+        toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=g).tolist()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        engine.runner.step([StepEntry(name, toks, [PREFILL_TOKENS - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+        engine.cache.close(name)
+    pre_ms = min(times[1:])
+    flops = measure.prefill_flops(cfg, layers, PREFILL_TOKENS)
+    prefill = {"value": PREFILL_TOKENS / (pre_ms / 1e3), "tokens": PREFILL_TOKENS, "ms": pre_ms,
+               "frac": flops / (pre_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), "tflops": flops / (pre_ms / 1e3) / 1e12}
+    del engine
+    gc.collect()
+    torch.cuda.empty_cache()
+
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = decode_point(b)["tokens_per_s"]
+
+    line = {
+        "metric": "decode tokens/s (Qwen2.5-7B shape, batch 8, context 4096)",
+        "value": main_pt["tokens_per_s"],
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": steps,
+        "warmup": warmup,
+        "ms_per_step": main_pt["ms_per_step"],
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic: seeded random weights, uniform-random token ids, random KV for the device-timed context",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen2.5-7B shape", "global_batch": args.batch, "seq_len": CONTEXT,
+            "parallelism": "single GPU", "layers": layers, "layers_of_config": CONFIG_7B["num_hidden_layers"],
+            "hidden": cfg.hidden_size, "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+            "page_size": PAGE, "l2": "inputs larger than L2 (all weights are read every step)",
+            "peaks": f"of {peaks['source']}",
+        },
+        "clocks": main_pt["clocks"],
+        "e2e": e2e,
+        "gpu_launches": main_pt["launches"],
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": gbs / peaks["hbm_gbs"]},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -115,6 +115,7 @@ class _DecodeGraph:
         self.meta = torch.zeros(self.layout.total, dtype=torch.int32, device=runner.device)
         self.graph = None
         self.logits = None
+        self.launches = 0
 
 
 class BatchBuilder:
@@ -355,13 +356,17 @@ class ModelRunner:
             g.ws.frozen = True
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
+            before = K.launches
             with torch.cuda.graph(graph):
                 g.logits = self._forward(g.ws, views, segments, B)
+            g.launches = K.launches - before
+            K.launches = before + 0          # the capture launched nothing
             g.graph = graph
             # the capture itself ran nothing: the eager run above already produced this step
             self.stats["graph_steps"] += 1
             return g.logits
         g.graph.replay()
+        K.launches += g.launches
         self.stats["graph_steps"] += 1
         return g.logits
 

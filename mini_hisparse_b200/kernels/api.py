@@ -43,7 +43,12 @@ def _stream():
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+launches = 0   # kernels launched through this module (a captured graph counts its launches once)
+
+
 def _check(lib, code: int, what: str):
+    global launches
+    launches += 1
     if code != 0:
         raise KernelError(f"{what}: {lib.mhb_last_error().decode()}")
 
