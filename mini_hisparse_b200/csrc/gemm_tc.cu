@@ -1,0 +1,370 @@
+// bfloat16 matrix product on the 5th-generation tensor cores of sm_100a:
+//   D[128 x BN] += A_tile[128 x 64] * B_tile[BN x 64]^T   per pipeline stage,
+// operands staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle), products
+// issued by one thread with tcgen05.mma, the float32 accumulator held in tensor memory and read
+// back with tcgen05.ld for the epilogue.
+//
+// Both operands are row-major with K contiguous (nn.Linear layout, mini_hisparse/model.py:57-60:
+// y = x W^T).  Two shapes of use:
+//   * many tokens (prefill): A = activations [M, K], B = weights [N, K]; C[m, n] row-major.
+//   * few tokens (decode):   A = weights [N, K] (the 128-row operand streams the weights),
+//     B = activations [M <= 64, K]; the tile is written transposed, C[m, n] again.
+// With nsplit > 1 the K range is cut; split z writes a float32 partial matrix at
+// C + z * split_stride and the consumer sums the parts in order.
+//
+// Warp roles (192 threads): warp 0 issues TMA loads, warp 1 owns tensor memory and issues the
+// MMAs, warps 2-5 read the accumulator (warp w may touch lanes 32*(w%4) .. +31) and store.
+// Every wait on an mbarrier is bounded; a wait that runs out sets bit 4 of *status and the CTA
+// leaves through the common exit, which frees its tensor memory.
+#include <cuda.h>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+using namespace mhb;
+
+MHB_EXPORT const char* mhb_last_error() { return error_buffer(); }
+
+namespace {
+
+constexpr int BM = 128;          // rows of the A operand per tile = TMEM lanes
+constexpr int BK = 64;           // bf16 elements per stage along K = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 20;
+
+// ---- PTX wrappers --------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait: false if the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the
+// 128-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): groups of 8 rows are
+// 1024 bytes apart (SBO); the leading offset is unused for this layout; version 1 = sm_100.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);          // start address, bits 0-13
+    d |= (uint64_t)1 << 16;                           // leading byte offset (ignored), bits 16-29
+    d |= (uint64_t)(1024 >> 4) << 32;                 // stride byte offset, bits 32-45
+    d |= (uint64_t)1 << 46;                           // descriptor version
+    d |= (uint64_t)2 << 61;                           // layout: 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = BN.
+__host__ __device__ constexpr uint32_t make_idesc(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <int BN, int STAGES>
+struct Smem {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BARRIER_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int TOTAL = BARRIER_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;   // + alignment slack
+};
+
+template <typename OT> __device__ __forceinline__ void store_out(OT* p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// C element of (a-row ra, b-row rb): TRANSPOSED ? C[rb, ra] : C[ra, rb]
+template <int BN, int STAGES, bool TRANSPOSED, typename OT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               OT* __restrict__ C, int Ra, int Rb, int K, long long ldc, int kb_per_split,
+               long long split_stride, int* __restrict__ status) {
+    using S = Smem<BN, STAGES>;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_base = smem_base + S::BARRIER_OFFSET;
+    auto full_bar = [&](int s) { return bar_base + 8 * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8 * (STAGES + s); };
+    const uint32_t tmem_full_bar = bar_base + 8 * (2 * STAGES);
+    uint32_t* tmem_slot = (uint32_t*)(smem + S::BARRIER_OFFSET + 8 * (2 * STAGES + 1));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ra0 = blockIdx.x * BM, rb0 = blockIdx.y * BN;
+    const int total_kb = (K + BK - 1) / BK;
+    const int kb_begin = blockIdx.z * kb_per_split;
+    const int kb_end = min(total_kb, kb_begin + kb_per_split);
+    const int num_kb = max(0, kb_end - kb_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        mbar_init(tmem_full_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+            int issued = 0;
+            for (int i = 0; i < num_kb && ok; ++i) {
+                const int s = i % STAGES;
+                const uint32_t phase = (i / STAGES) & 1;
+                ok = mbar_wait(empty_bar(s), phase ^ 1);
+                if (!ok) break;
+                mbar_expect_tx(full_bar(s), S::STAGE_BYTES);
+                const uint32_t a_dst = smem_base + s * S::STAGE_BYTES;
+                tma_load_2d(a_dst, &map_a, (kb_begin + i) * BK, ra0, full_bar(s));
+                tma_load_2d(a_dst + S::A_BYTES, &map_b, (kb_begin + i) * BK, rb0, full_bar(s));
+                issued = i + 1;
+            }
+            if (!ok) {
+                // do not leave while our own copies are in flight: wait (bounded) for the armed stages
+                for (int i = max(0, issued - STAGES); i < issued; ++i)
+                    mbar_wait(full_bar(i % STAGES), (i / STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BN);
+            for (int i = 0; i < num_kb && ok; ++i) {
+                const int s = i % STAGES;
+                const uint32_t phase = (i / STAGES) & 1;
+                ok = mbar_wait(full_bar(s), phase);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_base + s * S::STAGE_BYTES;
+                const uint32_t b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const uint64_t da = make_smem_desc(a_addr + k * UMMA_K * 2);
+                    const uint64_t db = make_smem_desc(b_addr + k * UMMA_K * 2);
+                    umma_bf16(tmem_base, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(empty_bar(s));       // frees the stage when these MMAs have read it
+            }
+            if (ok) umma_commit(tmem_full_bar);  // the accumulator is complete
+        }
+    } else {
+        // epilogue: warp w reads TMEM lanes 32*(w%4) .. +31 = rows of the A operand
+        const int quarter = warp & 3;
+        const int ra = ra0 + quarter * 32 + lane;
+        if (num_kb > 0) ok = mbar_wait(tmem_full_bar, 0);
+        tc_fence_after();
+        OT* Cz = C + (size_t)blockIdx.z * split_stride;
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t r[16];
+                if (num_kb > 0) {
+                    tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c0, r);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = 0;   // an empty split contributes zeros
+                }
+                if (TRANSPOSED) {
+                    // lanes run along ra = the contiguous dimension of C: coalesced per column
+                    if (ra < Ra) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int rb = rb0 + c0 + j;
+                            if (rb < Rb) store_out<OT>(Cz + (size_t)rb * ldc + ra, __uint_as_float(r[j]));
+                        }
+                    }
+                } else if (ra < Ra) {
+                    OT* row = Cz + (size_t)ra * ldc + rb0 + c0;
+                    if (rb0 + c0 + 16 <= Rb && ((uintptr_t)row & 15) == 0) {
+                        if constexpr (sizeof(OT) == 4) {
+#pragma unroll
+                            for (int j = 0; j < 16; j += 4)
+                                *(uint4*)(row + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                        } else {
+                            uint32_t p[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                                p[j] = *(uint32_t*)&v;
+                            }
+                            *(uint4*)(row) = make_uint4(p[0], p[1], p[2], p[3]);
+                            *(uint4*)(row + 8) = make_uint4(p[4], p[5], p[6], p[7]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (rb0 + c0 + j < Rb) store_out<OT>(row + j, __uint_as_float(r[j]));
+                    }
+                }
+            }
+        }
+    }
+    if (!ok && status) atomicOr(status, 4);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---- host: tensor maps ----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// A [rows, K] bfloat16 matrix with row stride ld (elements); box = box_rows x 64, 128-byte swizzle,
+// zeros outside the matrix.
+int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, long long ld, int box_rows) {
+    typedef std::tuple<const void*, long long, long long, long long, int> Key;
+    static std::map<Key, CUtensorMap> cache;
+    static std::mutex mu;
+    Key key(ptr, rows, K, ld, box_rows);
+    {
+        std::lock_guard<std::mutex> g(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) { *map = it->second; return 0; }
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail("gemm_tc: the driver has no cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("gemm_tc: cuTensorMapEncodeTiled failed with code %d (rows %lld, K %lld, ld %lld)",
+                                       (int)r, rows, K, ld);
+    std::lock_guard<std::mutex> g(mu);
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = *map;
+    return 0;
+}
+
+template <int BN, int STAGES, bool TRANSPOSED, typename OT>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int Ra, int Rb, int K, long long ldc,
+           int nsplit, int kb_per_split, long long split_stride, int* status, cudaStream_t stream) {
+    auto kern = gemm_tc_kernel<BN, STAGES, TRANSPOSED, OT>;
+    constexpr int smem = Smem<BN, STAGES>::TOTAL;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return fail("gemm_tc: cannot set %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid((Ra + BM - 1) / BM, (Rb + BN - 1) / BN, nsplit);
+    kern<<<grid, THREADS, smem, stream>>>(ma, mb, (OT*)C, Ra, Rb, K, ldc, kb_per_split, split_stride, status);
+    return check_launch("gemm_tc");
+}
+
+template <bool TRANSPOSED, typename OT>
+int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* C, int Ra, int Rb, int K,
+                long long ldc, int nsplit, int kbps, long long ss, int* status, cudaStream_t st) {
+    switch (bn) {
+        case 16: return launch<16, 8, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
+        case 32: return launch<32, 8, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
+        case 64: return launch<64, 8, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
+        case 128: return launch<128, 6, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
+        case 256: return launch<256, 4, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
+    }
+    return fail("gemm_tc: no tile for BN %d", bn);
+}
+}  // namespace
+
+// C[M, N] = X[M, K] * W[N, K]^T, bfloat16 in, float32 accumulation, C float32 or bfloat16.
+// swap != 0 streams W through the 128-row operand (few tokens); bn is the tile width along the
+// other operand (16..256).  Requirements (else an error, never a wrong result): K % 8 == 0,
+// lda % 8 == 0, ldw % 8 == 0, pointers 16-byte aligned.
+MHB_EXPORT int mhb_gemm_tc(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
+                           long long lda, long long ldw, long long ldc, int swap, int bn, int nsplit,
+                           long long split_stride, int* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || lda % 8 || ldw % 8) return fail("gemm_tc: K, lda and ldw must be multiples of 8 (K %d, lda %lld, ldw %lld)", K, lda, ldw);
+    if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return fail("gemm_tc: operands must be 16-byte aligned");
+    if (nsplit < 1) nsplit = 1;
+    if (nsplit > 1 && c_dtype != MHB_F32) return fail("gemm_tc: split-K partials must be float32");
+    const int total_kb = (K + BK - 1) / BK;
+    if (nsplit > total_kb) return fail("gemm_tc: %d splits for %d K blocks", nsplit, total_kb);
+    const int kbps = (total_kb + nsplit - 1) / nsplit;
+    if ((long long)kbps * (nsplit - 1) >= total_kb) return fail("gemm_tc: split %d of K blocks %d leaves an empty split", nsplit, total_kb);
+    CUtensorMap ma, mb;
+    int rc;
+    if (swap) {
+        if ((rc = make_map(&ma, W, N, K, ldw, BM))) return rc;
+        if ((rc = make_map(&mb, X, M, K, lda, bn))) return rc;
+        if (c_dtype == MHB_F32) return dispatch_bn<true, float>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, status, stream);
+        return dispatch_bn<true, __nv_bfloat16>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, status, stream);
+    }
+    if ((rc = make_map(&ma, X, M, K, lda, BM))) return rc;
+    if ((rc = make_map(&mb, W, N, K, ldw, bn))) return rc;
+    if (c_dtype == MHB_F32) return dispatch_bn<false, float>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, status, stream);
+    return dispatch_bn<false, __nv_bfloat16>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, status, stream);
+}

@@ -274,6 +274,8 @@ class ModelRunner:
         self.sm_count = self.batch.sm_count
         self.ws = Workspace(self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        if hasattr(self.rt, "status"):
+            self.rt.status = self.status
         self.use_graphs = use_graphs and model.graph_safe
         self.graphs: dict[tuple[int, int], _DecodeGraph] = {}
         self.observer = None
@@ -380,4 +382,6 @@ class ModelRunner:
                 what.append("a token id outside the vocabulary reached the embedding")
             if bits & 2:
                 what.append("a position had no valid page in its block table")
+            if bits & 4:
+                what.append("a bounded wait in the tensor-core matrix product ran out")
             raise StepError("; ".join(what) or f"kernel status {bits}")

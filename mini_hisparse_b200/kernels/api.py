@@ -135,6 +135,29 @@ def gemm_simt(a, w, out, bias=None, nsplit=1, split_stride=0):
         c_int(nsplit), c_longlong(split_stride), _stream()), "gemm_simt")
 
 
+def gemm_tc(a, w, out, *, swap: bool, bn: int, nsplit=1, split_stride=0, status=None):
+    """out[M, N] = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulate).
+
+    ``swap`` streams the weights through the 128-row operand (for few tokens, M <= bn <= 64);
+    ``bn`` is the tile width along the other operand."""
+    lib = build.load("gemm_tc")
+    M, K = a.shape
+    N = w.shape[0]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc: operands must be bfloat16")
+    if w.shape[1] != K:
+        raise KernelError(f"gemm_tc: a is [{M},{K}] but w is {list(w.shape)}")
+    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(-1) != 1:
+        raise KernelError("gemm_tc: the last dimension must be contiguous")
+    if swap and M > bn:
+        raise KernelError(f"gemm_tc: {M} tokens do not fit the swapped tile of {bn}")
+    _check(lib, lib.mhb_gemm_tc(
+        _ptr(a), _ptr(w), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K),
+        c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(-2)),
+        c_int(1 if swap else 0), c_int(bn), c_int(nsplit), c_longlong(split_stride), _ptr(status),
+        _stream()), "gemm_tc")
+
+
 def attention_simt(q, cache, out, part_acc, part_ml, items, num_items, max_items, positions,
                    block_table, tok_part_row, *, nq, nkv, d, page_size, window=0, scale=None):
     lib = build.load("attention_simt")

@@ -45,6 +45,10 @@ class Product:
             raise ValueError("split product has not been reduced")
         return self.tensor
 
+    def reduced(self) -> torch.Tensor:
+        """The product as one float32 matrix (for inspection; the kernels sum the parts themselves)."""
+        return self.tensor.float().sum(0) if self.nsplit > 1 else self.tensor.float()
+
 
 class Workspace:
     """Named scratch buffers, reused layer after layer.  ``frozen`` forbids growth (a captured
@@ -91,8 +95,10 @@ class Runtime:
         return ("elementwise", "gemm_simt", "attention_simt", "sampling")
 
     def linear(self, x: torch.Tensor, weight: torch.Tensor, ws: Workspace, name: str,
-               out_dtype: torch.dtype | None = None, bias: torch.Tensor | None = None) -> Product:
-        """x [M, K] times weight [N, K] transposed, float32 accumulation."""
+               out_dtype: torch.dtype | None = None, bias: torch.Tensor | None = None,
+               allow_split: bool = True) -> Product:
+        """x [M, K] times weight [N, K] transposed, float32 accumulation.  The result may come as
+        split-K partial matrices unless ``allow_split`` is False."""
         M, N = x.shape[0], weight.shape[0]
         out = ws.get(name, (M, N), out_dtype or self.dtype)
         K.gemm_simt(x, weight, out, bias=bias)

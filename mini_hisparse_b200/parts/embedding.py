@@ -56,4 +56,5 @@ class LMHead(Part):
         self.weight = embedding.weight
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        return ctx.rt.linear(h, self.weight, ctx.ws, "logits", out_dtype=torch.float32).matrix
+        return ctx.rt.linear(h, self.weight, ctx.ws, "logits", out_dtype=torch.float32,
+                             allow_split=False).matrix

@@ -119,6 +119,46 @@ def test_gemm_is_true_float32():
     assert abs(float(out[0, 0]) - exact) < 1e-4
 
 
+@pytest.mark.parametrize("M,N,K_,swap,bn,nsplit", [
+    (128, 128, 64, False, 128, 1), (200, 300, 136, False, 128, 1), (333, 1000, 3584, False, 256, 1),
+    (70, 520, 200, False, 128, 2), (8, 256, 512, True, 16, 1), (1, 777, 96, True, 16, 1),
+    (17, 1000, 3584, True, 32, 7), (64, 130, 1024, True, 64, 4), (2048, 2000, 512, False, 256, 1),
+])
+@pytest.mark.parametrize("out_dtype", DTYPES)
+def test_gemm_tensor_core(M, N, K_, swap, bn, nsplit, out_dtype):
+    """The tcgen05 product against float32 matmul of the same bfloat16 values: ragged edges in
+    every dimension, both operand orders, split K."""
+    a = rnd(M, K_, dtype=torch.bfloat16, seed=1)
+    w = rnd(N, K_, dtype=torch.bfloat16, seed=2)
+    ref = a.float() @ w.float().T
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    if nsplit > 1:
+        if out_dtype != torch.float32:
+            pytest.skip("partials are float32")
+        out = torch.full((nsplit, M, N), float("nan"), device=DEV)
+        K().gemm_tc(a, w, out, swap=swap, bn=bn, nsplit=nsplit, split_stride=out.stride(0), status=status)
+        got = out.sum(0)
+    else:
+        out = torch.full((M + 1, N), float("nan"), dtype=out_dtype, device=DEV)
+        K().gemm_tc(a, w, out[:M], swap=swap, bn=bn, status=status)
+        assert bool(out[M].isnan().all())               # nothing written past the last row
+        got = out[:M].float()
+    assert int(status) == 0
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(got, ref, atol=3e-5 * math.sqrt(K_) * 4, rtol=2e-5)
+    else:
+        torch.testing.assert_close(got, ref, atol=1e-2 * float(ref.abs().max()), rtol=1e-2)
+
+
+def test_gemm_tensor_core_refuses_unaligned_k():
+    from mini_hisparse_b200.kernels.api import KernelError
+
+    a = rnd(4, 100, dtype=torch.bfloat16)
+    w = rnd(9, 100, dtype=torch.bfloat16)
+    with pytest.raises(KernelError, match="multiples of 8"):
+        K().gemm_tc(a, w, torch.empty(4, 9, device=DEV), swap=True, bn=16)
+
+
 # ---- rotary + append -----------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,d,P_", [(4, 2, 16, 16), (3, 1, 32, 32), (10, 2, 48, 16), (7, 7, 128, 8)])

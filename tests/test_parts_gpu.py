@@ -96,7 +96,7 @@ def test_attention_mixer_over_its_cache(dtype, nq, nkv, d, theta):
         entries = [StepEntry(r, [0] * cuts[r][step], []) for r in ("a", "b")]
         ctx, views, segments = context(rt, cache, batch, ws, status, entries)
         h = torch.cat([hs[r][done[r]: done[r] + cuts[r][step]] for r in ("a", "b")]).to(DEV, dtype)
-        out = mixer.forward(h, ctx, batch.cache_view(0, views["groups"])).matrix.float().cpu()
+        out = mixer.forward(h, ctx, batch.cache_view(0, views["groups"])).reduced().cpu()
         row = 0
         for r in ("a", "b"):
             n = cuts[r][step]
@@ -124,7 +124,7 @@ def test_swiglu_embedding_head_parts(dtype):
     ff = FEED_FORWARDS.build(PartSpec.make("swiglu", hidden_size=88, intermediate_size=200), rt=rt)
     w = fill(ff, 3, dtype)
     h = torch.randn(11, 88).to(torch.bfloat16).float()
-    out = ff.forward(h.to(DEV, dtype), ctx).matrix.float().cpu()
+    out = ff.forward(h.to(DEV, dtype), ctx).reduced().cpu()
     ref = P.swiglu(h, w["gate_proj.weight"], w["up_proj.weight"], w["down_proj.weight"])
     torch.testing.assert_close(out, ref, **tol(dtype, ref))
 
@@ -168,6 +168,6 @@ def test_block_alone(dtype, folders):
     pend = (torch.randn(T, 96) * 0.3).to(torch.bfloat16).float()
     x = x0.clone().to(DEV)
     out = block.forward(x, Product(pend.to(DEV, dtype)), ctx, batch.cache_view(0, views["groups"]))
-    total = x.cpu() + out.matrix.float().cpu()
+    total = x.cpu() + out.reduced().cpu()
     ref = P.decoder_layer(pw, sd, 1, x0 + pend, torch.arange(T))
     torch.testing.assert_close(total, ref, **tol(dtype, ref))
