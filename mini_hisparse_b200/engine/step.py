@@ -192,7 +192,7 @@ class BatchBuilder:
             region[n_items * ITEM_INTS :] = 0
             buf[offs["tok_part_row"] : offs["tok_part_row"] + T] = plan.tok_part_row
             buf[offs["tok_nsplit"] : offs["tok_nsplit"] + T] = plan.tok_nsplit
-            facts.append({"num_items": n_items, "part_rows": plan.part_rows,
+            facts.append({"n_small": plan.n_small, "n_big": plan.n_big, "part_rows": plan.part_rows,
                           "any_split": bool(plan.part_rows)})
         return len(rows), facts
 
@@ -205,13 +205,12 @@ class BatchBuilder:
             offs = layout.group_offsets[gi]
             cap_items, width = layout.groups[gi]
             f = facts[gi]
-            n_launch = cap_items if launch_items else f["num_items"]
             group_meta.append(
                 {
                     "block_table": v(offs["block_table"], S * width).view(S, width),
                     "items": v(offs["items"], cap_items * ITEM_INTS),
-                    "num_items": n_launch,
-                    "launch_items": n_launch,
+                    "n_small": cap_items if launch_items else f["n_small"],
+                    "n_big": 0 if launch_items else f["n_big"],
                     "tok_part_row": v(offs["tok_part_row"], T),
                     "tok_nsplit": v(offs["tok_nsplit"], T),
                     "part_rows_cap": f["part_rows"],
@@ -350,7 +349,7 @@ class ModelRunner:
             # fixed facts for the capture: every item slot is launched, splits are constant
             fixed = []
             for gi, pg in enumerate(self.cache.page_groups):
-                fixed.append({"num_items": layout.groups[gi][0], "part_rows": B * g.nsplit[gi],
+                fixed.append({"n_small": layout.groups[gi][0], "n_big": 0, "part_rows": B * g.nsplit[gi],
                               "any_split": g.nsplit[gi] > 1})
             views = self.batch._views(g.meta, layout, B, B, B, fixed, launch_items=True)
             # one eager run sizes the workspace and warms the kernels up, then the capture

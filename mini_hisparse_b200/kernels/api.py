@@ -171,6 +171,24 @@ def attention_simt(q, cache, out, part_acc, part_ml, items, num_items, max_items
         "attention")
 
 
+MMA_HEAD_DIMS = (32, 64, 96, 128)   # head sizes the tensor-core attention kernel is built for
+
+
+def attention_mma(q, cache, out, part_acc, part_ml, items, num_items, rows, positions, block_table,
+                  tok_part_row, *, nq, nkv, d, page_size, window=0, scale=None):
+    """Tensor-core attention (bfloat16) over ``num_items`` items planned for tiles of ``rows`` rows."""
+    lib = build.load("attention_mma")
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError("attention_mma: q and the cache must be bfloat16")
+    if scale is None:
+        scale = float(d) ** -0.5
+    _check(lib, lib.mhb_attention_mma(
+        _ptr(q), _ptr(cache), _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(items), c_int(num_items),
+        c_int(num_items), c_int(rows), _ptr(positions), _ptr(block_table), c_int(block_table.shape[-1]),
+        _ptr(tok_part_row), c_int(nq), c_int(nkv), c_int(d), c_int(page_size), c_int(cache.shape[0]),
+        c_int(window or 0), c_float(scale), _stream()), "attention_mma")
+
+
 def attention_combine(part_acc, part_ml, tok_part_row, tok_nsplit, out, *, nq, d):
     lib = build.load("attention_simt")
     T = out.shape[0]

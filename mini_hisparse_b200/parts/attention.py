@@ -12,7 +12,7 @@ from .registry import POSITIONS, register_mixer
 from .spec import PagedKVNeed, ParamSpec, PartSpec
 
 ROW_TILE = 16          # query rows (tokens x heads of one group) per CTA of the attention kernel
-KEY_TILE = 32          # keys per inner tile; split boundaries are multiples of it
+KEY_TILE = 64          # split boundaries are multiples of the kernels' key tile
 ITEM_INTS = 8
 MIN_KEYS_PER_SPLIT = 256
 SPLIT_MAX_TOKENS = 16  # only short segments (decode tokens, tiny portions) are split along the keys
@@ -21,57 +21,70 @@ MAX_SPLITS = 64
 
 @dataclass
 class AttentionPlan:
-    """Host arrays of one page group for one step (see csrc/attention_simt.cu for the item layout)."""
+    """Host arrays of one page group for one step (see csrc/attention_simt.cu for the item layout).
+    Items of short segments (tiles of at most ROW_TILE rows, possibly split along the keys) come
+    first, then the items of long portions (tiles of at most ``need.tile_rows`` rows)."""
 
-    items: np.ndarray          # [n_items, 8] int32
+    items: np.ndarray          # [n_small + n_big, 8] int32
+    n_small: int
+    n_big: int
     tok_part_row: np.ndarray   # [T] int32
     tok_nsplit: np.ndarray     # [T] int32: 0 = written directly
     part_rows: int
 
 
+def _tiling(groups: int, rows: int):
+    """Head chunks and tokens per tile for tiles of ``rows`` query rows."""
+    if groups <= rows:
+        return [(0, groups)], rows // groups
+    return [(h, min(rows, groups - h)) for h in range(0, groups, rows)], 1
+
+
 def plan_attention(need: PagedKVNeed, segments, T: int, sm_count: int = 148,
                    fixed_nsplit: int | None = None) -> AttentionPlan:
-    """Cut the step's attention into items of at most ROW_TILE query rows.
+    """Cut the step's attention into items.
 
     A tile is a run of tokens of one segment times the heads of one KV group (or a chunk of
     them, if a group has more heads than a tile has rows).  Its keys are [kv_begin, kv_end):
-    everything up to its last token, minus what a window has passed.  Short segments with long
-    histories are split along the keys so that a small batch still fills the GPU; with
-    ``fixed_nsplit`` every short segment gets exactly that many splits (a captured graph needs
-    a fixed launch size), empty ones included.
+    everything up to its last token, minus what a window has passed.  Short segments (decode
+    tokens, tiny portions) get tiles of ROW_TILE rows and, when their histories are long, are
+    split along the keys so that a small batch still fills the GPU; with ``fixed_nsplit`` every
+    short segment gets exactly that many splits (a captured graph needs a fixed launch size),
+    empty ones included.  Long portions get tiles of ``need.tile_rows`` rows and are not split.
     """
     groups = need.q_heads // need.kv_heads
-    if groups <= ROW_TILE:
-        head_chunks = [(0, groups)]
-        tok_per_tile = ROW_TILE // groups
-    else:
-        head_chunks = [(h, min(ROW_TILE, groups - h)) for h in range(0, groups, ROW_TILE)]
-        tok_per_tile = 1
     window = need.window or 0
-    tiles = []
+    small_chunks, small_tpt = _tiling(groups, ROW_TILE)
+    big_chunks, big_tpt = _tiling(groups, need.tile_rows)
+    small_tiles, big_items = [], []
     for si, seg in enumerate(segments):
-        for a in range(0, seg.count, tok_per_tile):
-            nt = min(tok_per_tile, seg.count - a)
+        short = seg.count <= SPLIT_MAX_TOKENS
+        tpt = small_tpt if short else big_tpt
+        for a in range(0, seg.count, tpt):
+            nt = min(tpt, seg.count - a)
             first_pos = seg.start + a
             kv_end = first_pos + nt
             kv_begin = max(0, first_pos - window + 1) if window else 0
-            tiles.append((si, seg.offset + a, nt, kv_begin, kv_end, seg.count))
-    base_ctas = len(tiles) * len(head_chunks) * need.kv_heads
+            if short:
+                small_tiles.append((si, seg.offset + a, nt, kv_begin, kv_end))
+            else:
+                for h0, nh in big_chunks:
+                    big_items.append((si, seg.offset + a, nt, h0, nh, kv_begin, kv_end, -1))
+    base_ctas = (len(small_tiles) * len(small_chunks) + len(big_items)) * need.kv_heads
     items = []
     tok_part_row = np.zeros(T, np.int32)
     tok_nsplit = np.zeros(T, np.int32)
     part_rows = 0
-    for si, tok0, nt, kv_begin, kv_end, seg_count in tiles:
+    for si, tok0, nt, kv_begin, kv_end in small_tiles:
         nsplit = 1
-        if seg_count <= SPLIT_MAX_TOKENS:
-            if fixed_nsplit is not None:
-                nsplit = fixed_nsplit
-            elif base_ctas < 2 * sm_count:
-                want = -(-2 * sm_count // max(base_ctas, 1))
-                fit = max(1, (kv_end - kv_begin) // MIN_KEYS_PER_SPLIT)
-                nsplit = max(1, min(want, fit, MAX_SPLITS))
+        if fixed_nsplit is not None:
+            nsplit = fixed_nsplit
+        elif base_ctas < 2 * sm_count:
+            want = -(-2 * sm_count // max(base_ctas, 1))
+            fit = max(1, (kv_end - kv_begin) // MIN_KEYS_PER_SPLIT)
+            nsplit = max(1, min(want, fit, MAX_SPLITS))
         if nsplit == 1:
-            for h0, nh in head_chunks:
+            for h0, nh in small_chunks:
                 items.append((si, tok0, nt, h0, nh, kv_begin, kv_end, -1))
             continue
         span = kv_end - kv_begin
@@ -81,28 +94,28 @@ def plan_attention(need: PagedKVNeed, segments, T: int, sm_count: int = 148,
             tok_part_row[t] = part_rows
             tok_nsplit[t] = nsplit
             part_rows += nsplit
-        for s in range(nsplit):
-            b = min(kv_end, kv_begin + s * chunk)
+        for sp in range(nsplit):
+            b = min(kv_end, kv_begin + sp * chunk)
             e = min(kv_end, b + chunk)
-            for h0, nh in head_chunks:
-                items.append((si, tok0, nt, h0, nh, b, e, s))
-    arr = np.asarray(items, np.int32).reshape(-1, ITEM_INTS)
-    return AttentionPlan(arr, tok_part_row, tok_nsplit, part_rows)
+            for h0, nh in small_chunks:
+                items.append((si, tok0, nt, h0, nh, b, e, sp))
+    n_small = len(items)
+    arr = np.asarray(items + big_items, np.int32).reshape(-1, ITEM_INTS)
+    return AttentionPlan(arr, n_small, len(big_items), tok_part_row, tok_nsplit, part_rows)
 
 
 def plan_capacity(need: PagedKVNeed, max_tokens: int, max_segments: int,
                   fixed_nsplit: int | None = None) -> tuple[int, int]:
     """Upper bounds (items, partial rows) for a step of at most max_tokens / max_segments."""
     groups = need.q_heads // need.kv_heads
-    chunks = 1 if groups <= ROW_TILE else -(-groups // ROW_TILE)
-    tok_per_tile = max(1, ROW_TILE // groups)
+    small_chunks, small_tpt = _tiling(groups, ROW_TILE)
+    big_chunks, big_tpt = _tiling(groups, need.tile_rows)
     splits = fixed_nsplit or MAX_SPLITS
-    # every segment may end with a ragged tile; short segments may be split
-    tiles = max_tokens // tok_per_tile + max_segments
-    short_tiles = min(tiles, max_segments * -(-SPLIT_MAX_TOKENS // tok_per_tile))
-    items = (tiles + short_tiles * (splits - 1)) * chunks
-    part_rows = min(max_tokens, max_segments * SPLIT_MAX_TOKENS) * splits
-    return items, part_rows
+    # every segment may end with a ragged tile; only short segments are split
+    big = (max_tokens // big_tpt + max_segments) * len(big_chunks)
+    short_tokens = min(max_tokens, max_segments * SPLIT_MAX_TOKENS)
+    small = (short_tokens // small_tpt + max_segments) * len(small_chunks) * splits
+    return big + small, short_tokens * splits
 
 
 @register_mixer("gq_attention")
@@ -131,8 +144,14 @@ class GQAttention(Mixer):
         self.scale = float(self.d) ** -0.5
         self.qkv_weight = self.qkv_bias_vec = self.o_weight = None
 
+    @property
+    def tensor_core_attention(self) -> bool:
+        """bfloat16 and a head size the mma kernel is built for; else the CUDA-core kernel."""
+        return (self.rt is not None and self.rt.dtype == torch.bfloat16 and self.d in K.MMA_HEAD_DIMS)
+
     def cache_need(self):
-        return PagedKVNeed(kv_heads=self.nkv, head_dim=self.d, q_heads=self.nq, window=self.window)
+        return PagedKVNeed(kv_heads=self.nkv, head_dim=self.d, q_heads=self.nq, window=self.window,
+                           tile_rows=64 if self.tensor_core_attention else ROW_TILE)
 
     def parameters(self):
         q, kv = self.nq * self.d, self.nkv * self.d
@@ -173,12 +192,18 @@ class GQAttention(Mixer):
         part_rows = max(1, meta["part_rows_cap"])
         part_acc = ws.get("attn_part_acc", (part_rows, self.nq, self.d), torch.float32)
         part_ml = ws.get("attn_part_ml", (part_rows, self.nq, 2), torch.float32)
-        K.attention_simt(
-            q, cache.storage, attn, part_acc, part_ml, meta["items"], meta["num_items"],
-            meta["launch_items"], ctx.positions, meta["block_table"], meta["tok_part_row"],
-            nq=self.nq, nkv=self.nkv, d=self.d, page_size=cache.page_size,
-            window=self.window or 0, scale=self.scale,
-        )
+        common = dict(nq=self.nq, nkv=self.nkv, d=self.d, page_size=cache.page_size,
+                      window=self.window or 0, scale=self.scale)
+        args = (q, cache.storage, attn, part_acc, part_ml)
+        tail = (ctx.positions, meta["block_table"], meta["tok_part_row"])
+        n_small, n_big = meta["n_small"], meta["n_big"]
+        if self.tensor_core_attention:
+            if n_small:
+                K.attention_mma(*args, meta["items"], n_small, 16, *tail, **common)
+            if n_big:
+                K.attention_mma(*args, meta["items"][n_small * ITEM_INTS:], n_big, 64, *tail, **common)
+        elif n_small + n_big:
+            K.attention_simt(*args, meta["items"], n_small + n_big, n_small + n_big, *tail, **common)
         if meta["any_split"]:
             K.attention_combine(part_acc, part_ml, meta["tok_part_row"], meta["tok_nsplit"], attn,
                                 nq=self.nq, d=self.d)

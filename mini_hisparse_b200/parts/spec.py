@@ -138,6 +138,7 @@ class PagedKVNeed(CacheNeed):
     head_dim: int
     q_heads: int
     window: int | None = None
+    tile_rows: int = 16      # query rows per attention tile for long portions (a kernel's choice)
     kind: str = field(default="pages", init=False)
 
 

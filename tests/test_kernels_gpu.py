@@ -264,15 +264,16 @@ def paged_case(nq, nkv, d, P_, seg_specs, dtype, seed=0):
     return cache, table.to(DEV), segments, qs, ks, vs, torch.tensor(positions, dtype=torch.int32, device=DEV)
 
 
-def run_attention(nq, nkv, d, P_, seg_specs, dtype, window=None, fixed_nsplit=None, seed=0, edit=None):
-    from mini_hisparse_b200.parts.attention import plan_attention
+def run_attention(nq, nkv, d, P_, seg_specs, dtype, window=None, fixed_nsplit=None, seed=0, edit=None,
+                  kernel="simt"):
+    from mini_hisparse_b200.parts.attention import ITEM_INTS, plan_attention
     from mini_hisparse_b200.parts.spec import PagedKVNeed
 
     cache, table, segments, qs, ks, vs, positions = paged_case(nq, nkv, d, P_, seg_specs, dtype, seed)
     if edit:
         edit(qs, ks, vs, cache, table)
     T = sum(n for _, n in seg_specs)
-    need = PagedKVNeed(nkv, d, nq, window)
+    need = PagedKVNeed(nkv, d, nq, window, tile_rows=64 if kernel == "mma" else 16)
     plan = plan_attention(need, segments, T, 148, fixed_nsplit=fixed_nsplit)
     q = torch.cat([qq[h:] for qq, (h, n) in zip(qs, seg_specs)]).reshape(T, nq * d).to(DEV)
     out = torch.full((T, nq * d), float("nan"), dtype=dtype, device=DEV)
@@ -283,8 +284,15 @@ def run_attention(nq, nkv, d, P_, seg_specs, dtype, window=None, fixed_nsplit=No
     tpr = torch.from_numpy(plan.tok_part_row).to(DEV)
     tns = torch.from_numpy(plan.tok_nsplit).to(DEV)
     n_items = plan.items.shape[0]
-    K().attention_simt(q, cache, out, part_acc, part_ml, items, n_items, n_items, positions, table, tpr,
-                       nq=nq, nkv=nkv, d=d, page_size=P_, window=window or 0)
+    kw = dict(nq=nq, nkv=nkv, d=d, page_size=P_, window=window or 0)
+    if kernel == "mma":
+        if plan.n_small:
+            K().attention_mma(q, cache, out, part_acc, part_ml, items, plan.n_small, 16, positions, table, tpr, **kw)
+        if plan.n_big:
+            K().attention_mma(q, cache, out, part_acc, part_ml, items[plan.n_small * ITEM_INTS:], plan.n_big, 64,
+                              positions, table, tpr, **kw)
+    else:
+        K().attention_simt(q, cache, out, part_acc, part_ml, items, n_items, n_items, positions, table, tpr, **kw)
     if plan.part_rows:
         K().attention_combine(part_acc, part_ml, tpr, tns, out, nq=nq, d=d)
     ref = torch.cat([
@@ -292,6 +300,43 @@ def run_attention(nq, nkv, d, P_, seg_specs, dtype, window=None, fixed_nsplit=No
         for qq, kk, vv, (h, n) in zip(qs, ks, vs, seg_specs)
     ]).reshape(T, nq * d)
     return out.float().cpu(), ref, plan
+
+
+@pytest.mark.parametrize("nq,nkv,d,P_", [(4, 2, 32, 16), (3, 1, 32, 32), (28, 4, 128, 16), (20, 1, 96, 8),
+                                          (6, 3, 64, 7), (40, 2, 128, 16)])
+def test_attention_tensor_core_portions_and_decode_mixed(nq, nkv, d, P_):
+    """The mma kernel: long portions (64-row tiles), short ones (16-row tiles, warps split the
+    keys), portions that start inside a page, and groups larger than a tile."""
+    specs = [(0, 137), (45, 19), (130, 1), (63, 2), (200, 70), (0, 1), (5, 16)]
+    out, ref, plan = run_attention(nq, nkv, d, P_, specs, torch.bfloat16, kernel="mma")
+    assert plan.n_small and plan.n_big
+    torch.testing.assert_close(out, ref, **tol(torch.bfloat16, 2))
+
+
+def test_attention_tensor_core_splits_window_and_far_key():
+    bf = torch.bfloat16
+    out, ref, plan = run_attention(28, 4, 128, 16, [(700, 1), (33, 1), (1023, 1), (0, 1)], bf, fixed_nsplit=5, kernel="mma")
+    assert plan.part_rows == 20
+    torch.testing.assert_close(out, ref, **tol(bf, 2))
+    out, ref, plan = run_attention(8, 2, 64, 16, [(2000, 1)], bf, kernel="mma")
+    assert plan.part_rows > 1
+    torch.testing.assert_close(out, ref, **tol(bf, 2))
+    for window in (1, 5, 16, 40, 64, 65):
+        out, ref, _ = run_attention(4, 2, 32, 16, [(0, 150), (77, 3), (100, 1)], bf, window=window, kernel="mma")
+        torch.testing.assert_close(out, ref, **tol(bf, 2))
+
+    def edit(qs, ks, vs, cache, table):
+        d = qs[0].shape[-1]
+        direction = torch.zeros(d)
+        direction[5] = 1.0
+        for h in range(qs[0].shape[1]):
+            qs[0][-1, h] = direction * 60.0
+        ks[0][3, :] = (direction * 8.0).to(ks[0].dtype)
+        cache[int(table[0, 0]), 0, :, 3] = ks[0][3].to(cache.device)
+    out, ref, _ = run_attention(4, 2, 64, 16, [(640, 1)], bf, edit=edit, kernel="mma")
+    torch.testing.assert_close(out, ref, **tol(bf, 2))
+    out2, ref2, _ = run_attention(4, 2, 64, 16, [(0, 641)], bf, edit=edit, kernel="mma")
+    torch.testing.assert_close(out2, ref2, **tol(bf, 2))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
