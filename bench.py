@@ -97,22 +97,29 @@ def main() -> int:
         engine = Engine(model, num_pages=args.batch * (CONTEXT // PAGE + 1), page_size=PAGE,
                         max_requests=args.batch, max_tokens_per_step=4096)
         g = torch.Generator().manual_seed(3)
+        # prompts finish their prefill one step after the other: the first request decodes up to
+        # `batch` tokens before the last one starts, so everyone gets that many tokens more
+        budget = steps + warmup + args.batch + 2
         for i in range(args.batch):
-            prompt = torch.randint(0, vocab, (start_ctx,), generator=g).tolist()
-            engine.add_request(f"e{i}", prompt, max_new_tokens=steps + warmup + 1)
+            prompt = torch.randint(0, vocab, (CONTEXT - budget,), generator=g).tolist()
+            engine.add_request(f"e{i}", prompt, max_new_tokens=budget)
         while not all(r.decoding for r in engine.requests.values()):
             engine.step()                           # real prefill, untimed
         torch.cuda.synchronize()
         done = 0
+        stamps = []
         for i in range(warmup + steps):
             if i == warmup:
                 torch.cuda.synchronize()
                 t0 = time.perf_counter()
             n = len(engine.step())
+            stamps.append(time.perf_counter())
             if i >= warmup:
                 done += n
         torch.cuda.synchronize()
         sec = time.perf_counter() - t0
+        print("e2e step times (ms):", [round((b - a) * 1e3, 2) for a, b in zip(stamps, stamps[1:])],
+              file=sys.stderr)
         # per step: the packed index arrays go up from pinned memory, the sampled ids come down
         words = engine.runner.graphs[next(iter(engine.runner.graphs))].layout.total if engine.runner.graphs else 0
         e2e = {"value": done / sec, "unit": "tokens/s", "h2d_bytes_per_step": words * 4,

@@ -13,7 +13,7 @@
 //   ROWS = 16 (decode tokens, tiny portions): the four warps share the 16 rows and each takes
 //     16 of the 64 keys of a tile; their partial results are merged at the end.
 // Keys and values arrive in tiles of 64 by cp.async (16-byte chunks gathered through the block
-// table, double-buffered); rows are padded by 16 bytes, which keeps ldmatrix conflict-free for
+// table, two or three stages deep); rows are padded by 16 bytes, which keeps ldmatrix conflict-free for
 // every head size that is a multiple of 16.  Products are mma.sync m16n8k16: the score tile
 // feeds the value product straight from registers.
 #include "common.cuh"
@@ -73,7 +73,9 @@ struct Layout {
     static constexpr int Q_BYTES = ROWS * LD * 2;
     static constexpr int KV_BYTES = KT * LD * 2;            // one of K or V, one stage
     static constexpr int MERGE_BYTES = ROWS == 16 ? WARPS * 16 * (D + 2) * 4 : 0;
-    static constexpr int LOOP_BYTES = Q_BYTES + 4 * KV_BYTES;
+    // decode tiles are bound by memory latency: three stages keep two tiles in flight per CTA
+    static constexpr int STAGES = ROWS == 16 ? 3 : 2;
+    static constexpr int LOOP_BYTES = Q_BYTES + STAGES * 2 * KV_BYTES;
     static constexpr int TOTAL = LOOP_BYTES > MERGE_BYTES ? LOOP_BYTES : MERGE_BYTES;
 };
 
@@ -135,9 +137,13 @@ attention_mma_kernel(const AttnArgs a) {
         }
     };
 
+    constexpr int STAGES = L::STAGES;
     const int ntiles = (kv_end - kv_begin + KT - 1) / KT;
-    if (ntiles > 0) load_tile(0, kv_begin);
-    cp_async_commit();
+#pragma unroll
+    for (int st = 0; st < STAGES - 1; ++st) {
+        if (st < ntiles) load_tile(st, kv_begin + st * KT);
+        cp_async_commit();
+    }
 
     // ---- per-thread state: rows r0 = lane/4 and r0 + 8 of this warp's 16 rows ------------------
     const int wrow = SPLIT_KEYS ? 0 : warp * 16;
@@ -149,10 +155,11 @@ attention_mma_kernel(const AttnArgs a) {
     const float scale_log2 = a.scale * 1.4426950408889634f;
 
     for (int itile = 0; itile < ntiles; ++itile) {
-        const int stage = itile & 1;
-        if (itile + 1 < ntiles) load_tile(stage ^ 1, kv_begin + (itile + 1) * KT);
+        const int stage = itile % STAGES;
+        if (itile + STAGES - 1 < ntiles)
+            load_tile((itile + STAGES - 1) % STAGES, kv_begin + (itile + STAGES - 1) * KT);
         cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<STAGES - 1>();
         __syncthreads();
         if (itile == 0 && Q_IN_REGS) {
 #pragma unroll

@@ -82,6 +82,71 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const DT* __restrict__
     }
 }
 
+// The same with 4 elements per thread and the row kept in registers between the two passes
+// (rows of up to 4 * VEC_CACHE * blockDim elements; H % 4 == 0, 16-byte aligned rows).
+constexpr int VEC_CACHE = 4;
+
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *(const float4*)p; }
+template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+    const uint2 u = *(const uint2*)p;
+    const __nv_bfloat162 a = *(const __nv_bfloat162*)&u.x, b = *(const __nv_bfloat162*)&u.y;
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *(float4*)p = v; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *(const uint32_t*)&a;
+    u.y = *(const uint32_t*)&b;
+    *(uint2*)p = u;
+}
+
+template <typename DT, typename OT>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const DT* __restrict__ delta, int nsplit,
+                                       size_t split_stride, const float* __restrict__ weight, float eps,
+                                       const int* __restrict__ rows, OT* __restrict__ out, int H) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    float* xr = x + (size_t)s * H;
+    const bool write_back = (delta != nullptr) && (rows == nullptr);
+    const int nvec = H >> 2;
+    float4 v[VEC_CACHE];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < VEC_CACHE; ++c) {
+        const int i = threadIdx.x + c * blockDim.x;
+        if (i < nvec) {
+            float4 a = *(const float4*)(xr + 4 * i);
+            if (delta) {
+                for (int sp = 0; sp < nsplit; ++sp) {
+                    const float4 d = load4<DT>(delta + (size_t)sp * split_stride + (size_t)s * H + 4 * i);
+                    a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+                }
+                if (write_back) *(float4*)(xr + 4 * i) = a;
+            }
+            v[c] = a;
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        }
+    }
+    const float total = block_sum(ss, scratch);
+    const float rstd = rsqrtf(total / (float)H + eps);
+    OT* o = out + (size_t)r * H;
+#pragma unroll
+    for (int c = 0; c < VEC_CACHE; ++c) {
+        const int i = threadIdx.x + c * blockDim.x;
+        if (i < nvec) {
+            const float4 w = *(const float4*)(weight + 4 * i);
+            float4 a = v[c];
+            a.x = (a.x * rstd) * w.x; a.y = (a.y * rstd) * w.y;
+            a.z = (a.z * rstd) * w.z; a.w = (a.w * rstd) * w.w;
+            store4<OT>(o + 4 * i, a);
+        }
+    }
+}
+
 // Residual add alone (the last feed-forward's output when no norm follows on all rows).
 template <typename DT>
 __global__ void residual_add_kernel(float* __restrict__ x, const DT* __restrict__ delta, int nsplit,
@@ -96,6 +161,16 @@ MHB_EXPORT int mhb_add_rmsnorm(float* x, const void* delta, int delta_dtype, int
                                cudaStream_t stream) {
     if (R <= 0) return 0;
     if (nsplit > 1 && delta_dtype != MHB_F32) return fail("add_rmsnorm: split partials must be float32");
+    const bool aligned = H % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)weight & 15) == 0 &&
+                         ((uintptr_t)out & 15) == 0 && ((uintptr_t)delta & 15) == 0 && split_stride % 4 == 0;
+    int vthreads = ((H / 4 + VEC_CACHE - 1) / VEC_CACHE + 31) / 32 * 32;
+    if (vthreads < 64) vthreads = 64;
+    if (aligned && vthreads <= 1024) {
+        MHB_DISPATCH_DTYPE(delta_dtype, DT, MHB_DISPATCH_DTYPE(out_dtype, OT,
+            add_rmsnorm_vec_kernel<DT, OT><<<R, vthreads, 0, stream>>>(
+                x, (const DT*)delta, nsplit, (size_t)split_stride, weight, eps, rows, (OT*)out, H)));
+        return check_launch("add_rmsnorm");
+    }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     MHB_DISPATCH_DTYPE(delta_dtype, DT, MHB_DISPATCH_DTYPE(out_dtype, OT,
         add_rmsnorm_kernel<DT, OT><<<R, threads, 0, stream>>>(
@@ -130,15 +205,24 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, int nsplit, size_
                                    int table_width, const float* __restrict__ inv_freq,
                                    QT* __restrict__ q_out, CT* __restrict__ cache, int nq, int nkv,
                                    int d, int P, int num_pages, int write_kv, int rotate_q_k,
-                                   int* __restrict__ status) {
+                                   int heads_per_block, int* __restrict__ status) {
+    extern __shared__ float cs_table[];      // cos[d/2], sin[d/2] of this token's position
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int half = d >> 1;
     const int width = (nq + 2 * nkv) * d;
-    const IT* in = qkv;
     const size_t base = (size_t)t * width;
+    // heads are numbered q heads, then k heads, then v heads; this block takes a run of them
+    const int head_begin = blockIdx.y * heads_per_block;
+    const int head_end = min(nq + 2 * nkv, head_begin + heads_per_block);
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn = 0.f, cs = 1.f;
+        if (rotate_q_k) sincosf((float)pos * inv_freq[i], &sn, &cs);
+        cs_table[i] = cs;
+        cs_table[half + i] = sn;
+    }
     int page = -1;
-    if (write_kv) {
+    if (write_kv && head_end > nq) {
         page = block_table[(size_t)tok_seg[t] * table_width + pos / P];
         if (page < 0 || page >= num_pages) {  // never write outside the pool
             if (threadIdx.x == 0 && status) atomicOr(status, 2);
@@ -146,22 +230,18 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, int nsplit, size_
         }
     }
     const int within = pos % P;
+    __syncthreads();
     // q and k heads: one thread per (head, i < d/2) pair
-    const int pairs = (nq + nkv) * half;
-    for (int idx = threadIdx.x; idx < pairs; idx += blockDim.x) {
+    const int rot_end = min(head_end, nq + nkv);
+    for (int idx = head_begin * half + threadIdx.x; idx < rot_end * half; idx += blockDim.x) {
         const int head = idx / half, i = idx - head * half;
         const int col = head * d + i;
-        float a = load_split(in, base + col, nsplit, split_stride);
-        float b = load_split(in, base + col + half, nsplit, split_stride);
+        float a = load_split(qkv, base + col, nsplit, split_stride);
+        float b = load_split(qkv, base + col + half, nsplit, split_stride);
         if (bias) { a += bias[col]; b += bias[col + half]; }
-        float oa = a, ob = b;
-        if (rotate_q_k) {
-            const float angle = (float)pos * inv_freq[i];
-            float sn, cs;
-            sincosf(angle, &sn, &cs);
-            oa = a * cs - b * sn;
-            ob = b * cs + a * sn;
-        }
+        const float cs = cs_table[i], sn = cs_table[half + i];
+        const float oa = a * cs - b * sn;
+        const float ob = b * cs + a * sn;
         if (head < nq) {
             q_out[(size_t)t * nq * d + col] = from_float<QT>(oa);
             q_out[(size_t)t * nq * d + col + half] = from_float<QT>(ob);
@@ -173,11 +253,11 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, int nsplit, size_
         }
     }
     if (page >= 0) {
-        const int vbase = (nq + nkv) * d;
-        for (int idx = threadIdx.x; idx < nkv * d; idx += blockDim.x) {
-            const int kh = idx / d, e = idx - kh * d;
-            float v = load_split(in, base + vbase + idx, nsplit, split_stride);
-            if (bias) v += bias[vbase + idx];
+        const int v_begin = max(head_begin, nq + nkv);
+        for (int idx = v_begin * d + threadIdx.x; idx < head_end * d; idx += blockDim.x) {
+            const int kh = idx / d - (nq + nkv), e = idx % d;
+            float v = load_split(qkv, base + idx, nsplit, split_stride);
+            if (bias) v += bias[idx];
             cache[((((size_t)page * 2 + 1) * nkv + kh) * P + within) * d + e] = from_float<CT>(v);
         }
     }
@@ -192,12 +272,20 @@ MHB_EXPORT int mhb_rope_append(const void* qkv, int in_dtype, int nsplit, long l
     if (T <= 0) return 0;
     if (d % 2) return fail("rope_append: head_dim %d must be even", d);
     if (nsplit > 1 && in_dtype != MHB_F32) return fail("rope_append: split partials must be float32");
-    const int threads = 256;
+    const int threads = 128;
+    // few tokens: spread the heads of a token over several blocks so that the GPU is not idle
+    const int heads = nq + 2 * nkv;
+    int blocks_y = T >= 512 ? 1 : (512 + T - 1) / T;
+    if (blocks_y > heads) blocks_y = heads;
+    const int hpb = (heads + blocks_y - 1) / blocks_y;
+    blocks_y = (heads + hpb - 1) / hpb;
+    dim3 grid(T, blocks_y);
+    const size_t smem = sizeof(float) * d;
     MHB_DISPATCH_DTYPE(in_dtype, IT, MHB_DISPATCH_DTYPE(act_dtype, AT,
-        rope_append_kernel<IT, AT, AT><<<T, threads, 0, stream>>>(
+        rope_append_kernel<IT, AT, AT><<<grid, threads, smem, stream>>>(
             (const IT*)qkv, nsplit, (size_t)split_stride, bias, positions, tok_seg, block_table,
             table_width, inv_freq, (AT*)q_out, (AT*)cache, nq, nkv, d, P, num_pages, write_kv,
-            rotate, status)));
+            rotate, hpb, status)));
     return check_launch("rope_append");
 }
 
