@@ -5,7 +5,9 @@
 // s_t = (K[t] . q) * scale over the cached keys t <= the query's position (and inside the window,
 // if there is one), w = softmax(s), o = sum_t w_t V[t]; query head h reads KV head h / groups.
 // The work items are the same 8 ints {segment, first token, tokens, first head of the group,
-// heads, kv_begin, kv_end, split}; split >= 0 writes an un-normalised partial for combine.
+// heads, kv_begin, kv_end, split}; split >= 0 writes an un-normalised partial.  With a counter
+// array the CTA that finishes a token's last split merges all its splits (in split order, so the
+// result does not depend on which CTA comes last); without one, attention_combine does it.
 //
 // One CTA (4 warps) serves one item and one KV head.  The query heads of a KV group are stacked
 // into the row dimension of the tile, so a page of keys is read once for the whole group.
@@ -27,6 +29,7 @@ constexpr int KT = 64;          // keys per tile
 constexpr int WARPS = 4;
 constexpr int THREADS = WARPS * 32;
 constexpr int ITEM_INTS = 8;
+constexpr int MAX_MERGE_SPLITS = 64;   // most key splits of a token that the fused merge takes
 
 struct AttnArgs {
     const __nv_bfloat16* q;     // [T, nq, d]
@@ -38,6 +41,8 @@ struct AttnArgs {
     const int* positions;
     const int* block_table;
     const int* tok_part_row;
+    const int* tok_nsplit;      // splits of each token (used by the fused merge)
+    int* counters;              // one per (first token, KV head, head chunk): zero between launches
     int num_items, width, nq, nkv, P, num_pages, window;
     float scale;
 };
@@ -312,6 +317,53 @@ attention_mma_kernel(const AttnArgs a) {
                 }
             }
         }
+        if (split >= 0 && a.counters != nullptr) {
+            // the last CTA of this tile's splits merges them (reference/attention.py:11-20)
+            __shared__ int is_last;
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) {
+                const int chunks = (groups + 15) / 16;
+                int* counter = a.counters + ((size_t)tok0 * a.nkv + kvh) * chunks + head0 / 16;
+                const int ns = a.tok_nsplit[tok0];
+                const int prev = atomicAdd(counter, 1);
+                is_last = prev == ns - 1;
+                if (is_last) *counter = 0;
+            }
+            __syncthreads();
+            if (is_last) {
+                __threadfence();
+                // weights of every (row, split) once, then one load per split and output element
+                __shared__ float wgt_s[16][MAX_MERGE_SPLITS];
+                __shared__ float inv_s[16];
+                const int ns = min(a.tok_nsplit[tok0], MAX_MERGE_SPLITS);
+                if (tid < nrows) {
+                    const int t = tok0 + tid / nheads, hq = kvh * groups + head0 + tid % nheads;
+                    const size_t row0 = a.tok_part_row[t];
+                    float M = -INFINITY;
+                    for (int sp = 0; sp < ns; ++sp) M = fmaxf(M, __ldcg(a.part_ml + ((row0 + sp) * a.nq + hq) * 2));
+                    float lsum = 0.f;
+                    for (int sp = 0; sp < ns; ++sp) {
+                        const float ms = __ldcg(a.part_ml + ((row0 + sp) * a.nq + hq) * 2);
+                        const float w = ms > -INFINITY ? expf(ms - M) : 0.f;
+                        wgt_s[tid][sp] = w;
+                        lsum += w * __ldcg(a.part_ml + ((row0 + sp) * a.nq + hq) * 2 + 1);
+                    }
+                    inv_s[tid] = lsum > 0.f ? 1.f / lsum : 0.f;
+                }
+                __syncthreads();
+                for (int idx = tid; idx < nrows * D; idx += THREADS) {
+                    const int row = idx / D, e = idx - row * D;
+                    const int t = tok0 + row / nheads, hq = kvh * groups + head0 + row % nheads;
+                    const float* src = a.part_acc + ((size_t)a.tok_part_row[t] * a.nq + hq) * D + e;
+                    const size_t step = (size_t)a.nq * D;
+                    float acc = 0.f;
+#pragma unroll 4
+                    for (int sp = 0; sp < ns; ++sp) acc += wgt_s[row][sp] * __ldcg(src + sp * step);
+                    a.out[((size_t)t * a.nq + hq) * D + e] = __float2bfloat16_rn(acc * inv_s[row]);
+                }
+            }
+        }
     } else {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -372,14 +424,16 @@ int dispatch_d(int d, const AttnArgs& a, int launch_items, cudaStream_t stream) 
 MHB_EXPORT int mhb_attention_mma(const void* q, const void* cache, void* out, float* part_acc,
                                  float* part_ml, const int* items, int num_items, int launch_items,
                                  int rows, const int* positions, const int* block_table, int width,
-                                 const int* tok_part_row, int nq, int nkv, int d, int P, int num_pages,
-                                 int window, float scale, cudaStream_t stream) {
+                                 const int* tok_part_row, const int* tok_nsplit, int* counters, int nq,
+                                 int nkv, int d, int P, int num_pages, int window, float scale,
+                                 cudaStream_t stream) {
     if (launch_items <= 0) return 0;
     if (nkv <= 0 || nq % nkv) return fail("attention: %d query heads over %d KV heads", nq, nkv);
     AttnArgs a;
     a.q = (const __nv_bfloat16*)q; a.cache = (const __nv_bfloat16*)cache; a.out = (__nv_bfloat16*)out;
     a.part_acc = part_acc; a.part_ml = part_ml; a.items = items; a.positions = positions;
-    a.block_table = block_table; a.tok_part_row = tok_part_row; a.num_items = num_items; a.width = width;
+    a.block_table = block_table; a.tok_part_row = tok_part_row; a.tok_nsplit = tok_nsplit;
+    a.counters = counters; a.num_items = num_items; a.width = width;
     a.nq = nq; a.nkv = nkv; a.P = P; a.num_pages = num_pages; a.window = window; a.scale = scale;
     if (rows == 64) return dispatch_d<64>(d, a, launch_items, stream);
     if (rows == 16) return dispatch_d<16>(d, a, launch_items, stream);

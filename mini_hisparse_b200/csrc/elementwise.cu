@@ -121,8 +121,20 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const DT* __restri
         if (i < nvec) {
             float4 a = *(const float4*)(xr + 4 * i);
             if (delta) {
-                for (int sp = 0; sp < nsplit; ++sp) {
-                    const float4 d = load4<DT>(delta + (size_t)sp * split_stride + (size_t)s * H + 4 * i);
+                const DT* dp = delta + (size_t)s * H + 4 * i;
+                int sp = 0;
+                for (; sp + 4 <= nsplit; sp += 4) {      // four loads in flight; summed in order
+                    const float4 d0 = load4<DT>(dp + (size_t)(sp + 0) * split_stride);
+                    const float4 d1 = load4<DT>(dp + (size_t)(sp + 1) * split_stride);
+                    const float4 d2 = load4<DT>(dp + (size_t)(sp + 2) * split_stride);
+                    const float4 d3 = load4<DT>(dp + (size_t)(sp + 3) * split_stride);
+                    a.x += d0.x; a.y += d0.y; a.z += d0.z; a.w += d0.w;
+                    a.x += d1.x; a.y += d1.y; a.z += d1.z; a.w += d1.w;
+                    a.x += d2.x; a.y += d2.y; a.z += d2.z; a.w += d2.w;
+                    a.x += d3.x; a.y += d3.y; a.z += d3.z; a.w += d3.w;
+                }
+                for (; sp < nsplit; ++sp) {
+                    const float4 d = load4<DT>(dp + (size_t)sp * split_stride);
                     a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
                 }
                 if (write_back) *(float4*)(xr + 4 * i) = a;

@@ -124,7 +124,7 @@ template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat
 
 // C element of (a-row ra, b-row rb): TRANSPOSED ? C[rb, ra] : C[ra, rb]
 template <int BN, int STAGES, bool TRANSPOSED, typename OT>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, (Smem<BN, STAGES>::TOTAL <= 112 * 1024) ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                OT* __restrict__ C, int Ra, int Rb, int K, long long ldc, int kb_per_split,
                long long split_stride, int* __restrict__ status) {
@@ -329,9 +329,11 @@ template <bool TRANSPOSED, typename OT>
 int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* C, int Ra, int Rb, int K,
                 long long ldc, int nsplit, int kbps, long long ss, int* status, cudaStream_t st) {
     switch (bn) {
-        case 16: return launch<16, 8, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
-        case 32: return launch<32, 8, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
-        case 64: return launch<64, 8, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
+        // the narrow tiles stream weights: two CTAs per SM (<= 112 KB each) overlap one CTA's
+        // start-up and epilogue with the other's loads
+        case 16: return launch<16, 6, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
+        case 32: return launch<32, 5, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
+        case 64: return launch<64, 4, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
         case 128: return launch<128, 6, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
         case 256: return launch<256, 4, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
     }

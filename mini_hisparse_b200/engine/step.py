@@ -105,7 +105,8 @@ class _DecodeGraph:
     def __init__(self, runner: "ModelRunner", B: int, width: int):
         self.B = B
         self.ws = Workspace(runner.device)
-        self.nsplit = [runner.batch.decode_splits(g.need, B) for g in runner.cache.page_groups]
+        max_keys = width * runner.cache.cfg.page_size
+        self.nsplit = [runner.batch.decode_splits(g.need, B, max_keys) for g in runner.cache.page_groups]
         caps = []
         for g, ns in zip(runner.cache.page_groups, self.nsplit):
             groups = g.need.q_heads // g.need.kv_heads
@@ -132,14 +133,16 @@ class BatchBuilder:
         self.staging = _Staging()
 
     # ---- planning ----------------------------------------------------------------------------
-    def decode_splits(self, need: PagedKVNeed, B: int) -> int:
-        """Key splits per decoded token for a batch of B: enough CTAs for two waves."""
-        from ..parts.attention import MAX_SPLITS, ROW_TILE
+    def decode_splits(self, need: PagedKVNeed, B: int, max_keys: int) -> int:
+        """Key splits per decoded token for a batch of B with at most ``max_keys`` cached keys: as
+        many CTAs as are resident at once (two per SM), never more, so that no CTA waits for a
+        second wave, and no split shorter than MIN_KEYS_PER_SPLIT keys."""
+        from ..parts.attention import MAX_SPLITS, MIN_KEYS_PER_SPLIT, ROW_TILE
 
         groups = need.q_heads // need.kv_heads
         chunks = 1 if groups <= ROW_TILE else -(-groups // ROW_TILE)
         ctas = B * need.kv_heads * chunks
-        return max(1, min(MAX_SPLITS, -(-2 * self.sm_count // ctas)))
+        return max(1, min(MAX_SPLITS, (2 * self.sm_count) // ctas, max_keys // MIN_KEYS_PER_SPLIT))
 
     def segments(self, entries: list[StepEntry]) -> tuple[list[Segment], int]:
         segments, offset = [], 0

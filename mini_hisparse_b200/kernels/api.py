@@ -175,8 +175,12 @@ MMA_HEAD_DIMS = (32, 64, 96, 128)   # head sizes the tensor-core attention kerne
 
 
 def attention_mma(q, cache, out, part_acc, part_ml, items, num_items, rows, positions, block_table,
-                  tok_part_row, *, nq, nkv, d, page_size, window=0, scale=None):
-    """Tensor-core attention (bfloat16) over ``num_items`` items planned for tiles of ``rows`` rows."""
+                  tok_part_row, *, nq, nkv, d, page_size, window=0, scale=None, tok_nsplit=None,
+                  counters=None):
+    """Tensor-core attention (bfloat16) over ``num_items`` items planned for tiles of ``rows`` rows.
+
+    With ``counters`` (int32, zero, one per (token, KV head, chunk of 16 group heads)) the kernel
+    merges the key splits itself and leaves the counters zero; else call attention_combine."""
     lib = build.load("attention_mma")
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("attention_mma: q and the cache must be bfloat16")
@@ -185,8 +189,9 @@ def attention_mma(q, cache, out, part_acc, part_ml, items, num_items, rows, posi
     _check(lib, lib.mhb_attention_mma(
         _ptr(q), _ptr(cache), _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(items), c_int(num_items),
         c_int(num_items), c_int(rows), _ptr(positions), _ptr(block_table), c_int(block_table.shape[-1]),
-        _ptr(tok_part_row), c_int(nq), c_int(nkv), c_int(d), c_int(page_size), c_int(cache.shape[0]),
-        c_int(window or 0), c_float(scale), _stream()), "attention_mma")
+        _ptr(tok_part_row), _ptr(tok_nsplit), _ptr(counters), c_int(nq), c_int(nkv), c_int(d),
+        c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_float(scale), _stream()),
+        "attention_mma")
 
 
 def attention_combine(part_acc, part_ml, tok_part_row, tok_nsplit, out, *, nq, d):

@@ -33,10 +33,9 @@ class BFloat16Runtime(Runtime):
 
     def _splits(self, tiles: int, total_kb: int) -> int:
         """Enough K splits for about two CTAs per SM, none empty, none shorter than 4 K blocks."""
-        if tiles >= self.sm_count or total_kb < 2 * MIN_KB_PER_SPLIT:
+        want = min((2 * self.sm_count) // max(tiles, 1), total_kb // MIN_KB_PER_SPLIT)
+        if want <= 1:
             return 1
-        want = max(1, (2 * self.sm_count) // tiles)
-        want = min(want, total_kb // MIN_KB_PER_SPLIT)
         kb_per = -(-total_kb // want)
         return -(-total_kb // kb_per)
 

@@ -80,7 +80,7 @@ def plan_attention(need: PagedKVNeed, segments, T: int, sm_count: int = 148,
         if fixed_nsplit is not None:
             nsplit = fixed_nsplit
         elif base_ctas < 2 * sm_count:
-            want = -(-2 * sm_count // max(base_ctas, 1))
+            want = (2 * sm_count) // max(base_ctas, 1)
             fit = max(1, (kv_end - kv_begin) // MIN_KEYS_PER_SPLIT)
             nsplit = max(1, min(want, fit, MAX_SPLITS))
         if nsplit == 1:
@@ -199,12 +199,15 @@ class GQAttention(Mixer):
         n_small, n_big = meta["n_small"], meta["n_big"]
         if self.tensor_core_attention:
             if n_small:
-                K.attention_mma(*args, meta["items"], n_small, 16, *tail, **common)
+                chunks = -(-(self.nq // self.nkv) // ROW_TILE)
+                counters = ws.get_zeroed("attn_counters", (T * self.nkv * chunks,), torch.int32)
+                K.attention_mma(*args, meta["items"], n_small, 16, *tail, **common,
+                                tok_nsplit=meta["tok_nsplit"], counters=counters)
             if n_big:
                 K.attention_mma(*args, meta["items"][n_small * ITEM_INTS:], n_big, 64, *tail, **common)
         elif n_small + n_big:
             K.attention_simt(*args, meta["items"], n_small + n_big, n_small + n_big, *tail, **common)
-        if meta["any_split"]:
+        if meta["any_split"] and not self.tensor_core_attention:
             K.attention_combine(part_acc, part_ml, meta["tok_part_row"], meta["tok_nsplit"], attn,
                                 nq=self.nq, d=self.d)
         return rt.linear(attn, self.o_weight, ws, "mix_out")

@@ -73,6 +73,18 @@ class Workspace:
             self._buffers[name] = buf
         return buf[:nbytes].view(dtype).view(*shape)
 
+    def get_zeroed(self, name: str, shape, dtype) -> torch.Tensor:
+        """A buffer that is zero when first handed out; its users leave it zero."""
+        n = 1
+        for s in shape:
+            n *= int(s)
+        buf = self._buffers.get(name)
+        if buf is None or buf.numel() < n * dtype.itemsize:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer {name!r} would grow after it was frozen")
+            self._buffers[name] = torch.zeros(max(n * dtype.itemsize, 256), dtype=torch.uint8, device=self.device)
+        return self.get(name, shape, dtype)
+
     def nbytes(self) -> int:
         return sum(b.numel() for b in self._buffers.values())
 

@@ -285,15 +285,21 @@ def run_attention(nq, nkv, d, P_, seg_specs, dtype, window=None, fixed_nsplit=No
     tns = torch.from_numpy(plan.tok_nsplit).to(DEV)
     n_items = plan.items.shape[0]
     kw = dict(nq=nq, nkv=nkv, d=d, page_size=P_, window=window or 0)
+    fused = kernel == "mma" and seed % 2 == 0     # the kernel merges its own key splits
     if kernel == "mma":
         if plan.n_small:
-            K().attention_mma(q, cache, out, part_acc, part_ml, items, plan.n_small, 16, positions, table, tpr, **kw)
+            groups = nq // nkv
+            counters = torch.zeros(T * nkv * -(-groups // 16), dtype=torch.int32, device=DEV) if fused else None
+            K().attention_mma(q, cache, out, part_acc, part_ml, items, plan.n_small, 16, positions, table, tpr,
+                              tok_nsplit=tns, counters=counters, **kw)
+            if fused:
+                assert int(counters.abs().sum()) == 0        # left zero for the next launch
         if plan.n_big:
             K().attention_mma(q, cache, out, part_acc, part_ml, items[plan.n_small * ITEM_INTS:], plan.n_big, 64,
                               positions, table, tpr, **kw)
     else:
         K().attention_simt(q, cache, out, part_acc, part_ml, items, n_items, n_items, positions, table, tpr, **kw)
-    if plan.part_rows:
+    if plan.part_rows and not fused:
         K().attention_combine(part_acc, part_ml, tpr, tns, out, nq=nq, d=d)
     ref = torch.cat([
         P.causal_attention(qq.float(), kk.float(), vv.float(), window=window)[h:]
@@ -315,9 +321,13 @@ def test_attention_tensor_core_portions_and_decode_mixed(nq, nkv, d, P_):
 
 def test_attention_tensor_core_splits_window_and_far_key():
     bf = torch.bfloat16
-    out, ref, plan = run_attention(28, 4, 128, 16, [(700, 1), (33, 1), (1023, 1), (0, 1)], bf, fixed_nsplit=5, kernel="mma")
-    assert plan.part_rows == 20
-    torch.testing.assert_close(out, ref, **tol(bf, 2))
+    for seed in (0, 1):      # merged inside the kernel, and by attention_combine
+        out, ref, plan = run_attention(28, 4, 128, 16, [(700, 1), (33, 1), (1023, 1), (0, 1), (300, 2)], bf,
+                                       fixed_nsplit=5, kernel="mma", seed=seed)
+        assert plan.part_rows == 30
+        torch.testing.assert_close(out, ref, **tol(bf, 2))
+    out, ref, plan = run_attention(40, 2, 64, 16, [(500, 1), (90, 3)], bf, fixed_nsplit=3, kernel="mma")
+    torch.testing.assert_close(out, ref, **tol(bf, 2))          # groups of 20 heads: two chunks per token
     out, ref, plan = run_attention(8, 2, 64, 16, [(2000, 1)], bf, kernel="mma")
     assert plan.part_rows > 1
     torch.testing.assert_close(out, ref, **tol(bf, 2))
