@@ -97,6 +97,8 @@ attention_mma_kernel(const AttnArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     __shared__ int row_pos[ROWS];
 
+    pdl_launch_dependents();
+    pdl_wait();
     if ((int)blockIdx.x >= a.num_items) return;
     const int* it = a.items + (size_t)blockIdx.x * ITEM_INTS;
     const int seg = it[0], tok0 = it[1], ntok = it[2], head0 = it[3], nheads = it[4];
@@ -404,7 +406,7 @@ int launch(const AttnArgs& a, int launch_items, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid(launch_items, a.nkv);
-    kern<<<grid, THREADS, smem, stream>>>(a);
+    launch_kernel(kern, grid, dim3(THREADS), smem, stream, a);
     return check_launch("attention_mma");
 }
 

@@ -50,6 +50,8 @@ attention_simt_kernel(const AttnArgs a) {
     float* v_s = k_s + KT * (d + 1);         // [KT][d]
     __shared__ int row_pos[R_TILE];
 
+    pdl_launch_dependents();
+    pdl_wait();
     if ((int)blockIdx.x >= a.num_items) return;
     const int* it = a.items + (size_t)blockIdx.x * ITEM_INTS;
     const int seg = it[0], tok0 = it[1], ntok = it[2], head0 = it[3], nheads = it[4];
@@ -183,6 +185,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
                                          const int* __restrict__ tok_part_row,
                                          const int* __restrict__ tok_nsplit, OT* __restrict__ out,
                                          int nq, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y;
     const int ns = tok_nsplit[t];
     if (ns <= 0) return;  // written directly by the attention kernel
@@ -221,7 +225,7 @@ int launch_attention(const AttnArgs& a, int max_items, cudaStream_t stream) {
             if (e != cudaSuccess) return fail("attention: shared memory %zu: %s", smem,        \
                                               cudaGetErrorString(e));                           \
         }                                                                                       \
-        kern<<<grid, WARPS * 32, smem, stream>>>(a);                                            \
+        launch_kernel(kern, grid, dim3(WARPS * 32), smem, stream, a);                           \
         break;                                                                                  \
     }
     switch (dpl) {
@@ -258,7 +262,7 @@ MHB_EXPORT int mhb_attention_combine(const float* part_acc, const float* part_ml
     dim3 grid(T, nq);
     const int threads = d >= 128 ? 128 : 32 * ((d + 31) / 32);
     MHB_DISPATCH_DTYPE(dtype, OT,
-        attention_combine_kernel<OT><<<grid, threads, 0, stream>>>(part_acc, part_ml, tok_part_row,
-                                                                    tok_nsplit, (OT*)out, nq, d));
+        launch_kernel(attention_combine_kernel<OT>, grid, dim3(threads), 0, stream, part_acc, part_ml,
+                      tok_part_row, tok_nsplit, (OT*)out, nq, d));
     return check_launch("attention_combine");
 }

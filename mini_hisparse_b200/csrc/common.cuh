@@ -10,6 +10,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <string.h>
+#include <stdlib.h>
 
 #define MHB_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -76,6 +77,44 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return scratch[32];
 }
 
+}  // namespace mhb
+
+// ---- programmatic dependent launch -----------------------------------------------------------
+// Every kernel of the step is launched with the programmatic-stream-serialization attribute and
+// begins with pdl_launch_dependents(); pdl_wait().  The first lets the NEXT kernel's CTAs start as
+// soon as SM resources allow (its start-up, and in the matrix products the first weight tiles,
+// overlap this kernel's tail); the second holds this kernel until its predecessor has completed
+// and its writes are visible.  Before pdl_wait() a kernel touches constant data only (weights,
+// tensor maps).  Since every kernel waits for its predecessor, completion stays in stream order.
+// MHB_PDL=0 in the environment switches the attribute off (then both calls are no-ops).
+namespace mhb {
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("MHB_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
 }  // namespace mhb
 
 // Dispatch on a runtime dtype code: CALL is a statement that uses the type name T.

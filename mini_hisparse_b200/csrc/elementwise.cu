@@ -27,6 +27,8 @@ __device__ __forceinline__ float load_split(const T* p, size_t idx, int nsplit, 
 template <typename WT>
 __global__ void embed_kernel(const WT* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int H, int V, int* __restrict__ status) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int tok = tokens[t];
     float* o = out + (size_t)t * H;
@@ -44,7 +46,7 @@ MHB_EXPORT int mhb_embed(const void* table, int table_dtype, const int* tokens, 
     if (T <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
     MHB_DISPATCH_DTYPE(table_dtype, WT,
-        embed_kernel<WT><<<T, threads, 0, stream>>>((const WT*)table, tokens, out, H, V, status));
+        launch_kernel(embed_kernel<WT>, dim3(T), dim3(threads), 0, stream, (const WT*)table, tokens, out, H, V, status));
     return check_launch("embed");
 }
 
@@ -58,6 +60,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const DT* __restrict__
                                    float eps, const int* __restrict__ rows, OT* __restrict__ out,
                                    int H) {
     __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
     float* xr = x + (size_t)s * H;
@@ -108,6 +112,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const DT* __restri
                                        size_t split_stride, const float* __restrict__ weight, float eps,
                                        const int* __restrict__ rows, OT* __restrict__ out, int H) {
     __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
     float* xr = x + (size_t)s * H;
@@ -163,6 +169,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const DT* __restri
 template <typename DT>
 __global__ void residual_add_kernel(float* __restrict__ x, const DT* __restrict__ delta, int nsplit,
                                     size_t split_stride, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) x[i] += load_split(delta, i, nsplit, split_stride);
 }
@@ -179,13 +187,13 @@ MHB_EXPORT int mhb_add_rmsnorm(float* x, const void* delta, int delta_dtype, int
     if (vthreads < 64) vthreads = 64;
     if (aligned && vthreads <= 1024) {
         MHB_DISPATCH_DTYPE(delta_dtype, DT, MHB_DISPATCH_DTYPE(out_dtype, OT,
-            add_rmsnorm_vec_kernel<DT, OT><<<R, vthreads, 0, stream>>>(
+            launch_kernel(add_rmsnorm_vec_kernel<DT, OT>, dim3(R), dim3(vthreads), 0, stream, 
                 x, (const DT*)delta, nsplit, (size_t)split_stride, weight, eps, rows, (OT*)out, H)));
         return check_launch("add_rmsnorm");
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     MHB_DISPATCH_DTYPE(delta_dtype, DT, MHB_DISPATCH_DTYPE(out_dtype, OT,
-        add_rmsnorm_kernel<DT, OT><<<R, threads, 0, stream>>>(
+        launch_kernel(add_rmsnorm_kernel<DT, OT>, dim3(R), dim3(threads), 0, stream, 
             x, (const DT*)delta, nsplit, (size_t)split_stride, weight, eps, rows, (OT*)out, H)));
     return check_launch("add_rmsnorm");
 }
@@ -197,7 +205,7 @@ MHB_EXPORT int mhb_residual_add(float* x, const void* delta, int delta_dtype, in
     const int threads = 256;
     const unsigned blocks = (unsigned)((n + threads - 1) / threads);
     MHB_DISPATCH_DTYPE(delta_dtype, DT,
-        residual_add_kernel<DT><<<blocks, threads, 0, stream>>>(x, (const DT*)delta, nsplit,
+        launch_kernel(residual_add_kernel<DT>, dim3(blocks), dim3(threads), 0, stream, x, (const DT*)delta, nsplit,
                                                                  (size_t)split_stride, (size_t)n));
     return check_launch("residual_add");
 }
@@ -219,6 +227,8 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, int nsplit, size_
                                    int d, int P, int num_pages, int write_kv, int rotate_q_k,
                                    int heads_per_block, int* __restrict__ status) {
     extern __shared__ float cs_table[];      // cos[d/2], sin[d/2] of this token's position
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int half = d >> 1;
@@ -294,7 +304,7 @@ MHB_EXPORT int mhb_rope_append(const void* qkv, int in_dtype, int nsplit, long l
     dim3 grid(T, blocks_y);
     const size_t smem = sizeof(float) * d;
     MHB_DISPATCH_DTYPE(in_dtype, IT, MHB_DISPATCH_DTYPE(act_dtype, AT,
-        rope_append_kernel<IT, AT, AT><<<grid, threads, smem, stream>>>(
+        launch_kernel(rope_append_kernel<IT, AT, AT>, dim3(grid), dim3(threads), smem, stream, 
             (const IT*)qkv, nsplit, (size_t)split_stride, bias, positions, tok_seg, block_table,
             table_width, inv_freq, (AT*)q_out, (AT*)cache, nq, nkv, d, P, num_pages, write_kv,
             rotate, hpb, status)));
@@ -306,6 +316,8 @@ MHB_EXPORT int mhb_rope_append(const void* qkv, int in_dtype, int nsplit, long l
 template <typename IT, typename OT>
 __global__ void swiglu_kernel(const IT* __restrict__ gu, int nsplit, size_t split_stride,
                               OT* __restrict__ out, int I, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / I;
@@ -324,7 +336,7 @@ MHB_EXPORT int mhb_swiglu(const void* gu, int in_dtype, int nsplit, long long sp
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     MHB_DISPATCH_DTYPE(in_dtype, IT, MHB_DISPATCH_DTYPE(out_dtype, OT,
-        swiglu_kernel<IT, OT><<<blocks, threads, 0, stream>>>((const IT*)gu, nsplit,
+        launch_kernel(swiglu_kernel<IT, OT>, dim3(blocks), dim3(threads), 0, stream, (const IT*)gu, nsplit,
                                                             (size_t)split_stride, (OT*)out, I, total)));
     return check_launch("swiglu");
 }

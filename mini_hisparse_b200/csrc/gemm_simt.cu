@@ -23,6 +23,8 @@ gemm_simt_kernel(const AT* __restrict__ A, const WT* __restrict__ W, OT* __restr
                  long long ldc, int k_per_split, long long split_stride) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int k_begin = blockIdx.z * k_per_split;
@@ -89,8 +91,8 @@ MHB_EXPORT int mhb_gemm_simt(const void* A, int a_dtype, const void* W, int w_dt
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, nsplit);
     if (grid.y > 65535) return fail("gemm: M %d too large for one launch", M);
     MHB_DISPATCH_DTYPE(a_dtype, AT, MHB_DISPATCH_DTYPE(w_dtype, WT, MHB_DISPATCH_DTYPE(c_dtype, OT,
-        gemm_simt_kernel<AT, WT, OT><<<grid, THREADS, 0, stream>>>(
+        launch_kernel(gemm_simt_kernel<AT, WT, OT>, grid, dim3(THREADS), 0, stream,
             (const AT*)A, (const WT*)W, (OT*)C, bias, M, N, K, lda, ldw, ldc, k_per_split,
-            split_stride))));
+            (long long)split_stride))));
     return check_launch("gemm_simt");
 }

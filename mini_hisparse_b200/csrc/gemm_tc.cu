@@ -127,7 +127,7 @@ template <int BN, int STAGES, bool TRANSPOSED, typename OT>
 __global__ void __launch_bounds__(THREADS, (Smem<BN, STAGES>::TOTAL <= 112 * 1024) ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                OT* __restrict__ C, int Ra, int Rb, int K, long long ldc, int kb_per_split,
-               long long split_stride, int* __restrict__ status) {
+               long long split_stride, int constant_operand, int* __restrict__ status) {
     using S = Smem<BN, STAGES>;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
     extern __shared__ uint8_t smem_raw[];
@@ -146,6 +146,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int kb_end = min(total_kb, kb_begin + kb_per_split);
     const int num_kb = max(0, kb_end - kb_begin);
 
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         mbar_init(tmem_full_bar, 1);
@@ -164,7 +165,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
             int issued = 0;
-            for (int i = 0; i < num_kb && ok; ++i) {
+            // The operand that holds weights does not depend on the kernel before this one: its
+            // tiles of the first STAGES K blocks are requested before waiting for that kernel.
+            const int early = constant_operand ? min(num_kb, STAGES) : 0;
+            for (int i = 0; i < early; ++i) {
+                mbar_expect_tx(full_bar(i), S::STAGE_BYTES);
+                const uint32_t a_dst = smem_base + i * S::STAGE_BYTES;
+                if (constant_operand == 1) tma_load_2d(a_dst, &map_a, (kb_begin + i) * BK, ra0, full_bar(i));
+                else tma_load_2d(a_dst + S::A_BYTES, &map_b, (kb_begin + i) * BK, rb0, full_bar(i));
+                issued = i + 1;
+            }
+            pdl_wait();
+            for (int i = 0; i < early; ++i) {
+                const uint32_t a_dst = smem_base + i * S::STAGE_BYTES;
+                if (constant_operand == 1) tma_load_2d(a_dst + S::A_BYTES, &map_b, (kb_begin + i) * BK, rb0, full_bar(i));
+                else tma_load_2d(a_dst, &map_a, (kb_begin + i) * BK, ra0, full_bar(i));
+            }
+            for (int i = early; i < num_kb && ok; ++i) {
                 const int s = i % STAGES;
                 const uint32_t phase = (i / STAGES) & 1;
                 ok = mbar_wait(empty_bar(s), phase ^ 1);
@@ -207,6 +224,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int quarter = warp & 3;
         const int ra = ra0 + quarter * 32 + lane;
         if (num_kb > 0) ok = mbar_wait(tmem_full_bar, 0);
+        else pdl_wait();       // nothing was loaded: still do not write before the previous kernel is done
         tc_fence_after();
         OT* Cz = C + (size_t)blockIdx.z * split_stride;
         if (ok) {
@@ -311,7 +329,8 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, lon
 
 template <int BN, int STAGES, bool TRANSPOSED, typename OT>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int Ra, int Rb, int K, long long ldc,
-           int nsplit, int kb_per_split, long long split_stride, int* status, cudaStream_t stream) {
+           int nsplit, int kb_per_split, long long split_stride, int constant_operand, int* status,
+           cudaStream_t stream) {
     auto kern = gemm_tc_kernel<BN, STAGES, TRANSPOSED, OT>;
     constexpr int smem = Smem<BN, STAGES>::TOTAL;
     static bool configured = false;
@@ -321,21 +340,22 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int Ra, int Rb
         configured = true;
     }
     dim3 grid((Ra + BM - 1) / BM, (Rb + BN - 1) / BN, nsplit);
-    kern<<<grid, THREADS, smem, stream>>>(ma, mb, (OT*)C, Ra, Rb, K, ldc, kb_per_split, split_stride, status);
+    launch_kernel(kern, grid, dim3(THREADS), smem, stream, ma, mb, (OT*)C, Ra, Rb, K, ldc, kb_per_split,
+                  split_stride, constant_operand, status);
     return check_launch("gemm_tc");
 }
 
 template <bool TRANSPOSED, typename OT>
 int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* C, int Ra, int Rb, int K,
-                long long ldc, int nsplit, int kbps, long long ss, int* status, cudaStream_t st) {
+                long long ldc, int nsplit, int kbps, long long ss, int co, int* status, cudaStream_t st) {
     switch (bn) {
         // the narrow tiles stream weights: two CTAs per SM (<= 112 KB each) overlap one CTA's
         // start-up and epilogue with the other's loads
-        case 16: return launch<16, 6, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
-        case 32: return launch<32, 5, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
-        case 64: return launch<64, 4, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
-        case 128: return launch<128, 6, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
-        case 256: return launch<256, 4, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, status, st);
+        case 16: return launch<16, 6, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
+        case 32: return launch<32, 5, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
+        case 64: return launch<64, 4, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
+        case 128: return launch<128, 6, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
+        case 256: return launch<256, 4, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
     }
     return fail("gemm_tc: no tile for BN %d", bn);
 }
@@ -362,11 +382,11 @@ MHB_EXPORT int mhb_gemm_tc(const void* X, const void* W, void* C, int c_dtype, i
     if (swap) {
         if ((rc = make_map(&ma, W, N, K, ldw, BM))) return rc;
         if ((rc = make_map(&mb, X, M, K, lda, bn))) return rc;
-        if (c_dtype == MHB_F32) return dispatch_bn<true, float>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, status, stream);
-        return dispatch_bn<true, __nv_bfloat16>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, status, stream);
+        if (c_dtype == MHB_F32) return dispatch_bn<true, float>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
+        return dispatch_bn<true, __nv_bfloat16>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
     }
     if ((rc = make_map(&ma, X, M, K, lda, BM))) return rc;
     if ((rc = make_map(&mb, W, N, K, ldw, bn))) return rc;
-    if (c_dtype == MHB_F32) return dispatch_bn<false, float>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, status, stream);
-    return dispatch_bn<false, __nv_bfloat16>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, status, stream);
+    if (c_dtype == MHB_F32) return dispatch_bn<false, float>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
+    return dispatch_bn<false, __nv_bfloat16>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
 }

@@ -31,6 +31,8 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V,
     __shared__ int s_idx[THREADS];
     __shared__ float s_scan[THREADS + 1];
     __shared__ int s_result;
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (size_t)r * ld;
     // contiguous chunk per thread, so that prefix sums follow the index order
@@ -103,6 +105,6 @@ MHB_EXPORT int mhb_sample(const float* logits, long long ld, int R, int V, const
                           cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0) return fail("sample: empty vocabulary");
-    sample_kernel<<<R, THREADS, 0, stream>>>(logits, ld, V, temperature, seed, counter, out);
+    launch_kernel(sample_kernel, dim3(R), dim3(THREADS), 0, stream, logits, ld, V, temperature, seed, counter, out);
     return check_launch("sample");
 }

@@ -121,6 +121,12 @@ def compile_module(module: str, verbose: bool = True) -> Path:
             pass
         raise KernelBuildError(f"nvcc failed on {src.name}:\n{output}")
     os.replace(tmp, out)
+    for stale in out.parent.glob(f"libmhb_{module}_*.so"):     # older builds of this module
+        if stale != out:
+            try:
+                stale.unlink()
+            except OSError:
+                pass
     if verbose:
         _say(f"built {out.name} in {time.time() - start:.1f} s")
     return out
