@@ -22,13 +22,8 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# BASELINE.json configs[2]: Qwen2.5-7B shape
-CONFIG_7B = dict(
-    architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=152064, hidden_size=3584,
-    intermediate_size=18944, num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4,
-    rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False,
-    max_position_embeddings=32768, hidden_act="silu", use_sliding_window=False,
-)
+# BASELINE.json configs[2]: Qwen2.5-7B shape, kept as data beside the package
+CONFIG_7B = json.loads((ROOT / "mini_hisparse_b200" / "configs" / "qwen2.5-7b-shape.json").read_text())
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 PAGE = 16

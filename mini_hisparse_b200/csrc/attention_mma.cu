@@ -44,6 +44,7 @@ struct AttnArgs {
     const int* tok_nsplit;      // splits of each token (used by the fused merge)
     int* counters;              // one per (first token, KV head, head chunk): zero between launches
     int num_items, width, nq, nkv, P, num_pages, window;
+    int page_shift;             // log2(P) if P is a power of two, else -1
     float scale;
 };
 
@@ -122,25 +123,29 @@ attention_mma_kernel(const AttnArgs a) {
     }
     if (tid < ROWS) row_pos[tid] = tid < nrows ? a.positions[tok0 + tid / nheads] : -1;
 
-    // two threads per key row, each copies half of the row's 16-byte chunks
+    // Consecutive threads copy consecutive 16-byte chunks of a key row, so a warp's request covers
+    // whole rows (full 32-byte sectors).  A thread meets KT * (D/8) / THREADS rows per tile.
     auto load_tile = [&](int stage, int t0) {
-        const int j = tid >> 1, half = tid & 1;
-        const int kp = t0 + j;
-        int page = -1;
-        if (kp < kv_end) {
-            page = table[kp / a.P];
-            if (page >= a.num_pages) page = -1;
-        }
-        const __nv_bfloat16* src = a.cache;
-        if (page >= 0) src += (((size_t)page * 2) * a.nkv + kvh) * a.P * D + (size_t)(kp % a.P) * D;
-        const int bytes = page >= 0 ? 16 : 0;
-        const uint32_t kdst = kv_s + stage * 2 * L::KV_BYTES + j * LD * 2;
-        const uint32_t vdst = kdst + L::KV_BYTES;
+        constexpr int CPR = D / 8;                         // chunks per row
+        constexpr int ITERS = KT * CPR / THREADS;
+        const uint32_t kbase = kv_s + stage * 2 * L::KV_BYTES;
 #pragma unroll
-        for (int i = 0; i < D / 16; ++i) {
-            const int ch = half * (D / 16) + i;
-            cp_async16(kdst + ch * 16, src + ch * 8, bytes);
-            cp_async16(vdst + ch * 16, src + (page >= 0 ? plane : 0) + ch * 8, bytes);
+        for (int i = 0; i < ITERS; ++i) {
+            const int c = i * THREADS + tid;
+            const int j = c / CPR, ch = c % CPR;
+            const int kp = t0 + j;
+            int page = -1;
+            if (kp < kv_end) {
+                page = table[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.P)];
+                if (page >= a.num_pages) page = -1;
+            }
+            const int within = a.page_shift >= 0 ? (kp & (a.P - 1)) : (kp % a.P);
+            const __nv_bfloat16* src = a.cache;
+            if (page >= 0) src += (((size_t)page * 2) * a.nkv + kvh) * a.P * D + (size_t)within * D + ch * 8;
+            const int bytes = page >= 0 ? 16 : 0;
+            const uint32_t kdst = kbase + (j * LD + ch * 8) * 2;
+            cp_async16(kdst, src, bytes);
+            cp_async16(kdst + L::KV_BYTES, src + (page >= 0 ? plane : 0), bytes);
         }
     };
 
@@ -437,6 +442,8 @@ MHB_EXPORT int mhb_attention_mma(const void* q, const void* cache, void* out, fl
     a.block_table = block_table; a.tok_part_row = tok_part_row; a.tok_nsplit = tok_nsplit;
     a.counters = counters; a.num_items = num_items; a.width = width;
     a.nq = nq; a.nkv = nkv; a.P = P; a.num_pages = num_pages; a.window = window; a.scale = scale;
+    a.page_shift = -1;
+    if (P > 0 && (P & (P - 1)) == 0) { a.page_shift = 0; while ((1 << a.page_shift) < P) ++a.page_shift; }
     if (rows == 64) return dispatch_d<64>(d, a, launch_items, stream);
     if (rows == 16) return dispatch_d<16>(d, a, launch_items, stream);
     return fail("attention_mma: tile height %d", rows);
