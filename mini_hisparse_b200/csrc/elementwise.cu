@@ -312,31 +312,35 @@ MHB_EXPORT int mhb_rope_append(const void* qkv, int in_dtype, int nsplit, long l
 }
 
 // ---- SwiGLU gate ------------------------------------------------------------------------------
-// gu[t] = [gate (I) | up (I)]  ->  out[t, i] = silu(gate_i) * up_i   (mini_hisparse/model.py:70-71)
+// out[t, i] = silu(gate_i) * up_i   (mini_hisparse/model.py:70-71).  gu[t] holds 2 I values in
+// blocks: `block` gate values, then the `block` up values of the same indices (block = I is the
+// plain [gate | up] layout).
 template <typename IT, typename OT>
 __global__ void swiglu_kernel(const IT* __restrict__ gu, int nsplit, size_t split_stride,
-                              OT* __restrict__ out, int I, size_t total) {
+                              OT* __restrict__ out, int I, int block, size_t total) {
     pdl_launch_dependents();
     pdl_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / I;
     const int i = (int)(idx - t * I);
-    const float g = load_split(gu, t * 2 * I + i, nsplit, split_stride);
-    const float u = load_split(gu, t * 2 * I + I + i, nsplit, split_stride);
+    const int gcol = (i / block) * 2 * block + i % block;
+    const float g = load_split(gu, t * 2 * I + gcol, nsplit, split_stride);
+    const float u = load_split(gu, t * 2 * I + gcol + block, nsplit, split_stride);
     const float s = g / (1.f + expf(-g));
     out[idx] = from_float<OT>(s * u);
 }
 
 MHB_EXPORT int mhb_swiglu(const void* gu, int in_dtype, int nsplit, long long split_stride,
-                          void* out, int out_dtype, int T, int I, cudaStream_t stream) {
+                          void* out, int out_dtype, int T, int I, int block, cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (block <= 0 || I % block) return fail("swiglu: block %d does not divide %d", block, I);
     if (nsplit > 1 && in_dtype != MHB_F32) return fail("swiglu: split partials must be float32");
     const size_t total = (size_t)T * I;
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     MHB_DISPATCH_DTYPE(in_dtype, IT, MHB_DISPATCH_DTYPE(out_dtype, OT,
         launch_kernel(swiglu_kernel<IT, OT>, dim3(blocks), dim3(threads), 0, stream, (const IT*)gu, nsplit,
-                                                            (size_t)split_stride, (OT*)out, I, total)));
+                                                            (size_t)split_stride, (OT*)out, I, block, total)));
     return check_launch("swiglu");
 }

@@ -122,8 +122,14 @@ template <typename OT> __device__ __forceinline__ void store_out(OT* p, float v)
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-// C element of (a-row ra, b-row rb): TRANSPOSED ? C[rb, ra] : C[ra, rb]
-template <int BN, int STAGES, bool TRANSPOSED, typename OT>
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + expf(-g)) * u; }
+
+// C element of (a-row ra, b-row rb): TRANSPOSED ? C[rb, ra] : C[ra, rb].
+// EPI = 1 (SwiGLU): the weight operand holds gate and up rows interleaved in blocks of 16
+// (rows 32j .. 32j+15 = gate rows 16j .., rows 32j+16 .. 32j+31 = up rows 16j ..); the epilogue
+// writes silu(gate) * up, so C has half as many columns as the weight has rows
+// (mini_hisparse/model.py:70-71).  Not combined with split K.
+template <int BN, int STAGES, bool TRANSPOSED, typename OT, int EPI>
 __global__ void __launch_bounds__(THREADS, (Smem<BN, STAGES>::TOTAL <= 112 * 1024) ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                OT* __restrict__ C, int Ra, int Rb, int K, long long ldc, int kb_per_split,
@@ -227,7 +233,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         else pdl_wait();       // nothing was loaded: still do not write before the previous kernel is done
         tc_fence_after();
         OT* Cz = C + (size_t)blockIdx.z * split_stride;
-        if (ok) {
+        if (ok && EPI == 1) {
+            if constexpr (EPI == 1 && TRANSPOSED) {
+                // lanes 0-15 of a warp hold gate rows, lanes 16-31 the up rows of the same block
+                const int out_col = (ra0 + quarter * 32) / 2 + (lane & 15);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float mine = __uint_as_float(r[j]);
+                        const float up = __shfl_down_sync(0xffffffffu, mine, 16);
+                        const int rb = rb0 + c0 + j;
+                        if (lane < 16 && rb < Rb && 2 * out_col < Ra)
+                            store_out<OT>(C + (size_t)rb * ldc + out_col, silu_mul(mine, up));
+                    }
+                }
+            } else if constexpr (EPI == 1) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t g[16], u[16];     // the loads are warp-wide: every lane takes part
+                    tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c0, g);
+                    tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c0 + 16, u);
+                    tmem_ld_wait();
+                    if (ra >= Ra) continue;
+                    const int oc = (rb0 + c0) / 2;
+                    OT* row = C + (size_t)ra * ldc + oc;
+                    float v[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j]));
+                    if (rb0 + c0 + 32 <= Rb && ((uintptr_t)row & 15) == 0 && sizeof(OT) == 2) {
+                        uint32_t p[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            __nv_bfloat162 t2 = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                            p[j] = *(uint32_t*)&t2;
+                        }
+                        *(uint4*)(row) = make_uint4(p[0], p[1], p[2], p[3]);
+                        *(uint4*)((uint8_t*)row + 16) = make_uint4(p[4], p[5], p[6], p[7]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (rb0 + c0 + 16 + j < Rb) store_out<OT>(row + j, v[j]);
+                    }
+                }
+            }
+        } else if (ok) {
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 uint32_t r[16];
@@ -327,11 +380,11 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, lon
     return 0;
 }
 
-template <int BN, int STAGES, bool TRANSPOSED, typename OT>
+template <int BN, int STAGES, bool TRANSPOSED, typename OT, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int Ra, int Rb, int K, long long ldc,
            int nsplit, int kb_per_split, long long split_stride, int constant_operand, int* status,
            cudaStream_t stream) {
-    auto kern = gemm_tc_kernel<BN, STAGES, TRANSPOSED, OT>;
+    auto kern = gemm_tc_kernel<BN, STAGES, TRANSPOSED, OT, EPI>;
     constexpr int smem = Smem<BN, STAGES>::TOTAL;
     static bool configured = false;
     if (!configured) {
@@ -345,17 +398,19 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int Ra, int Rb
     return check_launch("gemm_tc");
 }
 
-template <bool TRANSPOSED, typename OT>
+template <bool TRANSPOSED, typename OT, int EPI>
 int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* C, int Ra, int Rb, int K,
                 long long ldc, int nsplit, int kbps, long long ss, int co, int* status, cudaStream_t st) {
     switch (bn) {
         // the narrow tiles stream weights: two CTAs per SM (<= 112 KB each) overlap one CTA's
         // start-up and epilogue with the other's loads
-        case 16: return launch<16, 6, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
-        case 32: return launch<32, 5, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
-        case 64: return launch<64, 4, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
-        case 128: return launch<128, 6, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
-        case 256: return launch<256, 4, TRANSPOSED, OT>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
+        case 16:
+            if (EPI == 1 && !TRANSPOSED) break;      // the SwiGLU epilogue pairs 16 + 16 columns
+            return launch<16, 6, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
+        case 32: return launch<32, 5, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
+        case 64: return launch<64, 4, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
+        case 128: return launch<128, 6, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
+        case 256: return launch<256, 4, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
     }
     return fail("gemm_tc: no tile for BN %d", bn);
 }
@@ -382,11 +437,35 @@ MHB_EXPORT int mhb_gemm_tc(const void* X, const void* W, void* C, int c_dtype, i
     if (swap) {
         if ((rc = make_map(&ma, W, N, K, ldw, BM))) return rc;
         if ((rc = make_map(&mb, X, M, K, lda, bn))) return rc;
-        if (c_dtype == MHB_F32) return dispatch_bn<true, float>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
-        return dispatch_bn<true, __nv_bfloat16>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
+        if (c_dtype == MHB_F32) return dispatch_bn<true, float, 0>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
+        return dispatch_bn<true, __nv_bfloat16, 0>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
     }
     if ((rc = make_map(&ma, X, M, K, lda, BM))) return rc;
     if ((rc = make_map(&mb, W, N, K, ldw, bn))) return rc;
-    if (c_dtype == MHB_F32) return dispatch_bn<false, float>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
-    return dispatch_bn<false, __nv_bfloat16>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
+    if (c_dtype == MHB_F32) return dispatch_bn<false, float, 0>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
+    return dispatch_bn<false, __nv_bfloat16, 0>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
+}
+
+// act[M, I] = silu(X Wg^T) * (X Wu^T) where W [2 I, K] holds gate and up rows interleaved in
+// blocks of 16 (see the kernel).  I must be a multiple of 16; no split K.
+MHB_EXPORT int mhb_gemm_tc_swiglu(const void* X, const void* W, void* C, int c_dtype, int M, int I, int K,
+                                  long long lda, long long ldw, long long ldc, int swap, int bn, int* status,
+                                  cudaStream_t stream) {
+    if (M <= 0 || I <= 0) return 0;
+    if (I % 16) return fail("gemm_tc_swiglu: the intermediate size %d must be a multiple of 16", I);
+    if (K <= 0 || K % 8 || lda % 8 || ldw % 8) return fail("gemm_tc: K, lda and ldw must be multiples of 8 (K %d, lda %lld, ldw %lld)", K, lda, ldw);
+    if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return fail("gemm_tc: operands must be 16-byte aligned");
+    if (c_dtype != MHB_BF16) return fail("gemm_tc_swiglu: the output must be bfloat16");
+    const int N = 2 * I;
+    const int total_kb = (K + BK - 1) / BK;
+    CUtensorMap ma, mb;
+    int rc;
+    if (swap) {
+        if ((rc = make_map(&ma, W, N, K, ldw, BM))) return rc;
+        if ((rc = make_map(&mb, X, M, K, lda, bn))) return rc;
+        return dispatch_bn<true, __nv_bfloat16, 1>(bn, ma, mb, C, N, M, K, ldc, 1, total_kb, 0, 1, status, stream);
+    }
+    if ((rc = make_map(&ma, X, M, K, lda, BM))) return rc;
+    if ((rc = make_map(&mb, W, N, K, ldw, bn))) return rc;
+    return dispatch_bn<false, __nv_bfloat16, 1>(bn, ma, mb, C, M, N, K, ldc, 1, total_kb, 0, 2, status, stream);
 }

@@ -110,13 +110,14 @@ def rope_append(qkv, bias, positions, tok_seg, block_table, inv_freq, q_out, cac
         c_int(1 if rotate else 0), _ptr(status), _stream()), "rope_append")
 
 
-def swiglu(gate_up, out, nsplit=1, split_stride=0):
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+def swiglu(gate_up, out, nsplit=1, split_stride=0, block=None):
+    """out[t, i] = silu(gate_i) * up_i; gate_up[t] holds blocks of ``block`` gate values followed by
+    the up values of the same indices (default: one block, [gate | up])."""
     lib = build.load("elementwise")
     T, I = out.shape
     _check(lib, lib.mhb_swiglu(_ptr(gate_up), c_int(dtype_code(gate_up.dtype)), c_int(nsplit),
                                c_longlong(split_stride), _ptr(out), c_int(dtype_code(out.dtype)),
-                               c_int(T), c_int(I), _stream()), "swiglu")
+                               c_int(T), c_int(I), c_int(block or I), _stream()), "swiglu")
 
 
 def gemm_simt(a, w, out, bias=None, nsplit=1, split_stride=0):
@@ -156,6 +157,24 @@ def gemm_tc(a, w, out, *, swap: bool, bn: int, nsplit=1, split_stride=0, status=
         c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(-2)),
         c_int(1 if swap else 0), c_int(bn), c_int(nsplit), c_longlong(split_stride), _ptr(status),
         _stream()), "gemm_tc")
+
+
+def gemm_tc_swiglu(a, w, out, *, swap: bool, bn: int, status=None):
+    """out[M, I] = silu(a Wg^T) * (a Wu^T); ``w`` [2 I, K] holds gate and up rows interleaved in
+    blocks of 16 (rows 32j..32j+15 gate, 32j+16..32j+31 up)."""
+    lib = build.load("gemm_tc")
+    M, K = a.shape
+    I = out.shape[1]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc_swiglu: operands and output must be bfloat16")
+    if w.shape != (2 * I, K):
+        raise KernelError(f"gemm_tc_swiglu: w is {list(w.shape)}, expected [{2 * I}, {K}]")
+    if swap and M > bn:
+        raise KernelError(f"gemm_tc: {M} tokens do not fit the swapped tile of {bn}")
+    _check(lib, lib.mhb_gemm_tc_swiglu(
+        _ptr(a), _ptr(w), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(I), c_int(K),
+        c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
+        c_int(1 if swap else 0), c_int(bn), _ptr(status), _stream()), "gemm_tc_swiglu")
 
 
 def attention_simt(q, cache, out, part_acc, part_ml, items, num_items, max_items, positions,

@@ -39,6 +39,35 @@ class BFloat16Runtime(Runtime):
         kb_per = -(-total_kb // want)
         return -(-total_kb // kb_per)
 
+    GATE_BLOCK = 16     # gate and up rows are interleaved in blocks of this many rows
+
+    def swiglu_layout(self, gate: torch.Tensor, up: torch.Tensor):
+        """The stacked gate/up weight in the layout this runtime's SwiGLU product wants, and the
+        block size of that layout (the rows of a block of gate are followed by the same rows of up)."""
+        I, Kd = gate.shape
+        if I % self.GATE_BLOCK or Kd % 8:
+            return torch.cat((gate, up), 0).contiguous(), I
+        b = self.GATE_BLOCK
+        w = torch.stack((gate.view(I // b, b, Kd), up.view(I // b, b, Kd)), 1).reshape(2 * I, Kd)
+        return w.contiguous(), b
+
+    def linear_swiglu(self, x, weight, block: int, ws: Workspace, name: str) -> torch.Tensor:
+        """silu(x Wg^T) * (x Wu^T) for a weight from swiglu_layout(): fused into the product's
+        epilogue when the layout is interleaved, else the product followed by the gate kernel."""
+        M, Kd = x.shape
+        I = weight.shape[0] // 2
+        out = ws.get(name, (M, I), self.dtype)
+        if block == self.GATE_BLOCK and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0:
+            if M <= 64:
+                swap, bn = True, (16 if M <= 16 else 32 if M <= 32 else 64)
+            else:
+                swap, bn = False, 256
+            K.gemm_tc_swiglu(x, weight, out, swap=swap, bn=bn, status=self.status)
+            return out
+        gu = self.linear(x, weight, ws, name + "_gu")
+        K.swiglu(gu.tensor, out, nsplit=gu.nsplit, split_stride=gu.split_stride, block=block)
+        return out
+
     def linear(self, x, weight, ws: Workspace, name: str, out_dtype=None, bias=None,
                allow_split: bool = True) -> Product:
         M, Kd = x.shape

@@ -117,6 +117,19 @@ class Runtime:
         return Product(out)
 
 
+    def swiglu_layout(self, gate: torch.Tensor, up: torch.Tensor):
+        """The stacked gate/up weight [2 I, K] and the block size of its layout: rows of a block of
+        gate are followed by the same rows of up.  Here: one block, [gate | up]."""
+        return torch.cat((gate, up), 0).contiguous(), gate.shape[0]
+
+    def linear_swiglu(self, x, weight, block: int, ws: Workspace, name: str) -> torch.Tensor:
+        """silu(x Wg^T) * (x Wu^T) in the compute dtype."""
+        gu = self.linear(x, weight, ws, name + "_gu")
+        out = ws.get(name, (x.shape[0], weight.shape[0] // 2), self.dtype)
+        K.swiglu(gu.tensor, out, nsplit=gu.nsplit, split_stride=gu.split_stride, block=block)
+        return out
+
+
 # ---------------------------------------------------------------------------------------
 @dataclass
 class Segment:

@@ -13,8 +13,9 @@ from .spec import ParamSpec, PartSpec
 class SwiGLU(FeedForward):
     """down(silu(gate(x)) * up(x)), no biases (mini_hisparse/model.py:63-71).
 
-    gate_proj and up_proj are stacked into one [2 I, H] weight at load so that one product
-    feeds the gate kernel; the checkpoint names stay gate_proj / up_proj / down_proj.
+    gate_proj and up_proj are stacked into one [2 I, H] weight at load, in the layout the
+    runtime's product wants (interleaved in blocks when the gate is fused into the product's
+    epilogue); the checkpoint names stay gate_proj / up_proj / down_proj.
     """
 
     def __init__(self, spec: PartSpec, rt=None):
@@ -22,6 +23,7 @@ class SwiGLU(FeedForward):
         self.hidden = int(spec["hidden_size"])
         self.inter = int(spec["intermediate_size"])
         self.gate_up = None
+        self.gate_block = self.inter
         self.down = None
 
     def parameters(self):
@@ -32,12 +34,10 @@ class SwiGLU(FeedForward):
         }
 
     def load(self, tensors):
-        self.gate_up = torch.cat((tensors["gate_proj.weight"], tensors["up_proj.weight"]), 0).contiguous()
+        self.gate_up, self.gate_block = self.rt.swiglu_layout(tensors["gate_proj.weight"], tensors["up_proj.weight"])
         self.down = tensors["down_proj.weight"].contiguous()
 
     def forward(self, h, ctx: StepContext) -> Product:
         rt, ws = ctx.rt, ctx.ws
-        gu = rt.linear(h, self.gate_up, ws, "gate_up")
-        act = ws.get("ff_act", (h.shape[0], self.inter), rt.dtype)
-        K.swiglu(gu.tensor, act, nsplit=gu.nsplit, split_stride=gu.split_stride)
+        act = rt.linear_swiglu(h, self.gate_up, self.gate_block, ws, "ff_act")
         return rt.linear(act, self.down, ws, "ff_out")

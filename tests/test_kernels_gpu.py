@@ -150,6 +150,28 @@ def test_gemm_tensor_core(M, N, K_, swap, bn, nsplit, out_dtype):
         torch.testing.assert_close(got, ref, atol=1e-2 * float(ref.abs().max()), rtol=1e-2)
 
 
+@pytest.mark.parametrize("M,I,K_,swap,bn", [(200, 176, 64, False, 256), (2048, 1184, 512, False, 256),
+                                              (8, 176, 96, True, 16), (33, 304, 3584, True, 64), (1, 18944, 128, True, 16)])
+def test_gemm_tensor_core_swiglu_epilogue(M, I, K_, swap, bn):
+    """silu(x Wg^T) * (x Wu^T) written by the product's epilogue from block-interleaved weights."""
+    x = rnd(M, K_, dtype=torch.bfloat16, seed=1)
+    gate = rnd(I, K_, dtype=torch.bfloat16, seed=2, scale=0.2)
+    up = rnd(I, K_, dtype=torch.bfloat16, seed=3, scale=0.2)
+    w = torch.stack((gate.view(I // 16, 16, K_), up.view(I // 16, 16, K_)), 1).reshape(2 * I, K_).contiguous()
+    out = torch.full((M + 1, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K().gemm_tc_swiglu(x, w, out[:M], swap=swap, bn=bn, status=status)
+    g, u = x.float() @ gate.float().T, x.float() @ up.float().T
+    ref = g * torch.sigmoid(g) * u
+    assert int(status) == 0 and bool(out[M].isnan().all())
+    torch.testing.assert_close(out[:M].float(), ref, atol=1e-2 * float(ref.abs().max()), rtol=1.6e-2)
+    # the stand-alone gate kernel reads the same interleaved layout
+    gu = (x.float() @ w.float().T).to(torch.bfloat16)
+    out2 = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    K().swiglu(gu, out2, block=16)
+    torch.testing.assert_close(out2.float(), ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2)
+
+
 def test_gemm_tensor_core_refuses_unaligned_k():
     from mini_hisparse_b200.kernels.api import KernelError
 
