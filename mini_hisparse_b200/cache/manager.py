@@ -63,6 +63,9 @@ class PageGroup:
         if need.window is None:
             self.width = min(self.width, cfg.num_pages)
         self.tables: dict[int, _RequestPages] = {}       # slot -> pages
+        # the block tables as one array [slot, logical page], -1 where no page is held; kept in
+        # step with ``tables`` so that a step copies rows instead of walking Python lists
+        self.table_np = np.full((cfg.max_requests, self.width), -1, np.int32)
         shape = (len(entries), cfg.num_pages, 2, need.kv_heads, cfg.page_size, need.head_dim)
         self.storage = (
             torch.zeros(shape, dtype=cfg.dtype, device=cfg.device) if cfg.allocate_storage else None
@@ -204,6 +207,8 @@ class CacheManager:
                 g.allocator.free(request, pages)
             raise
         for g, rp, pages in got:
+            if pages:
+                g.table_np[req.slot, len(rp.pages): len(rp.pages) + len(pages)] = pages
             rp.pages.extend(pages)
 
     def advance(self, request, count: int) -> None:
@@ -223,6 +228,7 @@ class CacheManager:
                 g.allocator.free(request, pages)
                 for i in range(rp.first_live, dead):
                     rp.pages[i] = -1
+                g.table_np[req.slot, rp.first_live:dead] = -1
                 self.stats["window_pages_freed"] += len(pages)
                 rp.first_live = dead
 
@@ -231,6 +237,7 @@ class CacheManager:
         req = self.requests.pop(request)
         for g in self.page_groups:
             rp = g.tables.pop(req.slot)
+            g.table_np[req.slot, : len(rp.pages)] = -1
             g.allocator.free(request, [p for p in rp.pages if p >= 0])
             g.allocator.release_owner(request)
         self._free_slots.append(req.slot)
@@ -240,13 +247,7 @@ class CacheManager:
     def table_rows(self, gid: int, slots, width: int | None = None) -> np.ndarray:
         """Block-table rows [len(slots), width] int32 of the given slots, -1 where no page is held."""
         g = self.page_groups[gid]
-        width = width or g.width
-        out = np.full((len(slots), width), -1, np.int32)
-        for i, s in enumerate(slots):
-            pages = g.tables[s].pages
-            n = min(len(pages), width)
-            out[i, :n] = pages[:n]
-        return out
+        return g.table_np[np.asarray(slots, np.intp), : (width or g.width)]
 
     def entry_storage(self, entry: int):
         kind, gid, j = self.entry_group[entry]
@@ -272,6 +273,9 @@ class CacheManager:
                     seen[p] = name
                     assert g.allocator.owner_of(p) == name, f"page {p}: table and allocator disagree"
                 assert all(p < 0 for p in rp.pages[: rp.first_live]), "a passed page is still mapped"
+                row = g.table_np[r.slot]
+                assert row[: len(rp.pages)].tolist() == rp.pages and (row[len(rp.pages):] == -1).all(), \
+                    "the table array and the page lists differ"
                 assert len(rp.pages) >= -(-r.length // self.cfg.page_size), "a cached position has no page"
             assert len(seen) == g.allocator.in_use, "the allocator holds pages that no table names"
             assert set(g.tables) == set(live_slots), "tables and live slots differ"

@@ -60,9 +60,12 @@ class Engine:
         if cache_config is None:
             if num_pages is None:
                 raise ValueError("give a CacheConfig or num_pages")
+            width = None
+            if model.spec.max_positions:
+                width = min(num_pages, -(-model.spec.max_positions // page_size))
             cache_config = CacheConfig(num_pages=num_pages, page_size=page_size,
-                                       max_requests=max_requests, dtype=model.rt.dtype,
-                                       device=str(model.rt.device))
+                                       max_requests=max_requests, max_pages_per_request=width,
+                                       dtype=model.rt.dtype, device=str(model.rt.device))
         if cache_config.dtype != model.rt.dtype or torch.device(cache_config.device) != model.rt.device:
             raise ValueError("model/cache dtype or device differ")   # mini_hisparse/engine.py:36-38
         self.cache = CacheManager(model.cache_needs, cache_config)
@@ -101,6 +104,7 @@ class Engine:
         logits = self.runner.step(entries)
         sampled: list[int] = []
         if logits is not None:
+            self.runner.queue_status()
             rs = [p.request for p in planned if p.sample]
             sampled = self.sampler.sample(
                 logits,
@@ -108,7 +112,8 @@ class Engine:
                 [r.params.seed for r in rs],
                 [len(r.generated) for r in rs],
             )
-        self.runner.check_status()
+            self.runner.check_status(queued=True)    # the status word is sticky: a step without
+                                                     # samples is checked with the next one
         emitted = self.scheduler.commit(planned, sampled)
         self.timeline.append({"active": len(self.scheduler.running), "waiting": len(self.scheduler.waiting),
                               "tokens": sum(len(p.tokens) for p in planned)})

@@ -21,7 +21,7 @@ import torch
 from ..cache.manager import CacheManager
 from ..kernels import api as K
 from ..kernels import build
-from ..parts.attention import ITEM_INTS, ROW_TILE, plan_attention, plan_capacity
+from ..parts.attention import ITEM_INTS, ROW_TILE, plan_attention, plan_capacity, plan_decode
 from ..parts.base import CacheView, Segment, StepContext, Workspace
 from ..parts.spec import PagedKVNeed
 
@@ -199,6 +199,30 @@ class BatchBuilder:
                           "any_split": bool(plan.part_rows)})
         return len(rows), facts
 
+    def _fill_decode(self, buf: np.ndarray, layout: _Layout, entries, segments, nsplit):
+        """_fill for a batch of single decoded tokens that all want their logits, without loops
+        over tokens: the arrays a captured decode graph reads."""
+        B = len(segments)
+        starts = np.fromiter((s.start for s in segments), np.int64, B)
+        slots = np.fromiter((s.slot for s in segments), np.intp, B)
+        ar = np.arange(B, dtype=np.int32)
+        buf[layout.tokens : layout.tokens + B] = [e.tokens[0] for e in entries]
+        buf[layout.positions : layout.positions + B] = starts
+        buf[layout.tok_seg : layout.tok_seg + B] = ar
+        buf[layout.seg_slot : layout.seg_slot + B] = slots
+        buf[layout.rows : layout.rows + B] = ar
+        for gi, g in enumerate(self.cache.page_groups):
+            offs = layout.group_offsets[gi]
+            cap_items, width = layout.groups[gi]
+            buf[offs["block_table"] : offs["block_table"] + B * width].reshape(B, width)[:] = g.table_np[slots, :width]
+            plan = plan_decode(g.need, starts, nsplit[gi])
+            n = plan.items.shape[0]
+            if n != cap_items:
+                raise StepError(f"decode plan has {n} items, the graph was captured for {cap_items}")
+            buf[offs["items"] : offs["items"] + n * ITEM_INTS] = plan.items.reshape(-1)
+            buf[offs["tok_part_row"] : offs["tok_part_row"] + B] = plan.tok_part_row
+            buf[offs["tok_nsplit"] : offs["tok_nsplit"] + B] = plan.tok_nsplit
+
     def _views(self, meta: torch.Tensor, layout: _Layout, T: int, S: int, R: int, facts, launch_items=None):
         def v(off, n):
             return meta[off : off + n]
@@ -276,6 +300,7 @@ class ModelRunner:
         self.sm_count = self.batch.sm_count
         self.ws = Workspace(self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         if hasattr(self.rt, "status"):
             self.rt.status = self.status
         self.use_graphs = use_graphs and model.graph_safe
@@ -345,7 +370,7 @@ class ModelRunner:
             g = self.graphs[(B, width)] = _DecodeGraph(self, B, width)
         layout = g.layout
         stage, turn = self.batch.staging.next(layout.total)
-        _, facts = self.batch._fill(stage.numpy(), layout, entries, segments, fixed_nsplit=g.nsplit)
+        self.batch._fill_decode(stage.numpy(), layout, entries, segments, g.nsplit)
         g.meta.copy_(stage[: layout.total], non_blocking=True)
         self.batch.staging.mark(turn)
         if g.graph is None:
@@ -374,9 +399,14 @@ class ModelRunner:
         self.stats["graph_steps"] += 1
         return g.logits
 
-    def check_status(self) -> None:
+    def queue_status(self) -> None:
+        """Start the copy of the status word to the host; read it with check_status(queued=True)
+        after the stream has been synchronised (saves a synchronisation of its own)."""
+        self.status_host.copy_(self.status, non_blocking=True)
+
+    def check_status(self, queued: bool = False) -> None:
         """Raise if a kernel flagged a bad index (ids outside the table, pages outside the pool)."""
-        bits = int(self.status.item())
+        bits = int(self.status_host.item()) if queued else int(self.status.item())
         if bits:
             self.status.zero_()
             what = []

@@ -104,6 +104,41 @@ def plan_attention(need: PagedKVNeed, segments, T: int, sm_count: int = 148,
     return AttentionPlan(arr, n_small, len(big_items), tok_part_row, tok_nsplit, part_rows)
 
 
+def plan_decode(need: PagedKVNeed, starts: np.ndarray, nsplit: int) -> AttentionPlan:
+    """The plan of a batch of single decoded tokens (token i belongs to segment i and sits at
+    position starts[i]) with exactly ``nsplit`` key splits each: what plan_attention gives for such
+    a batch with fixed_nsplit, computed with arrays instead of loops."""
+    B = len(starts)
+    groups = need.q_heads // need.kv_heads
+    chunks, _ = _tiling(groups, ROW_TILE)
+    C = len(chunks)
+    kv_end = starts.astype(np.int64) + 1
+    kv_begin = np.maximum(0, starts - need.window + 1) if need.window else np.zeros(B, np.int64)
+    items = np.empty((B, nsplit, C, ITEM_INTS), np.int32)
+    seg = np.arange(B, dtype=np.int32)
+    items[..., 0] = seg[:, None, None]
+    items[..., 1] = seg[:, None, None]
+    items[..., 2] = 1
+    items[..., 3] = np.asarray([h for h, _ in chunks], np.int32)[None, None, :]
+    items[..., 4] = np.asarray([n for _, n in chunks], np.int32)[None, None, :]
+    if nsplit == 1:
+        items[..., 5] = kv_begin[:, None, None]
+        items[..., 6] = kv_end[:, None, None]
+        items[..., 7] = -1
+        return AttentionPlan(items.reshape(-1, ITEM_INTS), B * C, 0, np.zeros(B, np.int32),
+                             np.zeros(B, np.int32), 0)
+    span = kv_end - kv_begin
+    chunk = -(-(-(-span // nsplit)) // KEY_TILE) * KEY_TILE
+    ks = np.arange(nsplit, dtype=np.int64)
+    b = np.minimum(kv_end[:, None], kv_begin[:, None] + ks[None, :] * chunk[:, None])
+    e = np.minimum(kv_end[:, None], b + chunk[:, None])
+    items[..., 5] = b[:, :, None]
+    items[..., 6] = e[:, :, None]
+    items[..., 7] = ks[None, :, None]
+    return AttentionPlan(items.reshape(-1, ITEM_INTS), B * nsplit * C, 0,
+                         (seg * nsplit).astype(np.int32), np.full(B, nsplit, np.int32), B * nsplit)
+
+
 def plan_capacity(need: PagedKVNeed, max_tokens: int, max_segments: int,
                   fixed_nsplit: int | None = None) -> tuple[int, int]:
     """Upper bounds (items, partial rows) for a step of at most max_tokens / max_segments."""
