@@ -56,6 +56,9 @@ def _run(config: dict, context: int, args) -> dict:
         gpu_pages=pages, host_pages=pages, page_size=page, kv_heads=cfg.num_key_value_heads,
         head_dim=cfg.head_dim, device="cuda:0", dtype=torch.bfloat16,
         index_budget_bytes=8 * 1024 ** 3,
+        # one attention window over the whole history (its --chunk-pages option): with the default
+        # of 4 pages a decode step of this size took 27 s on a B200
+        chunk_pages=context // page + 1,
     ))
     engine = Engine(model, cache)
     g = torch.Generator().manual_seed(3)

@@ -416,4 +416,6 @@ class ModelRunner:
                 what.append("a position had no valid page in its block table")
             if bits & 4:
                 what.append("a bounded wait in the tensor-core matrix product ran out")
+            if bits & 8:
+                what.append("a bounded wait in the TMA-fed attention kernel ran out")
             raise StepError("; ".join(what) or f"kernel status {bits}")

@@ -214,6 +214,30 @@ def attention_mma(q, cache, out, part_acc, part_ml, items, num_items, rows, posi
         "attention_mma")
 
 
+def attention_tma_supports(d: int, page_size: int) -> bool:
+    """Head sizes and page sizes the TMA-fed attention kernel is built for."""
+    return d in (64, 128) and 2 <= page_size <= 64 and 64 % page_size == 0
+
+
+def attention_tma(q, cache, out, part_acc, part_ml, items, num_items, rows, positions, block_table,
+                  tok_part_row, *, nq, nkv, d, page_size, window=0, scale=None, tok_nsplit=None,
+                  counters=None, status=None):
+    """attention_mma with keys and values staged by TMA through a ring of mbarrier-guarded stages."""
+    lib = build.load("attention_tma")
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError("attention_tma: q and the cache must be bfloat16")
+    if not cache.is_contiguous():
+        raise KernelError("attention_tma: the layer's pool must be contiguous")
+    if scale is None:
+        scale = float(d) ** -0.5
+    _check(lib, lib.mhb_attention_tma(
+        _ptr(q), _ptr(cache), _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(items), c_int(num_items),
+        c_int(num_items), c_int(rows), _ptr(positions), _ptr(block_table), c_int(block_table.shape[-1]),
+        _ptr(tok_part_row), _ptr(tok_nsplit), _ptr(counters), c_int(nq), c_int(nkv), c_int(d),
+        c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(status),
+        _stream()), "attention_tma")
+
+
 def attention_combine(part_acc, part_ml, tok_part_row, tok_nsplit, out, *, nq, d):
     lib = build.load("attention_simt")
     T = out.shape[0]

@@ -233,13 +233,16 @@ class GQAttention(Mixer):
         tail = (ctx.positions, meta["block_table"], meta["tok_part_row"])
         n_small, n_big = meta["n_small"], meta["n_big"]
         if self.tensor_core_attention:
+            tma = K.attention_tma_supports(self.d, cache.page_size)
+            kernel = K.attention_tma if tma else K.attention_mma
+            extra = {"status": ctx.status} if tma else {}
             if n_small:
                 chunks = -(-(self.nq // self.nkv) // ROW_TILE)
                 counters = ws.get_zeroed("attn_counters", (T * self.nkv * chunks,), torch.int32)
-                K.attention_mma(*args, meta["items"], n_small, 16, *tail, **common,
-                                tok_nsplit=meta["tok_nsplit"], counters=counters)
+                kernel(*args, meta["items"], n_small, 16, *tail, **common, **extra,
+                       tok_nsplit=meta["tok_nsplit"], counters=counters)
             if n_big:
-                K.attention_mma(*args, meta["items"][n_small * ITEM_INTS:], n_big, 64, *tail, **common)
+                kernel(*args, meta["items"][n_small * ITEM_INTS:], n_big, 64, *tail, **common, **extra)
         elif n_small + n_big:
             K.attention_simt(*args, meta["items"], n_small + n_big, n_small + n_big, *tail, **common)
         if meta["any_split"] and not self.tensor_core_attention:

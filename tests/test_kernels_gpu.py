@@ -295,7 +295,7 @@ def run_attention(nq, nkv, d, P_, seg_specs, dtype, window=None, fixed_nsplit=No
     if edit:
         edit(qs, ks, vs, cache, table)
     T = sum(n for _, n in seg_specs)
-    need = PagedKVNeed(nkv, d, nq, window, tile_rows=64 if kernel == "mma" else 16)
+    need = PagedKVNeed(nkv, d, nq, window, tile_rows=64 if kernel in ("mma", "tma") else 16)
     plan = plan_attention(need, segments, T, 148, fixed_nsplit=fixed_nsplit)
     q = torch.cat([qq[h:] for qq, (h, n) in zip(qs, seg_specs)]).reshape(T, nq * d).to(DEV)
     out = torch.full((T, nq * d), float("nan"), dtype=dtype, device=DEV)
@@ -307,18 +307,19 @@ def run_attention(nq, nkv, d, P_, seg_specs, dtype, window=None, fixed_nsplit=No
     tns = torch.from_numpy(plan.tok_nsplit).to(DEV)
     n_items = plan.items.shape[0]
     kw = dict(nq=nq, nkv=nkv, d=d, page_size=P_, window=window or 0)
-    fused = kernel == "mma" and seed % 2 == 0     # the kernel merges its own key splits
-    if kernel == "mma":
+    fused = kernel in ("mma", "tma") and seed % 2 == 0     # the kernel merges its own key splits
+    if kernel in ("mma", "tma"):
+        launch = K().attention_mma if kernel == "mma" else K().attention_tma
         if plan.n_small:
             groups = nq // nkv
             counters = torch.zeros(T * nkv * -(-groups // 16), dtype=torch.int32, device=DEV) if fused else None
-            K().attention_mma(q, cache, out, part_acc, part_ml, items, plan.n_small, 16, positions, table, tpr,
-                              tok_nsplit=tns, counters=counters, **kw)
+            launch(q, cache, out, part_acc, part_ml, items, plan.n_small, 16, positions, table, tpr,
+                   tok_nsplit=tns, counters=counters, **kw)
             if fused:
                 assert int(counters.abs().sum()) == 0        # left zero for the next launch
         if plan.n_big:
-            K().attention_mma(q, cache, out, part_acc, part_ml, items[plan.n_small * ITEM_INTS:], plan.n_big, 64,
-                              positions, table, tpr, **kw)
+            launch(q, cache, out, part_acc, part_ml, items[plan.n_small * ITEM_INTS:], plan.n_big, 64,
+                   positions, table, tpr, **kw)
     else:
         K().attention_simt(q, cache, out, part_acc, part_ml, items, n_items, n_items, positions, table, tpr, **kw)
     if plan.part_rows and not fused:
@@ -341,20 +342,32 @@ def test_attention_tensor_core_portions_and_decode_mixed(nq, nkv, d, P_):
     torch.testing.assert_close(out, ref, **tol(torch.bfloat16, 2))
 
 
-def test_attention_tensor_core_splits_window_and_far_key():
+@pytest.mark.parametrize("nq,nkv,d,P_", [(4, 2, 64, 16), (3, 1, 128, 32), (28, 4, 128, 16), (20, 1, 64, 8),
+                                          (6, 3, 128, 64), (40, 2, 128, 4)])
+def test_attention_tma_portions_and_decode_mixed(nq, nkv, d, P_):
+    """The TMA-fed kernel on the same mix: long portions, short ones, offsets inside a page, groups
+    larger than a tile, every page size that divides 64."""
+    specs = [(0, 137), (45, 19), (130, 1), (63, 2), (200, 70), (0, 1), (5, 16)]
+    out, ref, plan = run_attention(nq, nkv, d, P_, specs, torch.bfloat16, kernel="tma")
+    assert plan.n_small and plan.n_big
+    torch.testing.assert_close(out, ref, **tol(torch.bfloat16, 2))
+
+
+@pytest.mark.parametrize("kernel", ["mma", "tma"])
+def test_attention_tensor_core_splits_window_and_far_key(kernel):
     bf = torch.bfloat16
     for seed in (0, 1):      # merged inside the kernel, and by attention_combine
         out, ref, plan = run_attention(28, 4, 128, 16, [(700, 1), (33, 1), (1023, 1), (0, 1), (300, 2)], bf,
-                                       fixed_nsplit=5, kernel="mma", seed=seed)
+                                       fixed_nsplit=5, kernel=kernel, seed=seed)
         assert plan.part_rows == 30
         torch.testing.assert_close(out, ref, **tol(bf, 2))
-    out, ref, plan = run_attention(40, 2, 64, 16, [(500, 1), (90, 3)], bf, fixed_nsplit=3, kernel="mma")
+    out, ref, plan = run_attention(40, 2, 64, 16, [(500, 1), (90, 3)], bf, fixed_nsplit=3, kernel=kernel)
     torch.testing.assert_close(out, ref, **tol(bf, 2))          # groups of 20 heads: two chunks per token
-    out, ref, plan = run_attention(8, 2, 64, 16, [(2000, 1)], bf, kernel="mma")
+    out, ref, plan = run_attention(8, 2, 64, 16, [(2000, 1)], bf, kernel=kernel)
     assert plan.part_rows > 1
     torch.testing.assert_close(out, ref, **tol(bf, 2))
     for window in (1, 5, 16, 40, 64, 65):
-        out, ref, _ = run_attention(4, 2, 32, 16, [(0, 150), (77, 3), (100, 1)], bf, window=window, kernel="mma")
+        out, ref, _ = run_attention(4, 2, 64, 16, [(0, 150), (77, 3), (100, 1)], bf, window=window, kernel=kernel)
         torch.testing.assert_close(out, ref, **tol(bf, 2))
 
     def edit(qs, ks, vs, cache, table):
@@ -365,9 +378,9 @@ def test_attention_tensor_core_splits_window_and_far_key():
             qs[0][-1, h] = direction * 60.0
         ks[0][3, :] = (direction * 8.0).to(ks[0].dtype)
         cache[int(table[0, 0]), 0, :, 3] = ks[0][3].to(cache.device)
-    out, ref, _ = run_attention(4, 2, 64, 16, [(640, 1)], bf, edit=edit, kernel="mma")
+    out, ref, _ = run_attention(4, 2, 64, 16, [(640, 1)], bf, edit=edit, kernel=kernel)
     torch.testing.assert_close(out, ref, **tol(bf, 2))
-    out2, ref2, _ = run_attention(4, 2, 64, 16, [(0, 641)], bf, edit=edit, kernel="mma")
+    out2, ref2, _ = run_attention(4, 2, 64, 16, [(0, 641)], bf, edit=edit, kernel=kernel)
     torch.testing.assert_close(out2, ref2, **tol(bf, 2))
 
 

@@ -1,0 +1,83 @@
+"""The layer sizes of the benchmark (Qwen2.5-7B: hidden 3584, 28 query heads over 4 KV heads of 128,
+feed-forward 18944) with two layers and a smaller vocabulary that is no power of two: the kernels
+at the sizes they are tuned for, in float32 and in bfloat16, whole prompt, portions and decode,
+against the plain implementation run in float32 on the device."""
+import json
+
+import pytest
+import torch
+
+from conftest import random_tokens
+from plain import qwen2_plain as P
+
+pytestmark = pytest.mark.gpu
+
+CONFIG = dict(
+    architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=30011, hidden_size=3584,
+    intermediate_size=18944, num_hidden_layers=2, num_attention_heads=28, num_key_value_heads=4,
+    rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=4096,
+)
+
+
+@pytest.fixture(scope="module")
+def folder(tmp_path_factory):
+    """Weights drawn on the GPU (fast) and written through the package's safetensors writer."""
+    from mini_hisparse_b200 import resolve
+    from mini_hisparse_b200.weights import write_safetensors
+    from mini_hisparse_b200.weights.expected import expected_tensors_of_spec
+
+    out = tmp_path_factory.mktemp("shape7b")
+    gen = torch.Generator(device="cuda:0").manual_seed(77)
+    tensors = {}
+    for name, ps in expected_tensors_of_spec(resolve(CONFIG)[1]).items():
+        mean, std = (1.0, 0.1) if "norm" in name else (0.0, 0.02)
+        if ps.role == "matrix":
+            std = 1.5 / (ps.shape[-1] ** 0.5)       # activations of order one: attention is not uniform
+        t = torch.empty(ps.shape, device="cuda:0").normal_(mean, std, generator=gen)
+        tensors[name] = (t.bfloat16() if ps.role == "matrix" else t).cpu()
+    (out / "config.json").write_text(json.dumps(CONFIG))
+    write_safetensors(out / "model.safetensors", tensors)
+    return out
+
+
+@pytest.fixture(scope="module")
+def reference(folder):
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    cfg, w = P.load_folder(folder, dtype=torch.float32, device="cuda:0")
+    tokens = random_tokens(CONFIG["vocab_size"], 700, seed=9)
+    return tokens, P.forward_logits(cfg, w, tokens).cpu()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_7b_layer_sizes_all_cuts(folder, reference, dtype):
+    from mini_hisparse_b200 import CacheConfig, CacheManager, load_model
+    from mini_hisparse_b200.engine import ModelRunner, StepEntry
+
+    tokens, ref = reference
+    model = load_model(folder, dtype=dtype)
+    cache = CacheManager(model.cache_needs, CacheConfig(num_pages=96, page_size=16, max_requests=4,
+                                                        dtype=model.rt.dtype))
+    runner = ModelRunner(model, cache)
+    tol = dict(atol=1e-3, rtol=1e-3) if dtype == "float32" else dict(atol=0.03 * float(ref.abs().max()), rtol=0.03)
+
+    def run(name, cuts):
+        cache.open(name)
+        rows, i = [], 0
+        for n in cuts:
+            out = runner.step([StepEntry(name, tokens[i:i + n], list(range(n)))])
+            rows.append(out.float().cpu().clone())
+            i += n
+        runner.check_status()
+        cache.close(name)
+        return torch.cat(rows), i
+
+    got, n = run("whole", [700])
+    torch.testing.assert_close(got, ref[:n], **tol)
+    got, n = run("portions", [300, 65, 2, 130, 17, 2] + [1] * 20)       # the ones go through a graph
+    torch.testing.assert_close(got, ref[:n], **tol)
+    if dtype == "bfloat16":
+        agree = (got.argmax(-1) == ref[:n].argmax(-1)).float().mean()
+        assert agree > 0.9
+    assert runner.stats["graph_steps"] >= 20
+    cache.assert_invariants()
