@@ -96,3 +96,71 @@ MHB_EXPORT int mhb_gemm_simt(const void* A, int a_dtype, const void* W, int w_dt
             (long long)split_stride))));
     return check_launch("gemm_simt");
 }
+
+
+// ---- the same product for callers that cannot allocate (see gemm_simt_noalloc.h) -----------------
+#include "gemm_simt_noalloc.h"
+
+namespace {
+// Scratch of the no-allocation entry point: nsplit partial matrices of M x N floats.  Every GPU
+// that loads this library holds these 8 MiB until the process exits.  In HOST code this name is
+// only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float g_noalloc_scratch[MHB_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+float* g_noalloc_ptr[MAX_DEVICES] = {nullptr};
+
+// C[m, n] = sum over the splits, in split order
+__global__ void sum_partials_kernel(const float* __restrict__ parts, float* __restrict__ C, int M, int N,
+                                    long long ldc, int nsplit) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)M * N) return;
+    float v = parts[idx];
+    for (int s = 1; s < nsplit; ++s) v += parts[(size_t)s * M * N + idx];
+    C[(idx / N) * ldc + idx % N] = v;
+}
+
+// The device address of the scratch array on the current device; looked up once per device.
+int noalloc_scratch(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail("gemm_simt_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= MAX_DEVICES) return fail("gemm_simt_noalloc: device %d is beyond the %d this library tracks", dev, MAX_DEVICES);
+    if (g_noalloc_ptr[dev] == nullptr) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return fail("gemm_simt_noalloc: cudaGetSymbolAddress on device %d: %s", dev, cudaGetErrorString(e));
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return 0;
+}
+}  // namespace
+
+MHB_EXPORT int mhb_gemm_simt_noalloc(const void* A, int a_dtype, const void* W, int w_dtype, float* C, int M,
+                                     int N, int K, long long lda, long long ldw, long long ldc, int nsplit,
+                                     cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0) return fail("gemm_simt_noalloc: K must be positive");
+    if (nsplit < 1) nsplit = 1;
+    const long long need = (long long)nsplit * M * N;
+    if (need > (long long)MHB_NOALLOC_SCRATCH_FLOATS)
+        return fail("gemm_simt_noalloc: %d splits of a %d x %d product need %lld floats of scratch; the built-in "
+                    "array holds %d (use fewer splits, or mhb_gemm_simt with a buffer of your own)",
+                    nsplit, M, N, need, (int)MHB_NOALLOC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    int rc = noalloc_scratch(&scratch);
+    if (rc) return rc;
+    // every partial element is written by the product below before the sum reads it
+    rc = mhb_gemm_simt(A, a_dtype, W, w_dtype, scratch, MHB_F32, nullptr, M, N, K, lda, ldw, N, nsplit,
+                       (long long)M * N, stream);
+    if (rc) return rc;
+    const size_t total = (size_t)M * N;
+    const int threads = 256;
+    launch_kernel(sum_partials_kernel, dim3((unsigned)((total + threads - 1) / threads)), dim3(threads), 0, stream,
+                  (const float*)scratch, C, M, N, ldc, nsplit);
+    return check_launch("gemm_simt_noalloc");
+}
