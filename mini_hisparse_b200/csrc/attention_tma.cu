@@ -95,14 +95,10 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
     const int tile_begin = (kv_begin / KT) * KT;
     const int ntiles = kv_end > kv_begin ? (kv_end - tile_begin + KT - 1) / KT : 0;
 
-    // values that a partly filled last tile leaves untouched must be finite: zero the ring once
-    for (int i = tid; i < STAGES * L::STAGE_BYTES / 16; i += THREADS)
-        *(uint4*)(smem + L::Q_BYTES + i * 16) = make_uint4(0, 0, 0, 0);
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), CWARPS); }
         mbar_fence_init();
     }
-    fence_proxy_async();
     __syncthreads();
 
     if (warp == CWARPS) {
@@ -115,10 +111,14 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
             if (lane == 0) ok = mbar_wait(empty_bar(stage), phase ^ 1);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
+            // Every page slot of the stage is filled: a slot past the last key (or before the first,
+            // inside a page that a window has given back) gets the page of key kv_begin again, so
+            // that the masked positions hold finite numbers (0 * NaN would poison the output).
             const int kp0 = tile_begin + itile * KT + lane * a.P;
             int page = -1;
-            if (lane < pages_per_tile && kp0 < kv_end) {
-                page = table[kp0 / a.P];
+            if (lane < pages_per_tile) {
+                if (kp0 < kv_end) page = table[kp0 / a.P];
+                if (page < 0 || page >= a.num_pages) page = table[kv_begin / a.P];
                 if (page >= a.num_pages) page = -1;
             }
             const unsigned have = __ballot_sync(0xffffffffu, page >= 0);
