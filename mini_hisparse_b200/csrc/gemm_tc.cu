@@ -58,6 +58,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     }
     return false;
 }
+__device__ __forceinline__ void mbar_arrive_plain(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -344,6 +347,185 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+
+// ---- persistent variant for many tokens ---------------------------------------------------------------
+// One CTA per SM walks over output tiles (128 tokens x bn features, bn any multiple of 16 up to
+// 256, chosen by the host so that the last round of tiles is nearly full).  Tensor memory holds
+// TWO accumulators of 256 columns: while the epilogue warps read one and store it, the MMA warp
+// already fills the other, so the tensor pipe does not wait for the epilogue (which, with the
+// SwiGLU gate, costs a third of a tile's time).  A = activations [M, K], B = weights [N, K].
+constexpr int P_STAGES = 4;
+constexpr int P_BN_MAX = 256;
+struct PSmem {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = P_BN_MAX * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BARRIER_OFFSET = P_STAGES * STAGE_BYTES;
+    static constexpr int TOTAL = BARRIER_OFFSET + (2 * P_STAGES + 4) * 8 + 16 + 1024;
+};
+
+template <typename OT, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          OT* __restrict__ C, int Ra, int Rb, int K, long long ldc, int bn, int tiles_m,
+                          int num_tiles, int* __restrict__ status) {
+    using S = PSmem;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_base = smem_base + S::BARRIER_OFFSET;
+    auto full_bar = [&](int s) { return bar_base + 8 * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8 * (P_STAGES + s); };
+    auto acc_full_bar = [&](int b) { return bar_base + 8 * (2 * P_STAGES + b); };
+    auto acc_empty_bar = [&](int b) { return bar_base + 8 * (2 * P_STAGES + 2 + b); };
+    uint32_t* tmem_slot = (uint32_t*)(smem + S::BARRIER_OFFSET + 8 * (2 * P_STAGES + 4));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_kb = (K + BK - 1) / BK;
+    const uint32_t stage_tx = S::A_BYTES + bn * BK * 2;
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+            pdl_wait();
+            int it = 0;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int ra0 = (t % tiles_m) * BM, rb0 = (t / tiles_m) * bn;
+                for (int kb = 0; kb < total_kb; ++kb, ++it) {
+                    const int s = it % P_STAGES;
+                    ok = mbar_wait(empty_bar(s), ((it / P_STAGES) & 1) ^ 1);
+                    if (!ok) break;
+                    mbar_expect_tx(full_bar(s), stage_tx);
+                    const uint32_t a_dst = smem_base + s * S::STAGE_BYTES;
+                    tma_load_2d(a_dst, &map_a, kb * BK, ra0, full_bar(s));
+                    tma_load_2d(a_dst + S::A_BYTES, &map_b, kb * BK, rb0, full_bar(s));
+                }
+            }
+            // nothing of ours may still be in flight when the CTA leaves: wait for the last stages
+            for (int back = 1; back <= P_STAGES && back <= it; ++back) {
+                const int i = it - back;
+                mbar_wait(full_bar(i % P_STAGES), (i / P_STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(bn);
+            int it = 0, j = 0;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++j) {
+                const int b = j & 1;
+                ok = mbar_wait(acc_empty_bar(b), ((j >> 1) & 1) ^ 1);     // the epilogue has read this buffer
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = tmem_base + b * P_BN_MAX;
+                for (int kb = 0; kb < total_kb; ++kb, ++it) {
+                    const int s = it % P_STAGES;
+                    ok = mbar_wait(full_bar(s), (it / P_STAGES) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_base + s * S::STAGE_BYTES;
+                    const uint32_t b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16(acc, make_smem_desc(a_addr + k * UMMA_K * 2), make_smem_desc(b_addr + k * UMMA_K * 2),
+                                  idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(empty_bar(s));
+                }
+                if (ok) umma_commit(acc_full_bar(b));
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int j = 0;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++j) {
+            const int b = j & 1;
+            const int ra0 = (t % tiles_m) * BM, rb0 = (t / tiles_m) * bn;
+            const int ra = ra0 + quarter * 32 + lane;
+            ok = mbar_wait(acc_full_bar(b), (j >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + b * P_BN_MAX;
+            if constexpr (EPI == 1) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < bn; c0 += 32) {
+                    uint32_t g[16], u[16];
+                    tmem_ld16(acc + c0, g);
+                    tmem_ld16(acc + c0 + 16, u);
+                    tmem_ld_wait();
+                    if (ra >= Ra) continue;
+                    OT* row = C + (size_t)ra * ldc + (rb0 + c0) / 2;
+                    float v[16];
+#pragma unroll
+                    for (int x = 0; x < 16; ++x) v[x] = silu_mul(__uint_as_float(g[x]), __uint_as_float(u[x]));
+                    if (rb0 + c0 + 32 <= Rb && ((uintptr_t)row & 15) == 0 && sizeof(OT) == 2) {
+                        uint32_t p[8];
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) {
+                            __nv_bfloat162 t2 = __floats2bfloat162_rn(v[2 * x], v[2 * x + 1]);
+                            p[x] = *(uint32_t*)&t2;
+                        }
+                        *(uint4*)(row) = make_uint4(p[0], p[1], p[2], p[3]);
+                        *(uint4*)((uint8_t*)row + 16) = make_uint4(p[4], p[5], p[6], p[7]);
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < 16; ++x)
+                            if (rb0 + c0 + 16 + x < Rb) store_out<OT>(row + x, v[x]);
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = 0; c0 < bn; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(acc + c0, r);
+                    tmem_ld_wait();
+                    if (ra >= Ra) continue;
+                    OT* row = C + (size_t)ra * ldc + rb0 + c0;
+                    if (rb0 + c0 + 16 <= Rb && ((uintptr_t)row & 15) == 0) {
+                        if constexpr (sizeof(OT) == 4) {
+#pragma unroll
+                            for (int x = 0; x < 16; x += 4)
+                                *(uint4*)(row + x) = make_uint4(r[x], r[x + 1], r[x + 2], r[x + 3]);
+                        } else {
+                            uint32_t p[8];
+#pragma unroll
+                            for (int x = 0; x < 8; ++x) {
+                                __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(r[2 * x]), __uint_as_float(r[2 * x + 1]));
+                                p[x] = *(uint32_t*)&v2;
+                            }
+                            *(uint4*)(row) = make_uint4(p[0], p[1], p[2], p[3]);
+                            *(uint4*)(row + 8) = make_uint4(p[4], p[5], p[6], p[7]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < 16; ++x)
+                            if (rb0 + c0 + x < Rb) store_out<OT>(row + x, __uint_as_float(r[x]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_plain(acc_empty_bar(b));    // this warp has read its quarter
+        }
+    }
+    if (!ok && status) atomicOr(status, 4);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
 // ---- host: tensor maps ----------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -426,6 +608,50 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* C, i
     }
     return fail("gemm_tc: no tile for BN %d", bn);
 }
+
+// Tile width (multiple of 16, 128..256; for the SwiGLU epilogue a multiple of 32) that wastes the
+// least of the last round of tiles on `sms` persistent CTAs.
+int choose_persistent_bn(int tiles_m, int N, int sms, int step) {
+    int best = 256;
+    double best_cost = 1e30;
+    for (int bn = 256; bn >= 128; bn -= step) {
+        const int tiles = tiles_m * ((N + bn - 1) / bn);
+        const int rounds = (tiles + sms - 1) / sms;
+        const double cost = (double)rounds * (bn + 24);      // + a tile's fixed cost
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
+template <typename OT, int EPI>
+int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
+                      long long ldc, int* status, cudaStream_t stream) {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    const int tiles_m = (M + BM - 1) / BM;
+    const int bn = choose_persistent_bn(tiles_m, N, sms, EPI == 1 ? 32 : 16);
+    const int num_tiles = tiles_m * ((N + bn - 1) / bn);
+    CUtensorMap ma, mb;
+    int rc;
+    if ((rc = make_map(&ma, X, M, K, lda, BM))) return rc;
+    if ((rc = make_map(&mb, W, N, K, ldw, bn))) return rc;
+    auto kern = gemm_tc_persistent_kernel<OT, EPI>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PSmem::TOTAL);
+        if (e != cudaSuccess) return fail("gemm_tc: cannot set %d bytes of shared memory: %s", PSmem::TOTAL, cudaGetErrorString(e));
+        configured = true;
+    }
+    const int grid = num_tiles < sms ? num_tiles : sms;
+    launch_kernel(kern, dim3(grid), dim3(THREADS), PSmem::TOTAL, stream, ma, mb, (OT*)C, M, N, K, ldc, bn, tiles_m,
+                  num_tiles, status);
+    return check_launch("gemm_tc_persistent");
+}
 }  // namespace
 
 // C[M, N] = X[M, K] * W[N, K]^T, bfloat16 in, float32 accumulation, C float32 or bfloat16.
@@ -453,6 +679,10 @@ MHB_EXPORT int mhb_gemm_tc(const void* X, const void* W, void* C, int c_dtype, i
         if (c_dtype == MHB_F32) return dispatch_bn<true, float, 0>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, l2_prefetch_kb, status, stream);
         return dispatch_bn<true, __nv_bfloat16, 0>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, l2_prefetch_kb, status, stream);
     }
+    if (nsplit == 1 && bn == 256 && M >= 256) {       // many tokens: the persistent kernel
+        if (c_dtype == MHB_F32) return launch_persistent<float, 0>(X, W, C, M, N, K, lda, ldw, ldc, status, stream);
+        return launch_persistent<__nv_bfloat16, 0>(X, W, C, M, N, K, lda, ldw, ldc, status, stream);
+    }
     if ((rc = make_map(&ma, X, M, K, lda, BM))) return rc;
     if ((rc = make_map(&mb, W, N, K, ldw, bn))) return rc;
     if (c_dtype == MHB_F32) return dispatch_bn<false, float, 0>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, l2_prefetch_kb, status, stream);
@@ -478,6 +708,8 @@ MHB_EXPORT int mhb_gemm_tc_swiglu(const void* X, const void* W, void* C, int c_d
         if ((rc = make_map(&mb, X, M, K, lda, bn))) return rc;
         return dispatch_bn<true, __nv_bfloat16, 1>(bn, ma, mb, C, N, M, K, ldc, 1, total_kb, 0, 1, l2_prefetch_kb, status, stream);
     }
+    if (bn == 256 && M >= 256)
+        return launch_persistent<__nv_bfloat16, 1>(X, W, C, M, N, K, lda, ldw, ldc, status, stream);
     if ((rc = make_map(&ma, X, M, K, lda, BM))) return rc;
     if ((rc = make_map(&mb, W, N, K, ldw, bn))) return rc;
     return dispatch_bn<false, __nv_bfloat16, 1>(bn, ma, mb, C, M, N, K, ldc, 1, total_kb, 0, 2, l2_prefetch_kb, status, stream);
