@@ -384,6 +384,7 @@ int launch(const AttnArgs& a, int launch_items, cudaStream_t stream) {
     if (!configured && smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail("attention_mma: shared memory %d: %s", smem, cudaGetErrorString(e));
+        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         configured = true;
     }
     dim3 grid(launch_items, a.nkv);

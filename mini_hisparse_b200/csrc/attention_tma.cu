@@ -63,7 +63,7 @@ __device__ __forceinline__ uint32_t swz(uint32_t base, int rows_per_half, int r,
 __device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CWARPS * 32) : "memory"); }
 
 template <int D, int ROWS>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 2)
 attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a) {
     using L = Layout<D, ROWS>;
     constexpr int STAGES = L::STAGES;
@@ -376,6 +376,8 @@ int launch(const CUtensorMap& map, const AttnArgs& a, int launch_items, cudaStre
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail("attention_tma: shared memory %d: %s", smem, cudaGetErrorString(e));
+        // two CTAs per SM need the large shared-memory carve-out even when one CTA would fit a small one
+        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         configured = true;
     }
     launch_kernel(kern, dim3(launch_items, a.nkv), dim3(THREADS), smem, stream, map, a);
