@@ -66,9 +66,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int c0, int c1) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
-}
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -139,7 +136,7 @@ template <int BN, int STAGES, bool TRANSPOSED, typename OT, int EPI>
 __global__ void __launch_bounds__(THREADS, (Smem<BN, STAGES>::TOTAL <= 112 * 1024) ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                OT* __restrict__ C, int Ra, int Rb, int K, long long ldc, int kb_per_split,
-               long long split_stride, int constant_operand, int l2_prefetch_kb, int* __restrict__ status) {
+               long long split_stride, int constant_operand, int* __restrict__ status) {
     using S = Smem<BN, STAGES>;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
     extern __shared__ uint8_t smem_raw[];
@@ -186,15 +183,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (constant_operand == 1) tma_load_2d(a_dst, &map_a, (kb_begin + i) * BK, ra0, full_bar(i));
                 else tma_load_2d(a_dst + S::A_BYTES, &map_b, (kb_begin + i) * BK, rb0, full_bar(i));
                 issued = i + 1;
-            }
-            // ... and up to l2_prefetch_kb further weight tiles are pulled into L2 while the
-            // kernel before this one is still running and leaves the HBM idle.
-            if (constant_operand) {
-                const int stop = min(num_kb, early + l2_prefetch_kb);
-                for (int i = early; i < stop; ++i) {
-                    if (constant_operand == 1) tma_prefetch_l2_2d(&map_a, (kb_begin + i) * BK, ra0);
-                    else tma_prefetch_l2_2d(&map_b, (kb_begin + i) * BK, rb0);
-                }
             }
             pdl_wait();
             for (int i = 0; i < early; ++i) {
@@ -576,7 +564,7 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, lon
 
 template <int BN, int STAGES, bool TRANSPOSED, typename OT, int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int Ra, int Rb, int K, long long ldc,
-           int nsplit, int kb_per_split, long long split_stride, int constant_operand, int l2_kb, int* status,
+           int nsplit, int kb_per_split, long long split_stride, int constant_operand, int* status,
            cudaStream_t stream) {
     auto kern = gemm_tc_kernel<BN, STAGES, TRANSPOSED, OT, EPI>;
     constexpr int smem = Smem<BN, STAGES>::TOTAL;
@@ -588,23 +576,23 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int Ra, int Rb
     }
     dim3 grid((Ra + BM - 1) / BM, (Rb + BN - 1) / BN, nsplit);
     launch_kernel(kern, grid, dim3(THREADS), smem, stream, ma, mb, (OT*)C, Ra, Rb, K, ldc, kb_per_split,
-                  split_stride, constant_operand, l2_kb, status);
+                  split_stride, constant_operand, status);
     return check_launch("gemm_tc");
 }
 
 template <bool TRANSPOSED, typename OT, int EPI>
 int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* C, int Ra, int Rb, int K,
-                long long ldc, int nsplit, int kbps, long long ss, int co, int l2_kb, int* status, cudaStream_t st) {
+                long long ldc, int nsplit, int kbps, long long ss, int co, int* status, cudaStream_t st) {
     switch (bn) {
         // the narrow tiles stream weights: two CTAs per SM (<= 112 KB each) overlap one CTA's
         // start-up and epilogue with the other's loads
         case 16:
             if (EPI == 1 && !TRANSPOSED) break;      // the SwiGLU epilogue pairs 16 + 16 columns
-            return launch<16, 6, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, l2_kb, status, st);
-        case 32: return launch<32, 5, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, l2_kb, status, st);
-        case 64: return launch<64, 4, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, l2_kb, status, st);
-        case 128: return launch<128, 6, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, l2_kb, status, st);
-        case 256: return launch<256, 4, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, l2_kb, status, st);
+            return launch<16, 6, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
+        case 32: return launch<32, 5, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
+        case 64: return launch<64, 4, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
+        case 128: return launch<128, 6, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
+        case 256: return launch<256, 4, TRANSPOSED, OT, EPI>(ma, mb, C, Ra, Rb, K, ldc, nsplit, kbps, ss, co, status, st);
     }
     return fail("gemm_tc: no tile for BN %d", bn);
 }
@@ -656,12 +644,11 @@ int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K
 
 // C[M, N] = X[M, K] * W[N, K]^T, bfloat16 in, float32 accumulation, C float32 or bfloat16.
 // swap != 0 streams W through the 128-row operand (few tokens); bn is the tile width along the
-// other operand (16..256); l2_prefetch_kb = K blocks of weights per CTA to pull into L2 before the
-// wait for the previous kernel (0: none).  Requirements (else an error, never a wrong result): K % 8 == 0,
+// other operand (16..256).  Requirements (else an error, never a wrong result): K % 8 == 0,
 // lda % 8 == 0, ldw % 8 == 0, pointers 16-byte aligned.
 MHB_EXPORT int mhb_gemm_tc(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
                            long long lda, long long ldw, long long ldc, int swap, int bn, int nsplit,
-                           long long split_stride, int l2_prefetch_kb, int* status, cudaStream_t stream) {
+                           long long split_stride, int* status, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || lda % 8 || ldw % 8) return fail("gemm_tc: K, lda and ldw must be multiples of 8 (K %d, lda %lld, ldw %lld)", K, lda, ldw);
     if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return fail("gemm_tc: operands must be 16-byte aligned");
@@ -676,8 +663,8 @@ MHB_EXPORT int mhb_gemm_tc(const void* X, const void* W, void* C, int c_dtype, i
     if (swap) {
         if ((rc = make_map(&ma, W, N, K, ldw, BM))) return rc;
         if ((rc = make_map(&mb, X, M, K, lda, bn))) return rc;
-        if (c_dtype == MHB_F32) return dispatch_bn<true, float, 0>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, l2_prefetch_kb, status, stream);
-        return dispatch_bn<true, __nv_bfloat16, 0>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, l2_prefetch_kb, status, stream);
+        if (c_dtype == MHB_F32) return dispatch_bn<true, float, 0>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
+        return dispatch_bn<true, __nv_bfloat16, 0>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
     }
     if (nsplit == 1 && bn == 256 && M >= 256) {       // many tokens: the persistent kernel
         if (c_dtype == MHB_F32) return launch_persistent<float, 0>(X, W, C, M, N, K, lda, ldw, ldc, status, stream);
@@ -685,15 +672,15 @@ MHB_EXPORT int mhb_gemm_tc(const void* X, const void* W, void* C, int c_dtype, i
     }
     if ((rc = make_map(&ma, X, M, K, lda, BM))) return rc;
     if ((rc = make_map(&mb, W, N, K, ldw, bn))) return rc;
-    if (c_dtype == MHB_F32) return dispatch_bn<false, float, 0>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, l2_prefetch_kb, status, stream);
-    return dispatch_bn<false, __nv_bfloat16, 0>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, l2_prefetch_kb, status, stream);
+    if (c_dtype == MHB_F32) return dispatch_bn<false, float, 0>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
+    return dispatch_bn<false, __nv_bfloat16, 0>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
 }
 
 // act[M, I] = silu(X Wg^T) * (X Wu^T) where W [2 I, K] holds gate and up rows interleaved in
 // blocks of 16 (see the kernel).  I must be a multiple of 16; no split K.
 MHB_EXPORT int mhb_gemm_tc_swiglu(const void* X, const void* W, void* C, int c_dtype, int M, int I, int K,
-                                  long long lda, long long ldw, long long ldc, int swap, int bn,
-                                  int l2_prefetch_kb, int* status, cudaStream_t stream) {
+                                  long long lda, long long ldw, long long ldc, int swap, int bn, int* status,
+                                  cudaStream_t stream) {
     if (M <= 0 || I <= 0) return 0;
     if (I % 16) return fail("gemm_tc_swiglu: the intermediate size %d must be a multiple of 16", I);
     if (K <= 0 || K % 8 || lda % 8 || ldw % 8) return fail("gemm_tc: K, lda and ldw must be multiples of 8 (K %d, lda %lld, ldw %lld)", K, lda, ldw);
@@ -706,11 +693,11 @@ MHB_EXPORT int mhb_gemm_tc_swiglu(const void* X, const void* W, void* C, int c_d
     if (swap) {
         if ((rc = make_map(&ma, W, N, K, ldw, BM))) return rc;
         if ((rc = make_map(&mb, X, M, K, lda, bn))) return rc;
-        return dispatch_bn<true, __nv_bfloat16, 1>(bn, ma, mb, C, N, M, K, ldc, 1, total_kb, 0, 1, l2_prefetch_kb, status, stream);
+        return dispatch_bn<true, __nv_bfloat16, 1>(bn, ma, mb, C, N, M, K, ldc, 1, total_kb, 0, 1, status, stream);
     }
     if (bn == 256 && M >= 256)
         return launch_persistent<__nv_bfloat16, 1>(X, W, C, M, N, K, lda, ldw, ldc, status, stream);
     if ((rc = make_map(&ma, X, M, K, lda, BM))) return rc;
     if ((rc = make_map(&mb, W, N, K, ldw, bn))) return rc;
-    return dispatch_bn<false, __nv_bfloat16, 1>(bn, ma, mb, C, M, N, K, ldc, 1, total_kb, 0, 2, l2_prefetch_kb, status, stream);
+    return dispatch_bn<false, __nv_bfloat16, 1>(bn, ma, mb, C, M, N, K, ldc, 1, total_kb, 0, 2, status, stream);
 }

@@ -136,7 +136,7 @@ def gemm_simt(a, w, out, bias=None, nsplit=1, split_stride=0):
         c_int(nsplit), c_longlong(split_stride), _stream()), "gemm_simt")
 
 
-def gemm_tc(a, w, out, *, swap: bool, bn: int, nsplit=1, split_stride=0, status=None, l2_prefetch_kb=0):
+def gemm_tc(a, w, out, *, swap: bool, bn: int, nsplit=1, split_stride=0, status=None):
     """out[M, N] = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulate).
 
     ``swap`` streams the weights through the 128-row operand (for few tokens, M <= bn <= 64);
@@ -155,11 +155,11 @@ def gemm_tc(a, w, out, *, swap: bool, bn: int, nsplit=1, split_stride=0, status=
     _check(lib, lib.mhb_gemm_tc(
         _ptr(a), _ptr(w), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K),
         c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(-2)),
-        c_int(1 if swap else 0), c_int(bn), c_int(nsplit), c_longlong(split_stride),
-        c_int(l2_prefetch_kb), _ptr(status), _stream()), "gemm_tc")
+        c_int(1 if swap else 0), c_int(bn), c_int(nsplit), c_longlong(split_stride), _ptr(status),
+        _stream()), "gemm_tc")
 
 
-def gemm_tc_swiglu(a, w, out, *, swap: bool, bn: int, status=None, l2_prefetch_kb=0):
+def gemm_tc_swiglu(a, w, out, *, swap: bool, bn: int, status=None):
     """out[M, I] = silu(a Wg^T) * (a Wu^T); ``w`` [2 I, K] holds gate and up rows interleaved in
     blocks of 16 (rows 32j..32j+15 gate, 32j+16..32j+31 up)."""
     lib = build.load("gemm_tc")
@@ -174,8 +174,7 @@ def gemm_tc_swiglu(a, w, out, *, swap: bool, bn: int, status=None, l2_prefetch_k
     _check(lib, lib.mhb_gemm_tc_swiglu(
         _ptr(a), _ptr(w), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(I), c_int(K),
         c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
-        c_int(1 if swap else 0), c_int(bn), c_int(l2_prefetch_kb), _ptr(status), _stream()),
-        "gemm_tc_swiglu")
+        c_int(1 if swap else 0), c_int(bn), _ptr(status), _stream()), "gemm_tc_swiglu")
 
 
 def attention_simt(q, cache, out, part_acc, part_ml, items, num_items, max_items, positions,

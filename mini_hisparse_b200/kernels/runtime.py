@@ -15,7 +15,6 @@ from . import api as K
 
 BK = 64            # K elements per pipeline stage of the tensor-core kernel
 MIN_KB_PER_SPLIT = 4
-L2_PREFETCH_BYTES = 48 << 20    # weights a streaming product pulls into L2 before its predecessor ends
 
 
 class Float32Runtime(Runtime):
@@ -63,21 +62,14 @@ class BFloat16Runtime(Runtime):
                 swap, bn = True, (16 if M <= 16 else 32 if M <= 32 else 64)
             else:
                 swap, bn = False, 256
-            K.gemm_tc_swiglu(x, weight, out, swap=swap, bn=bn, status=self.status,
-                             l2_prefetch_kb=self._l2_kb(swap, -(-weight.shape[0] // 128), True))
+            K.gemm_tc_swiglu(x, weight, out, swap=swap, bn=bn, status=self.status)
             return out
         gu = self.linear(x, weight, ws, name + "_gu")
         K.swiglu(gu.tensor, out, nsplit=gu.nsplit, split_stride=gu.split_stride, block=block)
         return out
 
-    def _l2_kb(self, swap: bool, ctas: int, prefetch: bool) -> int:
-        """K blocks (of 128 weight rows x 64) each CTA of a streaming product may prefetch into L2."""
-        if not (swap and prefetch):
-            return 0
-        return max(0, L2_PREFETCH_BYTES // (ctas * 128 * BK * 2))
-
     def linear(self, x, weight, ws: Workspace, name: str, out_dtype=None, bias=None,
-               allow_split: bool = True, prefetch: bool = True) -> Product:
+               allow_split: bool = True) -> Product:
         M, Kd = x.shape
         N = weight.shape[0]
         out_dtype = out_dtype or self.dtype
@@ -100,11 +92,10 @@ class BFloat16Runtime(Runtime):
         if nsplit > 1:
             out = ws.get(name, (nsplit, M, N), torch.float32)
             K.gemm_tc(x, weight, out, swap=swap, bn=bn, nsplit=nsplit, split_stride=out.stride(0),
-                      status=self.status, l2_prefetch_kb=self._l2_kb(swap, tiles * nsplit, prefetch))
+                      status=self.status)
             return Product(out, nsplit)
         out = ws.get(name, (M, N), out_dtype)
-        K.gemm_tc(x, weight, out, swap=swap, bn=bn, status=self.status,
-                  l2_prefetch_kb=self._l2_kb(swap, tiles, prefetch))
+        K.gemm_tc(x, weight, out, swap=swap, bn=bn, status=self.status)
         return Product(out)
 
 

@@ -108,10 +108,9 @@ class Runtime:
 
     def linear(self, x: torch.Tensor, weight: torch.Tensor, ws: Workspace, name: str,
                out_dtype: torch.dtype | None = None, bias: torch.Tensor | None = None,
-               allow_split: bool = True, prefetch: bool = True) -> Product:
+               allow_split: bool = True) -> Product:
         """x [M, K] times weight [N, K] transposed, float32 accumulation.  The result may come as
-        split-K partial matrices unless ``allow_split`` is False.  ``prefetch=False`` says that the
-        kernel before this one is itself bound by memory, so pulling weights into L2 early is no use."""
+        split-K partial matrices unless ``allow_split`` is False."""
         M, N = x.shape[0], weight.shape[0]
         out = ws.get(name, (M, N), out_dtype or self.dtype)
         K.gemm_simt(x, weight, out, bias=bias)

@@ -40,4 +40,4 @@ class SwiGLU(FeedForward):
     def forward(self, h, ctx: StepContext) -> Product:
         rt, ws = ctx.rt, ctx.ws
         act = rt.linear_swiglu(h, self.gate_up, self.gate_block, ws, "ff_act")
-        return rt.linear(act, self.down, ws, "ff_out", prefetch=False)
+        return rt.linear(act, self.down, ws, "ff_out")
