@@ -1,0 +1,357 @@
+// Causal grouped-query attention for long prompt portions on the 5th-generation tensor cores.
+//
+// Math and work items as in attention_tma.cu (mini_hisparse/model.py:173-179): one CTA serves one
+// item (a run of tokens of one request times the heads of one KV group: up to 128 query rows) and
+// one KV head, against the cached keys [kv_begin, kv_end) read through the block table.
+//
+// Per tile of 64 keys:
+//   S = Q K^T        tcgen05.mma, M = 128 rows, N = 64 keys, K = head_dim; Q and the key tile are
+//                    K-major in shared memory (TMA, 128-byte swizzle); S lands in tensor memory.
+//   softmax          four warps, ONE QUERY ROW PER THREAD: tcgen05.ld brings the row's 64 scores into
+//                    registers, so maximum and sum need no shuffles; scores, exponentials and sums
+//                    are float32; P goes to shared memory as bfloat16 (K-major, swizzled).
+//   O += P V         tcgen05.mma, M = 128, N = head_dim, K = 64, accumulated in tensor memory; the
+//                    value tile [keys, head_dim] is the MN-major operand exactly as TMA wrote it.
+// The running maximum that the exponentials refer to is only raised when a row's true maximum has
+// grown by more than 2^8 (so p <= 256, exact enough in bfloat16 and float32); only then the row's
+// accumulator in tensor memory is rescaled (tcgen05.ld, multiply, tcgen05.st).  That is rare after
+// the first tiles, so a softmax thread normally touches 64 scores per tile and nothing else.
+// Two S buffers let the MMA warp compute the next tile's scores while the softmax warps work; two
+// CTAs share an SM (tensor memory 2 x 256 columns), so one CTA's softmax overlaps the other's MMAs.
+// Warp 0 issues the TMA loads, warp 1 owns tensor memory and issues the MMAs, warps 2-5 are the
+// softmax warps.  Every mbarrier wait is bounded (status bit 16 when one runs out).
+//
+// Needs head_dim 64 or 128 and a page size that divides 64; items are never split along the keys.
+#include "mma_helpers.cuh"
+#include "tc_helpers.cuh"
+#include "tma_helpers.cuh"
+
+using namespace mhb;
+
+MHB_EXPORT const char* mhb_last_error() { return error_buffer(); }
+
+namespace {
+constexpr int ROWS = 128;
+constexpr int KT = 64;
+constexpr int STAGES = 2;
+constexpr int THREADS = 192;
+constexpr int ITEM_INTS = 8;
+
+struct AttnArgs {
+    const __nv_bfloat16* q;
+    __nv_bfloat16* out;
+    const int* items;
+    const int* positions;
+    const int* block_table;
+    int* status;
+    int num_items, width, nq, nkv, P, num_pages, window;
+    float scale;
+};
+
+template <int D>
+struct Layout {
+    static constexpr int HALVES = D / 64;
+    static constexpr int Q_BYTES = HALVES * ROWS * 128;
+    static constexpr int K_BYTES = HALVES * KT * 128;          // also V
+    static constexpr int STAGE_BYTES = 2 * K_BYTES;
+    static constexpr int P_BYTES = ROWS * 128;                 // one P buffer: 128 rows x 64 keys
+    static constexpr int KV_OFFSET = Q_BYTES;
+    static constexpr int P_OFFSET = KV_OFFSET + STAGES * STAGE_BYTES;
+    static constexpr int BAR_OFFSET = P_OFFSET + P_BYTES;
+    static constexpr int NUM_BARS = 2 * STAGES + 1 + 2 + 2 + 1 + 1;   // kv full/empty, q, s full/free, p full, o done
+    static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16;
+    static constexpr int TMEM_COLS = 256;                      // S: 2 x 64 columns, O tile: D columns from column 128
+};
+
+__device__ __forceinline__ uint32_t swz_addr(uint32_t base, int rows_per_half, int r, int e) {
+    return base + (e >> 6) * rows_per_half * 128 + r * 128 + ((((e & 63) >> 3) ^ (r & 7)) << 4);
+}
+
+template <int D>
+__global__ void __launch_bounds__(THREADS, 2)
+attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a) {
+    using L = Layout<D>;
+    constexpr int HALVES = L::HALVES;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t base = smem_addr(smem);
+    const uint32_t q_s = base, kv_s = base + L::KV_OFFSET, p_s = base + L::P_OFFSET;
+    const uint32_t bars = base + L::BAR_OFFSET;
+    auto kv_full = [&](int s) { return bars + 8 * s; };
+    auto kv_empty = [&](int s) { return bars + 8 * (STAGES + s); };
+    const uint32_t q_full = bars + 8 * (2 * STAGES);
+    auto s_full = [&](int b) { return bars + 8 * (2 * STAGES + 1 + b); };
+    auto s_free = [&](int b) { return bars + 8 * (2 * STAGES + 3 + b); };
+    const uint32_t p_full = bars + 8 * (2 * STAGES + 5);
+    const uint32_t o_done = bars + 8 * (2 * STAGES + 6);
+    uint32_t* tmem_slot = (uint32_t*)(smem + L::BAR_OFFSET + 8 * L::NUM_BARS);
+
+    pdl_launch_dependents();
+    pdl_wait();
+    if ((int)blockIdx.x >= a.num_items) return;
+    const int* it = a.items + (size_t)blockIdx.x * ITEM_INTS;
+    const int seg = it[0], tok0 = it[1], ntok = it[2], head0 = it[3], nheads = it[4];
+    const int kv_begin = it[5], kv_end = it[6];
+    const int kvh = blockIdx.y;
+    const int groups = a.nq / a.nkv;
+    const int nrows = ntok * nheads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* table = a.block_table + (size_t)seg * a.width;
+    const int tile_begin = (kv_begin / KT) * KT;
+    const int ntiles = kv_end > kv_begin ? (kv_end - tile_begin + KT - 1) / KT : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
+        mbar_init(q_full, 4);
+        for (int b = 0; b < 2; ++b) { mbar_init(s_full(b), 1); mbar_init(s_free(b), 4); }
+        mbar_init(p_full, 4);
+        mbar_init(o_done, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(smem_addr(tmem_slot), L::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        // ---- TMA warp: one lane per page of a tile; every page slot of a stage is filled ------------
+        const int pages_per_tile = KT / a.P;
+        for (int j = 0; j < ntiles && ok; ++j) {
+            const int stage = j % STAGES;
+            if (lane == 0) ok = mbar_wait(kv_empty(stage), ((j / STAGES) & 1) ^ 1);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            const int kp0 = tile_begin + j * KT + lane * a.P;
+            int page = -1;
+            if (lane < pages_per_tile) {
+                if (kp0 < kv_end) page = table[kp0 / a.P];
+                if (page < 0 || page >= a.num_pages) page = table[kv_begin / a.P];   // masked keys: any finite data
+                if (page >= a.num_pages) page = -1;
+            }
+            const unsigned have = __ballot_sync(0xffffffffu, page >= 0);
+            if (lane == 0) mbar_expect_tx(kv_full(stage), __popc(have) * 2 * a.P * D * 2);
+            __syncwarp();
+            if (page >= 0) {
+                const int row0 = ((page * 2) * a.nkv + kvh) * a.P;
+                const uint32_t dst = kv_s + stage * L::STAGE_BYTES + lane * a.P * 128;
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) {
+                    tma_load_2d(dst + h * KT * 128, &kv_map, h * 64, row0, kv_full(stage));
+                    tma_load_2d(dst + L::K_BYTES + h * KT * 128, &kv_map, h * 64, row0 + a.nkv * a.P, kv_full(stage));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA warp ----------------------------------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = umma_idesc(KT, false);      // S: N = 64 keys, both operands K-major
+            constexpr uint32_t idesc_o = umma_idesc(D, true);        // O tile: N = head_dim, V is MN-major
+            auto issue_s = [&](int j) {          // S(j) = Q K(j)^T into S buffer j & 1
+                const uint32_t k_s = kv_s + (j % STAGES) * L::STAGE_BYTES;
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k) {
+                    const uint64_t da = smem_desc_kmajor(q_s + (k >> 2) * (ROWS * 128) + (k & 3) * 32);
+                    const uint64_t db = smem_desc_kmajor(k_s + (k >> 2) * (KT * 128) + (k & 3) * 32);
+                    umma_bf16(tmem + (j & 1) * KT, da, db, idesc_s, k > 0 ? 1u : 0u);
+                }
+                umma_commit(s_full(j & 1));
+            };
+            ok = mbar_wait(q_full, 0);
+            if (ok && ntiles > 0) {
+                ok = mbar_wait(kv_full(0), 0);
+                if (ok) { tc_fence_after(); issue_s(0); }
+            }
+            for (int j = 0; j < ntiles && ok; ++j) {
+                if (j + 1 < ntiles) {
+                    ok = mbar_wait(kv_full((j + 1) % STAGES), ((j + 1) / STAGES) & 1);
+                    if (ok) ok = mbar_wait(s_free((j + 1) & 1), (((j + 1) >> 1) & 1) ^ 1);   // softmax has read S(j - 1)
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_s(j + 1);
+                }
+                ok = mbar_wait(p_full, j & 1);          // P(j) is in shared memory, O is rescaled if needed
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t v_s = kv_s + (j % STAGES) * L::STAGE_BYTES + L::K_BYTES;
+#pragma unroll
+                for (int k = 0; k < KT / 16; ++k) {
+                    const uint64_t da = smem_desc_kmajor(p_s + k * 32);
+                    const uint64_t db = smem_desc_mnmajor(v_s + k * 16 * 128, KT * 128, 1024);
+                    umma_bf16(tmem + 128, da, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(o_done);                    // P and O are free again when this completes
+                umma_commit(kv_empty(j % STAGES));      // K(j) and V(j) are consumed
+            }
+        }
+    } else {
+        // ---- softmax warps: thread = query row -----------------------------------------------------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const bool live = row < nrows;
+        const int t = tok0 + (live ? row / nheads : 0), hq = kvh * groups + head0 + (live ? row % nheads : 0);
+        {   // stage this thread's query row (swizzled, K-major)
+            const __nv_bfloat16* src = a.q + ((size_t)t * a.nq + hq) * D;
+#pragma unroll
+            for (int ch = 0; ch < D / 8; ++ch) cp_async16(swz_addr(q_s, ROWS, row, ch * 8), src + ch * 8, live ? 16 : 0);
+            cp_async_commit();
+            cp_async_wait<0>();
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(q_full);
+        }
+        const int qp = live ? a.positions[t] : -1;
+        const float scale_log2 = a.scale * 1.4426950408889634f;
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+        float m_ref = -INFINITY;      // the maximum the exponentials refer to (at most 2^8 below the true one)
+        float l_run = 0.f;
+
+        for (int j = 0; j < ntiles; ++j) {
+            ok = mbar_wait(s_full(j & 1), (j >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            float s[KT];
+#pragma unroll
+            for (int c = 0; c < KT; c += 16) {
+                uint32_t r[16];
+                tmem_ld16(lane_addr + (j & 1) * KT + c, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int x = 0; x < 16; ++x) s[c + x] = __uint_as_float(r[x]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free(j & 1));
+            const int t0 = tile_begin + j * KT;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int x = 0; x < KT; ++x) {
+                const int kp = t0 + x;
+                const bool valid = kp >= kv_begin && kp < kv_end && kp <= qp && (a.window <= 0 || kp > qp - a.window);
+                s[x] = valid ? s[x] : -INFINITY;
+                mx = fmaxf(mx, s[x]);
+            }
+            // raise the reference maximum only when the row's maximum outgrew it by more than 2^8
+            const bool raise = mx > -INFINITY && (m_ref == -INFINITY || (mx - m_ref) * scale_log2 > 8.f);
+            const float m_old = m_ref;
+            if (raise) m_ref = mx;
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            // P (one buffer) and O are only ours once the previous tile's P V has completed
+            if (j > 0) {
+                ok = mbar_wait(o_done, (j - 1) & 1);
+                if (!ok) break;
+                tc_fence_after();
+            }
+            const bool rescale = raise && m_old > -INFINITY;     // there is an accumulator to rescale
+            if (__any_sync(0xffffffffu, rescale)) {
+                const float alpha = rescale ? exp2f((m_old - m_use) * scale_log2) : 1.f;
+                l_run *= alpha;
+#pragma unroll
+                for (int c = 0; c < D; c += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(lane_addr + 128 + c, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int x = 0; x < 16; ++x) r[x] = __float_as_uint(__uint_as_float(r[x]) * alpha);
+                    tmem_st16(lane_addr + 128 + c, r);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+            }
+            float psum = 0.f;
+            const uint32_t prow = p_s + row * 128;
+#pragma unroll
+            for (int ch = 0; ch < KT / 8; ++ch) {
+                float p[8];
+#pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                    p[x] = exp2f((s[ch * 8 + x] - m_use) * scale_log2);
+                    psum += p[x];
+                }
+                const uint32_t w0 = pack_bf16(p[0], p[1]), w1 = pack_bf16(p[2], p[3]);
+                const uint32_t w2 = pack_bf16(p[4], p[5]), w3 = pack_bf16(p[6], p[7]);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + ((ch ^ (row & 7)) << 4)),
+                             "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+            }
+            l_run += psum;
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
+        }
+        if (ok && ntiles > 0) ok = mbar_wait(o_done, (ntiles - 1) & 1);
+        tc_fence_after();
+        if (ok) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            __nv_bfloat16* dst = a.out + ((size_t)t * a.nq + hq) * D;
+#pragma unroll
+            for (int c = 0; c < D; c += 16) {
+                uint32_t r[16];
+                if (ntiles > 0) {
+                    tmem_ld16(lane_addr + 128 + c, r);      // warp-wide: every lane takes part
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int x = 0; x < 16; ++x) r[x] = 0;
+                }
+                if (live) {
+                    uint4 v0, v1;
+                    v0.x = pack_bf16(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
+                    v0.y = pack_bf16(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
+                    v0.z = pack_bf16(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
+                    v0.w = pack_bf16(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
+                    v1.x = pack_bf16(__uint_as_float(r[8]) * inv, __uint_as_float(r[9]) * inv);
+                    v1.y = pack_bf16(__uint_as_float(r[10]) * inv, __uint_as_float(r[11]) * inv);
+                    v1.z = pack_bf16(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
+                    v1.w = pack_bf16(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
+                    *(uint4*)(dst + c) = v0;
+                    *(uint4*)(dst + c + 8) = v1;
+                }
+            }
+        }
+    }
+    if (!ok && lane == 0 && a.status) atomicOr(a.status, 16);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, L::TMEM_COLS);
+}
+
+template <int D>
+int launch(const CUtensorMap& map, const AttnArgs& a, int launch_items, cudaStream_t stream) {
+    auto kern = attention_tc_kernel<D>;
+    constexpr int smem = Layout<D>::TOTAL;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return fail("attention_tc: shared memory %d: %s", smem, cudaGetErrorString(e));
+        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        configured = true;
+    }
+    launch_kernel(kern, dim3(launch_items, a.nkv), dim3(THREADS), smem, stream, map, a);
+    return check_launch("attention_tc");
+}
+}  // namespace
+
+MHB_EXPORT int mhb_attention_tc_supports(int d, int P) {
+    return (d == 64 || d == 128) && P >= 2 && P <= KT && KT % P == 0;
+}
+
+// Items must be planned for tiles of 128 rows and carry split = -1.  cache: one layer's pool
+// [num_pages, 2, nkv, P, d] bfloat16.
+MHB_EXPORT int mhb_attention_tc(const void* q, const void* cache, void* out, const int* items, int num_items,
+                                const int* positions, const int* block_table, int width, int nq, int nkv, int d,
+                                int P, int num_pages, int window, float scale, int* status, cudaStream_t stream) {
+    if (num_items <= 0) return 0;
+    if (nkv <= 0 || nq % nkv) return fail("attention: %d query heads over %d KV heads", nq, nkv);
+    if (!mhb_attention_tc_supports(d, P))
+        return fail("attention_tc: head_dim %d with pages of %d keys is not built (head_dim 64 or 128, page size dividing 64)", d, P);
+    const long long total_rows = (long long)num_pages * 2 * nkv * P;
+    if (total_rows > 0x7fffffffLL) return fail("attention_tc: the pool has too many rows for one tensor map");
+    CUtensorMap map;
+    int rc = make_bf16_map(&map, cache, total_rows, d, d, P);
+    if (rc) return rc;
+    AttnArgs a;
+    a.q = (const __nv_bfloat16*)q; a.out = (__nv_bfloat16*)out; a.items = items; a.positions = positions;
+    a.block_table = block_table; a.status = status; a.num_items = num_items; a.width = width; a.nq = nq;
+    a.nkv = nkv; a.P = P; a.num_pages = num_pages; a.window = window; a.scale = scale;
+    return d == 128 ? launch<128>(map, a, num_items, stream) : launch<64>(map, a, num_items, stream);
+}

@@ -1,0 +1,81 @@
+// tcgen05 primitives (5th-generation tensor cores with tensor memory) for kernels beside the
+// matrix product: allocation of tensor memory, fences, MMA issue and commit, loads from tensor
+// memory, and the shared-memory and instruction descriptors for bfloat16 operands stored with
+// the 128-byte swizzle.
+#pragma once
+#include <stdint.h>
+
+namespace mhb {
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem]; `accumulate` = 0 overwrites D.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrive on an mbarrier when every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 16 consecutive 32-bit columns of this thread's lane (warp w of a CTA may touch lanes 32*(w%4)..+31).
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Descriptor of a K-major operand tile: rows of 128 bytes (64 bf16 along K), 128-byte swizzle,
+// groups of 8 rows 1024 bytes apart.  A step of 16 elements along K advances the address by 32 bytes.
+__device__ __forceinline__ uint64_t smem_desc_kmajor(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;                 // leading offset: unused for swizzled K-major
+    d |= (uint64_t)(1024 >> 4) << 32;       // stride between 8-row groups
+    d |= (uint64_t)1 << 46;                 // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                 // 128-byte swizzle
+    return d;
+}
+// Descriptor of an MN-major operand tile: each row of 128 bytes holds 64 consecutive elements
+// along M/N for ONE index of K (what a [keys, head_dim] tile is for the product P * V);
+// groups of 8 rows (8 K indices) are `k_group_bytes` apart, the next 64 elements along M/N are
+// `mn_block_bytes` apart.  A step of 16 along K advances the address by 16 rows.
+__device__ __forceinline__ uint64_t smem_desc_mnmajor(uint32_t saddr, uint32_t mn_block_bytes, uint32_t k_group_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((mn_block_bytes >> 4) & 0x3FFF) << 16;    // leading offset: next block along M/N
+    d |= (uint64_t)((k_group_bytes >> 4) & 0x3FFF) << 32;     // stride offset: next 8 rows along K
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor: D float32, A and B bfloat16, A K-major, M = 128, N = n; B MN-major if asked.
+__host__ __device__ constexpr uint32_t umma_idesc(int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(128 >> 4) << 24);
+}
+
+}  // namespace mhb

@@ -418,4 +418,6 @@ class ModelRunner:
                 what.append("a bounded wait in the tensor-core matrix product ran out")
             if bits & 8:
                 what.append("a bounded wait in the TMA-fed attention kernel ran out")
+            if bits & 16:
+                what.append("a bounded wait in the tcgen05 attention kernel ran out")
             raise StepError("; ".join(what) or f"kernel status {bits}")

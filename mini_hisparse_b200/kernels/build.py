@@ -30,7 +30,7 @@ NVCC_FLAGS = [
 ]
 
 # Every module the package has; __graft_entry__.build() compiles all of them.
-MODULES = ("elementwise", "gemm_simt", "gemm_tc", "attention_simt", "attention_mma", "attention_tma", "sampling")
+MODULES = ("elementwise", "gemm_simt", "gemm_tc", "attention_simt", "attention_mma", "attention_tma", "attention_tc", "sampling")
 
 
 class KernelBuildError(RuntimeError):

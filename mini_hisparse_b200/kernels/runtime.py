@@ -29,7 +29,7 @@ class BFloat16Runtime(Runtime):
         self.status = None      # set by the runner: kernels report bounded waits that ran out
 
     def kernel_modules(self):
-        return ("elementwise", "gemm_simt", "gemm_tc", "attention_simt", "attention_mma", "attention_tma", "sampling")
+        return ("elementwise", "gemm_simt", "gemm_tc", "attention_simt", "attention_mma", "attention_tma", "attention_tc", "sampling")
 
     def _splits(self, tiles: int, total_kb: int) -> int:
         """Enough K splits for about two CTAs per SM, none empty, none shorter than 4 K blocks."""

@@ -184,9 +184,17 @@ class GQAttention(Mixer):
         """bfloat16 and a head size the mma kernel is built for; else the CUDA-core kernel."""
         return (self.rt is not None and self.rt.dtype == torch.bfloat16 and self.d in K.MMA_HEAD_DIMS)
 
+    @property
+    def big_tile_rows(self) -> int:
+        """Query rows per tile for long portions: 128 for the tcgen05 kernel, 64 for the mma.sync
+        kernels, 16 for the CUDA-core kernel."""
+        if not self.tensor_core_attention:
+            return ROW_TILE
+        return 128 if self.d in (64, 128) else 64
+
     def cache_need(self):
         return PagedKVNeed(kv_heads=self.nkv, head_dim=self.d, q_heads=self.nq, window=self.window,
-                           tile_rows=64 if self.tensor_core_attention else ROW_TILE)
+                           tile_rows=self.big_tile_rows)
 
     def parameters(self):
         q, kv = self.nq * self.d, self.nkv * self.d
@@ -242,7 +250,16 @@ class GQAttention(Mixer):
                 kernel(*args, meta["items"], n_small, 16, *tail, **common, **extra,
                        tok_nsplit=meta["tok_nsplit"], counters=counters)
             if n_big:
-                kernel(*args, meta["items"][n_small * ITEM_INTS:], n_big, 64, *tail, **common, **extra)
+                big_items = meta["items"][n_small * ITEM_INTS:]
+                if self.big_tile_rows == 128:
+                    if not tma:
+                        raise K.KernelError(
+                            f"attention: pages of {cache.page_size} keys do not divide 64, which the "
+                            f"tensor-core kernels for head_dim {self.d} need")
+                    K.attention_tc(q, cache.storage, attn, big_items, n_big, ctx.positions, meta["block_table"],
+                                   status=ctx.status, **common)
+                else:
+                    kernel(*args, big_items, n_big, 64, *tail, **common, **extra)
         elif n_small + n_big:
             K.attention_simt(*args, meta["items"], n_small + n_big, n_small + n_big, *tail, **common)
         if meta["any_split"] and not self.tensor_core_attention:
