@@ -63,6 +63,12 @@ struct Layout {
     static constexpr int TMEM_COLS = 256;                      // S: 2 x 64 columns, O tile: D columns from column 128
 };
 
+// 2^x by the special-function unit (about 2 ulp; the result is rounded to bfloat16 anyway); 2^-inf = 0
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t swz_addr(uint32_t base, int rows_per_half, int r, int e) {
     return base + (e >> 6) * rows_per_half * 128 + r * 128 + ((((e & 63) >> 3) ^ (r & 7)) << 4);
 }
@@ -210,32 +216,45 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
             ok = mbar_wait(s_full(j & 1), (j >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
-            float s[KT];
-#pragma unroll
-            for (int c = 0; c < KT; c += 16) {
-                uint32_t r[16];
-                tmem_ld16(lane_addr + (j & 1) * KT + c, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int x = 0; x < 16; ++x) s[c + x] = __uint_as_float(r[x]);
-            }
+            uint32_t sr[KT];
+            tmem_ld64(lane_addr + (j & 1) * KT, sr);
+            tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_free(j & 1));
             const int t0 = tile_begin + j * KT;
             float mx = -INFINITY;
+            // most tiles lie wholly inside this row's range of keys: no mask then
+            const int lo = max(kv_begin, a.window > 0 ? qp - a.window + 1 : 0), hi = min(kv_end - 1, qp);
+            if (t0 >= lo && t0 + KT - 1 <= hi) {
 #pragma unroll
-            for (int x = 0; x < KT; ++x) {
-                const int kp = t0 + x;
-                const bool valid = kp >= kv_begin && kp < kv_end && kp <= qp && (a.window <= 0 || kp > qp - a.window);
-                s[x] = valid ? s[x] : -INFINITY;
-                mx = fmaxf(mx, s[x]);
+                for (int x = 0; x < KT; ++x) mx = fmaxf(mx, __uint_as_float(sr[x]));
+            } else {
+#pragma unroll
+                for (int x = 0; x < KT; ++x) {
+                    const int kp = t0 + x;
+                    const float v = (kp >= lo && kp <= hi) ? __uint_as_float(sr[x]) : -INFINITY;
+                    sr[x] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
+                }
             }
             // raise the reference maximum only when the row's maximum outgrew it by more than 2^8
             const bool raise = mx > -INFINITY && (m_ref == -INFINITY || (mx - m_ref) * scale_log2 > 8.f);
             const float m_old = m_ref;
             if (raise) m_ref = mx;
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            // the exponentials (2^(s * c - m * c): one FMA and one ex2 each), packed to bfloat16, while
+            // the previous tile's P V may still run
+            const float m_scaled = m_use * scale_log2;
+            float psum = 0.f;
+            uint32_t pw[KT / 2];
+#pragma unroll
+            for (int x = 0; x < KT; x += 2) {
+                const float p0 = fast_exp2(fmaf(__uint_as_float(sr[x]), scale_log2, -m_scaled));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(sr[x + 1]), scale_log2, -m_scaled));
+                psum += p0 + p1;
+                pw[x >> 1] = pack_bf16(p0, p1);
+            }
             // P (one buffer) and O are only ours once the previous tile's P V has completed
             if (j > 0) {
                 ok = mbar_wait(o_done, (j - 1) & 1);
@@ -258,21 +277,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
                 tmem_st_wait();
                 tc_fence_before();
             }
-            float psum = 0.f;
             const uint32_t prow = p_s + row * 128;
 #pragma unroll
-            for (int ch = 0; ch < KT / 8; ++ch) {
-                float p[8];
-#pragma unroll
-                for (int x = 0; x < 8; ++x) {
-                    p[x] = exp2f((s[ch * 8 + x] - m_use) * scale_log2);
-                    psum += p[x];
-                }
-                const uint32_t w0 = pack_bf16(p[0], p[1]), w1 = pack_bf16(p[2], p[3]);
-                const uint32_t w2 = pack_bf16(p[4], p[5]), w3 = pack_bf16(p[6], p[7]);
+            for (int ch = 0; ch < KT / 8; ++ch)
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + ((ch ^ (row & 7)) << 4)),
-                             "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
-            }
+                             "r"(pw[ch * 4]), "r"(pw[ch * 4 + 1]), "r"(pw[ch * 4 + 2]), "r"(pw[ch * 4 + 3]) : "memory");
             l_run += psum;
             fence_proxy_async();
             __syncwarp();

@@ -100,6 +100,8 @@ def plan_attention(need: PagedKVNeed, segments, T: int, sm_count: int = 148,
             for h0, nh in small_chunks:
                 items.append((si, tok0, nt, h0, nh, b, e, sp))
     n_small = len(items)
+    # long tiles first: the CTAs that walk the most keys must not be the last to start
+    big_items.sort(key=lambda it: it[5] - it[6])
     arr = np.asarray(items + big_items, np.int32).reshape(-1, ITEM_INTS)
     return AttentionPlan(arr, n_small, len(big_items), tok_part_row, tok_nsplit, part_rows)
 
