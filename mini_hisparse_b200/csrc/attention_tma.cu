@@ -1,9 +1,11 @@
-// Causal grouped-query attention over the paged KV cache with TMA-fed key/value tiles.
+// Causal grouped-query attention over the paged KV cache with TMA-fed key/value tiles, for decode
+// tokens and short portions (long portions go to attention_tc.cu).
 //
-// The math, the work items and the two tile shapes are those of attention_mma.cu
-// (mini_hisparse/model.py:173-179, mini_hisparse/attention.py:26-35): 64 query rows per CTA for
-// long portions, 16 rows with the keys of a tile split over the four compute warps for decode
-// tokens, key splits across CTAs merged by the last CTA of a token.  What differs is how keys and
+// The math, the work items and the tile shape are those of attention_mma.cu
+// (mini_hisparse/model.py:173-179, mini_hisparse/attention.py:26-35): 16 query rows per CTA, the
+// keys of a tile split over the four compute warps, key splits across CTAs merged by the last CTA
+// of a token.  (The 64-row shape of the template is kept for reference but not instantiated: the
+// tcgen05 kernel serves every size this one takes.)  What differs is how keys and
 // values reach shared memory: a fifth warp walks the block table and issues one
 // cp.async.bulk.tensor (TMA) per page, plane and 64-column half, with the 128-byte swizzle, into a
 // ring of stages guarded by full/empty mbarriers.  The compute warps never issue a load, so the
@@ -389,7 +391,7 @@ MHB_EXPORT int mhb_attention_tma_supports(int d, int P) {
     return (d == 64 || d == 128) && P >= 2 && P <= KT && KT % P == 0;
 }
 
-// cache: one layer's pool [num_pages, 2, nkv, P, d] bfloat16; rows = 64 or 16 as in attention_mma.
+// cache: one layer's pool [num_pages, 2, nkv, P, d] bfloat16; rows = 16 (items of short segments).
 MHB_EXPORT int mhb_attention_tma(const void* q, const void* cache, void* out, float* part_acc, float* part_ml,
                                  const int* items, int num_items, int launch_items, int rows,
                                  const int* positions, const int* block_table, int width,
@@ -411,7 +413,6 @@ MHB_EXPORT int mhb_attention_tma(const void* q, const void* cache, void* out, fl
     a.tok_nsplit = tok_nsplit; a.counters = counters; a.status = status; a.num_items = num_items;
     a.width = width; a.nq = nq; a.nkv = nkv; a.P = P; a.num_pages = num_pages; a.window = window;
     a.scale = scale;
-    if (rows == 64) return d == 128 ? launch<128, 64>(map, a, launch_items, stream) : launch<64, 64>(map, a, launch_items, stream);
     if (rows == 16) return d == 128 ? launch<128, 16>(map, a, launch_items, stream) : launch<64, 16>(map, a, launch_items, stream);
     return fail("attention_tma: tile height %d", rows);
 }

@@ -295,7 +295,7 @@ def run_attention(nq, nkv, d, P_, seg_specs, dtype, window=None, fixed_nsplit=No
     if edit:
         edit(qs, ks, vs, cache, table)
     T = sum(n for _, n in seg_specs)
-    need = PagedKVNeed(nkv, d, nq, window, tile_rows={"mma": 64, "tma": 64, "tc": 128}.get(kernel, 16))
+    need = PagedKVNeed(nkv, d, nq, window, tile_rows={"mma": 64, "tc": 128}.get(kernel, 16))
     plan = plan_attention(need, segments, T, 148, fixed_nsplit=fixed_nsplit)
     q = torch.cat([qq[h:] for qq, (h, n) in zip(qs, seg_specs)]).reshape(T, nq * d).to(DEV)
     out = torch.full((T, nq * d), float("nan"), dtype=dtype, device=DEV)
@@ -307,8 +307,9 @@ def run_attention(nq, nkv, d, P_, seg_specs, dtype, window=None, fixed_nsplit=No
     tns = torch.from_numpy(plan.tok_nsplit).to(DEV)
     n_items = plan.items.shape[0]
     kw = dict(nq=nq, nkv=nkv, d=d, page_size=P_, window=window or 0)
-    fused = kernel in ("mma", "tma", "tc") and seed % 2 == 0     # the kernel merges its own key splits
-    if kernel in ("mma", "tma", "tc"):
+    # "tc": short segments by the TMA-fed mma kernel, long portions by the tcgen05 kernel (the engine's pairing)
+    fused = kernel in ("mma", "tc") and seed % 2 == 0     # the kernel merges its own key splits
+    if kernel in ("mma", "tc"):
         launch = K().attention_mma if kernel == "mma" else K().attention_tma
         if plan.n_small:
             groups = nq // nkv
@@ -348,18 +349,7 @@ def test_attention_tensor_core_portions_and_decode_mixed(nq, nkv, d, P_):
 
 
 @pytest.mark.parametrize("nq,nkv,d,P_", [(4, 2, 64, 16), (3, 1, 128, 32), (28, 4, 128, 16), (20, 1, 64, 8),
-                                          (6, 3, 128, 64), (40, 2, 128, 4)])
-def test_attention_tma_portions_and_decode_mixed(nq, nkv, d, P_):
-    """The TMA-fed kernel on the same mix: long portions, short ones, offsets inside a page, groups
-    larger than a tile, every page size that divides 64."""
-    specs = [(0, 137), (45, 19), (130, 1), (63, 2), (200, 70), (0, 1), (5, 16)]
-    out, ref, plan = run_attention(nq, nkv, d, P_, specs, torch.bfloat16, kernel="tma")
-    assert plan.n_small and plan.n_big
-    torch.testing.assert_close(out, ref, **tol(torch.bfloat16, 2))
-
-
-@pytest.mark.parametrize("nq,nkv,d,P_", [(4, 2, 64, 16), (3, 1, 128, 32), (28, 4, 128, 16), (20, 1, 64, 8),
-                                          (6, 3, 128, 64), (256, 2, 128, 16)])
+                                          (6, 3, 128, 64), (256, 2, 128, 16), (40, 2, 128, 4)])
 def test_attention_tcgen05_long_portions(nq, nkv, d, P_):
     """The tcgen05 kernel (128-row tiles, S and the O tile in tensor memory) on long portions that
     start at 0 and inside a page, beside short ones that go to the 16-row kernel."""
@@ -369,7 +359,7 @@ def test_attention_tcgen05_long_portions(nq, nkv, d, P_):
     torch.testing.assert_close(out, ref, **tol(torch.bfloat16, 2))
 
 
-@pytest.mark.parametrize("kernel", ["mma", "tma", "tc"])
+@pytest.mark.parametrize("kernel", ["mma", "tc"])
 def test_attention_tensor_core_splits_window_and_far_key(kernel):
     bf = torch.bfloat16
     for seed in (0, 1):      # merged inside the kernel, and by attention_combine
