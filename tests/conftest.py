@@ -38,7 +38,16 @@ TINY_C = dict(
     head_dim=48, rms_norm_eps=3e-6, rope_parameters={"rope_theta": 50000.0, "rope_type": "default"},
     tie_word_embeddings=False, max_position_embeddings=1024,
 )
-TINY = {"A": (TINY_A, 16), "B": (TINY_B, 32), "C": (TINY_C, 16)}
+# A fourth shape that no tensor-core kernel takes in bfloat16: a width that is no multiple of 8
+# (the CUDA-core product), a head size of 80 (the CUDA-core attention), a feed-forward width that
+# is no multiple of 16 (the plain gate/up layout), as many KV heads as query heads, pages of 8.
+TINY_D = dict(
+    architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=1001, hidden_size=100,
+    intermediate_size=150, num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=5,
+    head_dim=80, rms_norm_eps=1e-4, rope_theta=12345.6, tie_word_embeddings=True,
+    max_position_embeddings=300,
+)
+TINY = {"A": (TINY_A, 16), "B": (TINY_B, 32), "C": (TINY_C, 16), "D": (TINY_D, 8)}
 
 
 def pytest_configure(config):

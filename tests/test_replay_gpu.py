@@ -10,7 +10,8 @@ from plain import qwen2_plain as P
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [7, 33, 64, 100, 129, 50], "B": [1, 31, 100, 257, 64, 18], "C": [40, 150, 9, 77, 3, 65]}
+LENGTHS = {"A": [7, 33, 64, 100, 129, 50], "B": [1, 31, 100, 257, 64, 18], "C": [40, 150, 9, 77, 3, 65],
+           "D": [70, 5, 200, 33, 64, 2]}
 
 
 def requests_of(name):
@@ -36,7 +37,7 @@ MODES = {
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_replay_all_cuts(folders, plain_logits, tmp_path, name, dtype):
     requests = requests_of(name)
     page = TINY[name][1]
@@ -48,6 +49,7 @@ def test_replay_all_cuts(folders, plain_logits, tmp_path, name, dtype):
         for mode, steps in plans.items():
             done = {rid: 0 for rid in requests}
             worst = 0.0
+            same = rows_seen = 0
             for entries, end in steps:
                 logits = run.step(entries, end)
                 row = 0
@@ -65,12 +67,13 @@ def test_replay_all_cuts(folders, plain_logits, tmp_path, name, dtype):
                             f"{mode}: request {e['id']} first wrong token at position "
                             f"{done[e['id']] + first} (portion of {n} starting at {done[e['id']]}, "
                             f"page size {page}): {err}") from None
-                    if dtype == "bfloat16":
-                        agree = (got.argmax(-1) == ref.argmax(-1)).float().mean()
-                        assert agree >= 0.9 or n < 10
+                    same += int((got.argmax(-1) == ref.argmax(-1)).sum())
+                    rows_seen += n
                     row += n
                     done[e["id"]] += n
             assert all(done[rid] == len(t) for rid, t in requests.items()), mode
+            # bfloat16 may flip near-ties of the top logit; over a whole mode nine in ten must agree
+            assert same >= (1.0 if dtype == "float32" else 0.9) * rows_seen - (1 if dtype == "float32" else 0), (mode, same, rows_seen)
         assert run.close() == 0
     finally:
         if run.proc.poll() is None:
