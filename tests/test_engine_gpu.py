@@ -95,6 +95,34 @@ def test_long_decoding_and_first_tokens(folders, dtype):
         assert agree > 0.9
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_across_a_block_table_width_step(tmp_path, dtype):
+    """A context that grows past 4,096 tokens (256 pages): the captured decode graph is keyed by the
+    block table's width and has to be captured again at the step; the keys of a token are split
+    over many CTAs.  Every decoded token must be the plain implementation's choice for the
+    engine's own history (or lose to it by a near-tie in bfloat16)."""
+    from mini_hisparse_b200 import Engine, write_random_model
+    from conftest import TINY_A
+
+    cfg = dict(TINY_A, max_position_embeddings=8192)
+    write_random_model(cfg, 21, tmp_path, dtype=torch.bfloat16, matrix_std=0.1)
+    pc, w = P.load_folder(tmp_path)
+    model = load(tmp_path, dtype)
+    prompt = random_tokens(cfg["vocab_size"], 4085, seed=5)
+    engine = Engine(model, num_pages=300, page_size=16, max_requests=2, max_tokens_per_step=2048)
+    engine.add_request("long", prompt, max_new_tokens=24)
+    out = engine.run()["long"]
+    assert len(out) == 24 and len(engine.runner.graphs) >= 2        # two widths were captured
+    logits = P.forward_logits(pc, w, prompt + out)[len(prompt) - 1: -1]
+    picks = logits.argmax(-1).tolist()
+    if dtype == "float32":
+        assert picks == out
+    else:
+        for i, (a, b) in enumerate(zip(out, picks)):
+            gap = float(logits[i].max() - logits[i][a])
+            assert a == b or gap < 0.05 * float(logits[i].abs().max()), (i, a, b, gap)
+
+
 def test_few_pages_requests_wait_and_pages_are_used_again(folders):
     from mini_hisparse_b200 import CapacityError, Engine
 
