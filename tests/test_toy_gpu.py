@@ -1,7 +1,9 @@
 """Generality of the parts: a toy model defined HERE, with a mixer that keeps a state of its own,
-a layer that runs twice, a layer that reads another layer's cache and a layer without position
-encoding, is registered, built from a model folder and stepped in portions, without a change to
-the framework's files.  It is compared with a whole-sequence computation written here."""
+a feed-forward that routes each token to one of two experts, a position encoding of its own
+(rotary with stretched wavelengths), a layer that runs twice, a layer that reads another layer's
+cache and a layer without position encoding, is registered, built from a model folder and stepped
+in portions, without a change to the framework's files.  It is compared with a whole-sequence
+computation written here.  None of these toys is anyone's model."""
 import json
 from dataclasses import dataclass
 
@@ -19,8 +21,53 @@ TOY = dict(architectures=["ToyForCausalLM"], vocab_size=130, hidden_size=48, int
 
 def register_toy():
     from mini_hisparse_b200 import register_architecture
-    from mini_hisparse_b200.parts import (LayerSpec, Mixer, ModelSpec, ParamSpec, PartSpec, Product,
-                                          RunEntry, StateNeed, register_mixer)
+    from mini_hisparse_b200.parts import (FeedForward, LayerSpec, Mixer, ModelSpec, ParamSpec, Part, PartSpec,
+                                          Product, RunEntry, StateNeed, register_feed_forward, register_mixer,
+                                          register_position)
+
+    @register_position("toy_stretched_rotary", replace=True)
+    class StretchedRotary(Part):
+        """Half-split rotation whose wavelengths are `stretch` times longer."""
+
+        rotates = True
+
+        def __init__(self, spec, rt=None):
+            super().__init__(spec, rt)
+            d = spec["head_dim"]
+            inv = spec["theta"] ** (-torch.arange(0, d, 2).float() / d) / spec["stretch"]
+            self.inv_freq = inv.to(rt.device) if rt is not None else inv
+
+    @register_feed_forward("toy_routed", replace=True)
+    class Routed(FeedForward):
+        """Each token goes to the expert with the larger router logit (float32); an expert is
+        a two-matrix ReLU network.  Plain torch on the device: a toy, not a product path."""
+
+        graph_safe = False
+
+        def __init__(self, spec, rt=None):
+            super().__init__(spec, rt)
+            self.h, self.i = spec["hidden_size"], spec["intermediate_size"]
+
+        def parameters(self):
+            p = {"router.weight": ParamSpec((2, self.h))}
+            for e in range(2):
+                p[f"experts.{e}.w1.weight"] = ParamSpec((self.i, self.h))
+                p[f"experts.{e}.w2.weight"] = ParamSpec((self.h, self.i))
+            return p
+
+        def load(self, tensors):
+            self.t = {k: v.float() for k, v in tensors.items()}
+
+        def forward(self, h, ctx):
+            x = h.float()
+            choice = (x @ self.t["router.weight"].T).argmax(-1)
+            out = torch.zeros_like(x)
+            for e in range(2):
+                rows = choice == e
+                out[rows] = torch.relu(x[rows] @ self.t[f"experts.{e}.w1.weight"].T) @ self.t[f"experts.{e}.w2.weight"].T
+            res = ctx.ws.get("toy_ff", tuple(h.shape), ctx.rt.dtype)
+            res.copy_(out)
+            return Product(res)
 
     @register_mixer("toy_running_mean", replace=True)
     class RunningMean(Mixer):
@@ -72,9 +119,12 @@ def register_toy():
             return PartSpec.make("gq_attention", hidden_size=H, q_heads=c["q_heads"], kv_heads=c["kv_heads"],
                                  head_dim=c["head_dim"], qkv_bias=False, window=None, position=position)
 
-        rotary = PartSpec.make("rotary", head_dim=c["head_dim"], theta=c["theta"])
+        rotary = PartSpec.make("toy_stretched_rotary", head_dim=c["head_dim"], theta=c["theta"], stretch=4.0)
+        routed = PartSpec.make("toy_routed", hidden_size=H, intermediate_size=c["intermediate_size"])
         mixers = [attn(rotary), PartSpec.make("toy_running_mean", hidden_size=H), attn(PartSpec.make("none"))]
-        layers = tuple(LayerSpec(f"toy.layers.{i}", "pre_norm", m, norm, ff, norm) for i, m in enumerate(mixers))
+        ffs = [ff, routed, ff]
+        layers = tuple(LayerSpec(f"toy.layers.{i}", "pre_norm", m, norm, f, norm)
+                       for i, (m, f) in enumerate(zip(mixers, ffs)))
         order = (RunEntry(0), RunEntry(1), RunEntry(2), RunEntry(1), RunEntry(2, cache_of=2))
         return ModelSpec("ToyForCausalLM", c["vocab_size"], H,
                          PartSpec.make("token_embedding", vocab_size=c["vocab_size"], hidden_size=H), "toy.embed",
@@ -98,8 +148,10 @@ def toy_reference(w, tokens):
         k = (h @ w[p + "k_proj.weight"].T).view(T, c["kv_heads"], c["head_dim"])
         v = (h @ w[p + "v_proj.weight"].T).view(T, c["kv_heads"], c["head_dim"])
         if rotate:
-            cos, sin = P.rope_tables(pos, c["head_dim"], c["theta"], torch.float32)
-            q, k = P.rotate(q, cos, sin), P.rotate(k, cos, sin)
+            inv = c["theta"] ** (-torch.arange(0, c["head_dim"], 2).float() / c["head_dim"]) / 4.0
+            ang = pos.float()[:, None] * inv[None, :]
+            ang = torch.cat((ang, ang), -1)[:, None, :]
+            q, k = P.rotate(q, ang.cos(), ang.sin()), P.rotate(k, ang.cos(), ang.sin())
         if reuse is not None:
             k, v = shared_kv[reuse]
         shared_kv[entry] = (k, v)
@@ -109,10 +161,21 @@ def toy_reference(w, tokens):
         mean = h.cumsum(0) / torch.arange(1, T + 1)[:, None]
         return mean @ w[f"toy.layers.{i}.self_attn.mix.weight"].T
 
+    def routed(i, h):
+        p = f"toy.layers.{i}.mlp."
+        choice = (h @ w[p + "router.weight"].T).argmax(-1)
+        out = torch.zeros_like(h)
+        for e in range(2):
+            rows = choice == e
+            out[rows] = torch.relu(h[rows] @ w[p + f"experts.{e}.w1.weight"].T) @ w[p + f"experts.{e}.w2.weight"].T
+        return out
+
     def block(i, x, mix):
         p = f"toy.layers.{i}."
         x = x + mix(P.rms_norm(x, w[p + "input_layernorm.weight"], c["eps"]))
         h = P.rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"])
+        if i == 1:
+            return x + routed(i, h)
         return x + P.swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
 
     x = block(0, x, lambda h: attention(0, h, True, 0))
