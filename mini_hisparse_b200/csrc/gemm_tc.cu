@@ -17,6 +17,7 @@
 // Every wait on an mbarrier is bounded; a wait that runs out sets bit 4 of *status and the CTA
 // leaves through the common exit, which frees its tensor memory.
 #include <cuda.h>
+#include <climits>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -57,6 +58,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         if (done) return true;
     }
     return false;
+}
+// One look at the barrier, no waiting.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
 }
 __device__ __forceinline__ void mbar_arrive_plain(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -336,14 +347,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 
-// ---- persistent variant for many tokens ---------------------------------------------------------------
-// One CTA per SM walks over output tiles (128 tokens x bn features, bn any multiple of 16 up to
-// 256, chosen by the host so that the last round of tiles is nearly full).  Tensor memory holds
-// TWO accumulators of 256 columns: while the epilogue warps read one and store it, the MMA warp
-// already fills the other, so the tensor pipe does not wait for the epilogue (which, with the
-// SwiGLU gate, costs a third of a tile's time).  A = activations [M, K], B = weights [N, K].
+// ---- persistent variant for more than 64 tokens -------------------------------------------------------
+// One CTA per SM; tiles of 128 tokens x bn features (bn = 256 unless the matrix is narrower: a
+// 128 x N x 16 MMA with N < 256 is issued no faster than it runs, so narrower tiles only lose).
+// Whole rounds of tiles are dealt round-robin, so that the CTAs of a round read neighbouring
+// tiles and share them in L2.  The tiles of the last, incomplete round are not given to some
+// CTAs while the others idle: their (tile, K block) units are cut into one contiguous range per
+// CTA, all of the same length ("stream-K"), walked after the whole rounds so that the CTAs stay
+// roughly in step along K and keep sharing operand tiles in L2.
+// A tile whose K range is shared is written by all its holders as float32 partial tiles to a
+// workspace; when a CTA has gone through all its work it comes back to its shared tiles (two
+// at most), waits (bounded) for the other holders' parts, and reduces ITS share of the tile's
+// columns: the parts are added in the order of their K ranges, so the sum is deterministic.
+// All CTAs reach that point at about the same time, so the waits are short, and all are
+// resident (one per SM), so nobody waits for a CTA that cannot run.
+// Tensor memory holds TWO accumulators of 256 columns: while the epilogue warps read one, the MMA
+// warp fills the other.  A = activations [M, K], B = weights [N, K].
 constexpr int P_STAGES = 4;
 constexpr int P_BN_MAX = 256;
+constexpr int P_FLAG_CAP = 1 << 16;              // tiles the flag array covers
+constexpr int P_MAX_CTAS = 160;                  // the workspace has two tiles for each
+constexpr uint32_t P_PARTIAL_FLOATS = BM * P_BN_MAX;
 struct PSmem {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = P_BN_MAX * BK * 2;
@@ -352,11 +376,22 @@ struct PSmem {
     static constexpr int TOTAL = BARRIER_OFFSET + (2 * P_STAGES + 4) * 8 + 16 + 1024;
 };
 
+// First unit of CTA c's range: the even cut, moved onto a tile boundary when it falls within
+// `slack` K blocks of one (a sliver of a tile would cost a partial tile for next to no work).
+__host__ __device__ inline long long stream_bound(int c, int grid, long long total_units, int total_kb, int slack) {
+    long long b = (long long)c * total_units / grid;
+    const int r = (int)(b % total_kb);
+    if (r && r <= slack) b -= r;
+    else if (r && total_kb - r <= slack) b += total_kb - r;
+    return b;
+}
+
 template <typename OT, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                           OT* __restrict__ C, int Ra, int Rb, int K, long long ldc, int bn, int tiles_m,
-                          int num_tiles, int* __restrict__ status) {
+                          int whole_tiles, int tail_tiles, int slack, float* __restrict__ partials,
+                          int* __restrict__ flags, int* __restrict__ status) {
     using S = PSmem;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -367,8 +402,23 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     auto acc_full_bar = [&](int b) { return bar_base + 8 * (2 * P_STAGES + b); };
     auto acc_empty_bar = [&](int b) { return bar_base + 8 * (2 * P_STAGES + 2 + b); };
     uint32_t* tmem_slot = (uint32_t*)(smem + S::BARRIER_OFFSET + 8 * (2 * P_STAGES + 4));
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_kb = (K + BK - 1) / BK;
+    // tiles [0, whole_tiles) go round-robin; the units of tiles [whole_tiles, + tail_tiles) are shared
+    const long long total_units = (long long)tail_tiles * total_kb;
+    const long long u_begin = stream_bound(blockIdx.x, gridDim.x, total_units, total_kb, slack);
+    const long long u_end = stream_bound(blockIdx.x + 1, gridDim.x, total_units, total_kb, slack);
+    // segment j of this CTA: a tile and a range of its K blocks; false when there is no more
+    auto segment = [&](int j, long long& u, int& t, int& kb0, int& kb1) -> bool {
+        const long long whole = (long long)blockIdx.x + (long long)j * gridDim.x;
+        if (whole < whole_tiles) { t = (int)whole; kb0 = 0; kb1 = total_kb; return true; }
+        if (u >= u_end) return false;
+        t = whole_tiles + (int)(u / total_kb);
+        kb0 = (int)(u % total_kb);
+        kb1 = (u_end - u < total_kb - kb0) ? kb0 + (int)(u_end - u) : total_kb;
+        u += kb1 - kb0;
+        return true;
+    };
     const uint32_t stage_tx = S::A_BYTES + bn * BK * 2;
 
     pdl_launch_dependents();
@@ -390,10 +440,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
             pdl_wait();
-            int it = 0;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            int it = 0, t, kb0, kb1;
+            long long u = u_begin;
+            for (int j = 0; ok && segment(j, u, t, kb0, kb1); ++j) {
                 const int ra0 = (t % tiles_m) * BM, rb0 = (t / tiles_m) * bn;
-                for (int kb = 0; kb < total_kb; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % P_STAGES;
                     ok = mbar_wait(empty_bar(s), ((it / P_STAGES) & 1) ^ 1);
                     if (!ok) break;
@@ -412,100 +463,201 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = make_idesc(bn);
-            int it = 0, j = 0;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++j) {
+            int it = 0, t, kb0, kb1;
+            long long u = u_begin;
+            for (int j = 0; ok && segment(j, u, t, kb0, kb1); ++j) {
                 const int b = j & 1;
                 ok = mbar_wait(acc_empty_bar(b), ((j >> 1) & 1) ^ 1);     // the epilogue has read this buffer
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc = tmem_base + b * P_BN_MAX;
-                for (int kb = 0; kb < total_kb; ++kb, ++it) {
-                    const int s = it % P_STAGES;
-                    ok = mbar_wait(full_bar(s), (it / P_STAGES) & 1);
+                // The first shared-memory access after an MMA or a commit stalls this thread for some
+                // 250 cycles; a second look right behind it is cheap.  So when the next stage has
+                // landed as well, both are issued in one round (never waiting for the second).
+                for (int kb = kb0; kb < kb1 && ok;) {
+                    const int s0 = it % P_STAGES, s1 = (it + 1) % P_STAGES;
+                    ok = mbar_wait(full_bar(s0), (it / P_STAGES) & 1);
                     if (!ok) break;
+                    const int n = (kb1 - kb >= 2 && mbar_test(full_bar(s1), ((it + 1) / P_STAGES) & 1)) ? 2 : 1;
                     tc_fence_after();
-                    const uint32_t a_addr = smem_base + s * S::STAGE_BYTES;
-                    const uint32_t b_addr = a_addr + S::A_BYTES;
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_bf16(acc, make_smem_desc(a_addr + k * UMMA_K * 2), make_smem_desc(b_addr + k * UMMA_K * 2),
-                                  idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(empty_bar(s));
+                    for (int h = 0; h < 2; ++h) {
+                        if (h < n) {
+                            const uint32_t a_addr = smem_base + (h ? s1 : s0) * S::STAGE_BYTES;
+                            const uint32_t b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+                            for (int k = 0; k < BK / UMMA_K; ++k)
+                                umma_bf16(acc, make_smem_desc(a_addr + k * UMMA_K * 2), make_smem_desc(b_addr + k * UMMA_K * 2),
+                                          idesc, (kb + h > kb0 || k > 0) ? 1u : 0u);
+                            umma_commit(empty_bar(h ? s1 : s0));
+                        }
+                    }
+                    kb += n;
+                    it += n;
                 }
                 if (ok) umma_commit(acc_full_bar(b));
             }
         }
     } else {
         const int quarter = warp & 3;
-        int j = 0;
-        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++j) {
+        const int row_in_tile = quarter * 32 + lane;
+        constexpr int UNIT = EPI == 1 ? 32 : 16;        // columns that are stored together
+        // Store one unit of a row: 16 sums (or 16 gate and 16 up sums) at columns c0.. of tile (ra0, rb0).
+        auto emit = [&](int ra, int rb0, int c0, const uint32_t (&r)[16], const uint32_t (&r2)[16]) {
+            if (ra >= Ra) return;
+            if constexpr (EPI == 1) {
+                OT* row = C + (size_t)ra * ldc + (rb0 + c0) / 2;
+                float v[16];
+#pragma unroll
+                for (int x = 0; x < 16; ++x) v[x] = silu_mul(__uint_as_float(r[x]), __uint_as_float(r2[x]));
+                if (rb0 + c0 + 32 <= Rb && ((uintptr_t)row & 15) == 0 && sizeof(OT) == 2) {
+                    uint32_t p[8];
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) {
+                        __nv_bfloat162 t2 = __floats2bfloat162_rn(v[2 * x], v[2 * x + 1]);
+                        p[x] = *(uint32_t*)&t2;
+                    }
+                    *(uint4*)(row) = make_uint4(p[0], p[1], p[2], p[3]);
+                    *(uint4*)((uint8_t*)row + 16) = make_uint4(p[4], p[5], p[6], p[7]);
+                } else {
+#pragma unroll
+                    for (int x = 0; x < 16; ++x)
+                        if (rb0 + c0 + 16 + x < Rb) store_out<OT>(row + x, v[x]);
+                }
+            } else {
+                OT* row = C + (size_t)ra * ldc + rb0 + c0;
+                if (rb0 + c0 + 16 <= Rb && ((uintptr_t)row & 15) == 0) {
+                    if constexpr (sizeof(OT) == 4) {
+#pragma unroll
+                        for (int x = 0; x < 16; x += 4)
+                            *(uint4*)(row + x) = make_uint4(r[x], r[x + 1], r[x + 2], r[x + 3]);
+                    } else {
+                        uint32_t p[8];
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) {
+                            __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(r[2 * x]), __uint_as_float(r[2 * x + 1]));
+                            p[x] = *(uint32_t*)&v2;
+                        }
+                        *(uint4*)(row) = make_uint4(p[0], p[1], p[2], p[3]);
+                        *(uint4*)(row + 8) = make_uint4(p[4], p[5], p[6], p[7]);
+                    }
+                } else {
+#pragma unroll
+                    for (int x = 0; x < 16; ++x)
+                        if (rb0 + c0 + x < Rb) store_out<OT>(row + x, __uint_as_float(r[x]));
+                }
+            }
+        };
+        // ---- first pass: every segment; a tile that is shared goes to the workspace ----------------
+        int shared_tile[2], shared_count = 0;
+        int t, kb0, kb1;
+        long long u = u_begin;
+        for (int j = 0; ok && segment(j, u, t, kb0, kb1); ++j) {
             const int b = j & 1;
             const int ra0 = (t % tiles_m) * BM, rb0 = (t / tiles_m) * bn;
-            const int ra = ra0 + quarter * 32 + lane;
             ok = mbar_wait(acc_full_bar(b), (j >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
             const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + b * P_BN_MAX;
-            if constexpr (EPI == 1) {
-#pragma unroll 1
-                for (int c0 = 0; c0 < bn; c0 += 32) {
-                    uint32_t g[16], u[16];
-                    tmem_ld16(acc + c0, g);
-                    tmem_ld16(acc + c0 + 16, u);
-                    tmem_ld_wait();
-                    if (ra >= Ra) continue;
-                    OT* row = C + (size_t)ra * ldc + (rb0 + c0) / 2;
-                    float v[16];
-#pragma unroll
-                    for (int x = 0; x < 16; ++x) v[x] = silu_mul(__uint_as_float(g[x]), __uint_as_float(u[x]));
-                    if (rb0 + c0 + 32 <= Rb && ((uintptr_t)row & 15) == 0 && sizeof(OT) == 2) {
-                        uint32_t p[8];
-#pragma unroll
-                        for (int x = 0; x < 8; ++x) {
-                            __nv_bfloat162 t2 = __floats2bfloat162_rn(v[2 * x], v[2 * x + 1]);
-                            p[x] = *(uint32_t*)&t2;
-                        }
-                        *(uint4*)(row) = make_uint4(p[0], p[1], p[2], p[3]);
-                        *(uint4*)((uint8_t*)row + 16) = make_uint4(p[4], p[5], p[6], p[7]);
-                    } else {
-#pragma unroll
-                        for (int x = 0; x < 16; ++x)
-                            if (rb0 + c0 + 16 + x < Rb) store_out<OT>(row + x, v[x]);
-                    }
-                }
-            } else {
+            if (kb0 > 0 || kb1 < total_kb) {
+                // slot 1 holds the part that begins the tile, slot 0 a later part
+                float* mine = partials + (size_t)(2 * blockIdx.x + (kb0 == 0 ? 1 : 0)) * P_PARTIAL_FLOATS;
 #pragma unroll 1
                 for (int c0 = 0; c0 < bn; c0 += 16) {
                     uint32_t r[16];
                     tmem_ld16(acc + c0, r);
                     tmem_ld_wait();
-                    if (ra >= Ra) continue;
-                    OT* row = C + (size_t)ra * ldc + rb0 + c0;
-                    if (rb0 + c0 + 16 <= Rb && ((uintptr_t)row & 15) == 0) {
-                        if constexpr (sizeof(OT) == 4) {
+                    uint4* dst = (uint4*)(mine + ((size_t)(c0 >> 4) * BM + row_in_tile) * 16);
 #pragma unroll
-                            for (int x = 0; x < 16; x += 4)
-                                *(uint4*)(row + x) = make_uint4(r[x], r[x + 1], r[x + 2], r[x + 3]);
-                        } else {
-                            uint32_t p[8];
-#pragma unroll
-                            for (int x = 0; x < 8; ++x) {
-                                __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(r[2 * x]), __uint_as_float(r[2 * x + 1]));
-                                p[x] = *(uint32_t*)&v2;
-                            }
-                            *(uint4*)(row) = make_uint4(p[0], p[1], p[2], p[3]);
-                            *(uint4*)(row + 8) = make_uint4(p[4], p[5], p[6], p[7]);
-                        }
-                    } else {
-#pragma unroll
-                        for (int x = 0; x < 16; ++x)
-                            if (rb0 + c0 + x < Rb) store_out<OT>(row + x, __uint_as_float(r[x]));
-                    }
+                    for (int x = 0; x < 4; ++x) dst[x] = make_uint4(r[4 * x], r[4 * x + 1], r[4 * x + 2], r[4 * x + 3]);
                 }
+                tc_fence_before();
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive_plain(acc_empty_bar(b));
+                    atomicAdd(flags + 4 * t + quarter, 1);      // this quarter of the rows has landed
+                }
+                if (shared_count < 2) shared_tile[shared_count++] = t;
+                continue;
+            }
+#pragma unroll 1
+            for (int c0 = 0; c0 < bn; c0 += UNIT) {
+                uint32_t r[16], r2[16];
+                tmem_ld16(acc + c0, r);
+                if constexpr (EPI == 1) tmem_ld16(acc + c0 + 16, r2);
+                tmem_ld_wait();
+                emit(ra0 + row_in_tile, rb0, c0, r, r2);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_plain(acc_empty_bar(b));    // this warp has read its quarter
+        }
+        // ---- second pass: the shared tiles.  The CTAs that hold parts of a tile divide its columns
+        // among themselves; each adds the parts in the order of their K ranges and stores. ---------
+        for (int i = 0; i < shared_count && ok; ++i) {
+            const int ts = shared_tile[i];
+            const long long u_lo = (long long)(ts - whole_tiles) * total_kb, u_hi = u_lo + total_kb - 1;
+            auto cta_of = [&](long long unit) {
+                int c = (int)(unit * gridDim.x / total_units);
+                while (c + 1 < (int)gridDim.x && stream_bound(c + 1, gridDim.x, total_units, total_kb, slack) <= unit) ++c;
+                while (c > 0 && stream_bound(c, gridDim.x, total_units, total_kb, slack) > unit) --c;
+                return c;
+            };
+            const int c_first = cta_of(u_lo), parts = cta_of(u_hi) - c_first + 1, rank = blockIdx.x - c_first;
+            const volatile int* flag = flags + 4 * ts + quarter;
+            uint32_t spins = 0;
+            while (*flag < parts && ++spins < WAIT_LIMIT) __nanosleep(32);
+            if (spins >= WAIT_LIMIT) { ok = false; break; }
+            __threadfence();
+            const int ra0 = (ts % tiles_m) * BM, rb0 = (ts / tiles_m) * bn;
+#pragma unroll 1
+            for (int c0 = rank * UNIT; c0 < bn; c0 += parts * UNIT) {
+                float s[16], s2[16];
+#pragma unroll
+                for (int x = 0; x < 16; ++x) s[x] = s2[x] = 0.f;
+                // the loads of several parts are in flight together; the sums stay in the parts' order
+                constexpr int BATCH = EPI == 1 ? 2 : 4;
+                for (int p0 = 0; p0 < parts; p0 += BATCH) {
+                    uint4 v[BATCH][4], w[EPI == 1 ? BATCH : 1][4];
+#pragma unroll
+                    for (int q = 0; q < BATCH; ++q) {
+                        const int p = p0 + q < parts ? p0 + q : parts - 1;
+                        const float* src = partials + (size_t)(2 * (c_first + p) + (p == 0 ? 1 : 0)) * P_PARTIAL_FLOATS;
+                        const uint4* a = (const uint4*)(src + ((size_t)(c0 >> 4) * BM + row_in_tile) * 16);
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) v[q][x] = __ldcg(a + x);
+                        if constexpr (EPI == 1) {
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) w[q][x] = __ldcg(a + BM * 4 + x);    // the next 16 columns: the up half
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < BATCH; ++q) {
+                        if (p0 + q < parts) {
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) {
+                                s[4 * x] += __uint_as_float(v[q][x].x); s[4 * x + 1] += __uint_as_float(v[q][x].y);
+                                s[4 * x + 2] += __uint_as_float(v[q][x].z); s[4 * x + 3] += __uint_as_float(v[q][x].w);
+                            }
+                            if constexpr (EPI == 1) {
+#pragma unroll
+                                for (int x = 0; x < 4; ++x) {
+                                    s2[4 * x] += __uint_as_float(w[q][x].x); s2[4 * x + 1] += __uint_as_float(w[q][x].y);
+                                    s2[4 * x + 2] += __uint_as_float(w[q][x].z); s2[4 * x + 3] += __uint_as_float(w[q][x].w);
+                                }
+                            }
+                        }
+                    }
+                }
+                uint32_t r[16], r2[16];
+#pragma unroll
+                for (int x = 0; x < 16; ++x) { r[x] = __float_as_uint(s[x]); r2[x] = __float_as_uint(s2[x]); }
+                emit(ra0 + row_in_tile, rb0, c0, r, r2);
+            }
+            __syncwarp();
+            // the last quarter-warp to have read puts the counter back to zero for the next launch
+            if (lane == 0 && atomicAdd(flags + 4 * ts + quarter, 1) == 2 * parts - 1) flags[4 * ts + quarter] = 0;
         }
     }
     if (!ok && status) atomicOr(status, 4);
@@ -598,7 +750,7 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* C, i
 }
 
 // Tile width (multiple of 16, 128..256; for the SwiGLU epilogue a multiple of 32) that wastes the
-// least of the last round of tiles on `sms` persistent CTAs.
+// least of the last round of whole tiles on `sms` persistent CTAs.
 int choose_persistent_bn(int tiles_m, int N, int sms, int step) {
     int best = 256;
     double best_cost = 1e30;
@@ -611,19 +763,49 @@ int choose_persistent_bn(int tiles_m, int N, int sms, int step) {
     return best;
 }
 
+// `partials` (2 P_MAX_CTAS tiles of 128 x 256 floats) and `flags` (4 P_FLAG_CAP ints, zero; the kernel
+// leaves them zero) let CTAs share a tile's K range; without them the ranges are cut at tile
+// boundaries only.
 template <typename OT, int EPI>
 int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
-                      long long ldc, int* status, cudaStream_t stream) {
+                      long long ldc, float* partials, int* flags, int* status, cudaStream_t stream) {
     static int sms = 0;
     if (!sms) {
         int dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
+        if (sms > P_MAX_CTAS) sms = P_MAX_CTAS;
     }
+    const int step = EPI == 1 ? 32 : 16;
+    int bn = N >= P_BN_MAX ? P_BN_MAX : (N + step - 1) / step * step;
     const int tiles_m = (M + BM - 1) / BM;
-    const int bn = choose_persistent_bn(tiles_m, N, sms, EPI == 1 ? 32 : 16);
-    const int num_tiles = tiles_m * ((N + bn - 1) / bn);
+    long long num_tiles = (long long)tiles_m * ((N + bn - 1) / bn);
+    const int total_kb = (K + BK - 1) / BK;
+    if (num_tiles > INT_MAX / 2) return fail("gemm_tc: too many tiles (%lld)", num_tiles);
+    long long whole_tiles = num_tiles, tail_tiles = 0;
+    int slack = 0;
+    const long long rest = num_tiles % sms;
+    // Share the K range of the tiles of the last round when it would leave a fifth or more of
+    // the SMs idle.  Sharing puts the CTAs out of step along K, so operand tiles are read from
+    // memory more often, and the exchange costs some 15 us: it pays for a long K only.
+    bool share = false;
+    if (partials && flags && num_tiles <= P_FLAG_CAP && num_tiles > sms && rest > 0 &&
+        rest * 5 <= (long long)sms * 4 && total_kb >= 128) {
+        const long long per_cta = rest * total_kb / sms;
+        if (per_cta >= 2) {
+            share = true;
+            tail_tiles = rest;
+            whole_tiles = num_tiles - rest;
+            slack = (int)(per_cta / 4 < 8 ? per_cta / 4 : 8);
+        }
+    }
+    if (!share && N >= P_BN_MAX) {
+        // whole tiles only: a narrower tile may fill the last round better
+        bn = choose_persistent_bn(tiles_m, N, sms, step);
+        num_tiles = whole_tiles = (long long)tiles_m * ((N + bn - 1) / bn);
+    }
+    const long long grid = share ? sms : (num_tiles < sms ? num_tiles : sms);
     CUtensorMap ma, mb;
     int rc;
     if ((rc = make_map(&ma, X, M, K, lda, BM))) return rc;
@@ -635,20 +817,21 @@ int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K
         if (e != cudaSuccess) return fail("gemm_tc: cannot set %d bytes of shared memory: %s", PSmem::TOTAL, cudaGetErrorString(e));
         configured = true;
     }
-    const int grid = num_tiles < sms ? num_tiles : sms;
-    launch_kernel(kern, dim3(grid), dim3(THREADS), PSmem::TOTAL, stream, ma, mb, (OT*)C, M, N, K, ldc, bn, tiles_m,
-                  num_tiles, status);
+    launch_kernel(kern, dim3((unsigned)grid), dim3(THREADS), PSmem::TOTAL, stream, ma, mb, (OT*)C, M, N, K, ldc, bn,
+                  tiles_m, (int)whole_tiles, (int)tail_tiles, slack, partials, flags, status);
     return check_launch("gemm_tc_persistent");
 }
 }  // namespace
 
 // C[M, N] = X[M, K] * W[N, K]^T, bfloat16 in, float32 accumulation, C float32 or bfloat16.
 // swap != 0 streams W through the 128-row operand (few tokens); bn is the tile width along the
-// other operand (16..256).  Requirements (else an error, never a wrong result): K % 8 == 0,
+// other operand (16..256), or 0 for the persistent kernel (which then takes `partials` and `flags`,
+// see launch_persistent; both may be null).  Requirements (else an error, never a wrong result): K % 8 == 0,
 // lda % 8 == 0, ldw % 8 == 0, pointers 16-byte aligned.
 MHB_EXPORT int mhb_gemm_tc(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
                            long long lda, long long ldw, long long ldc, int swap, int bn, int nsplit,
-                           long long split_stride, int* status, cudaStream_t stream) {
+                           long long split_stride, float* partials, int* flags, int* status,
+                           cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || lda % 8 || ldw % 8) return fail("gemm_tc: K, lda and ldw must be multiples of 8 (K %d, lda %lld, ldw %lld)", K, lda, ldw);
     if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return fail("gemm_tc: operands must be 16-byte aligned");
@@ -666,9 +849,10 @@ MHB_EXPORT int mhb_gemm_tc(const void* X, const void* W, void* C, int c_dtype, i
         if (c_dtype == MHB_F32) return dispatch_bn<true, float, 0>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
         return dispatch_bn<true, __nv_bfloat16, 0>(bn, ma, mb, C, N, M, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
     }
-    if (nsplit == 1 && bn == 256 && M >= 256) {       // many tokens: the persistent kernel
-        if (c_dtype == MHB_F32) return launch_persistent<float, 0>(X, W, C, M, N, K, lda, ldw, ldc, status, stream);
-        return launch_persistent<__nv_bfloat16, 0>(X, W, C, M, N, K, lda, ldw, ldc, status, stream);
+    if (bn == 0) {       // the persistent kernel picks its own tiles
+        if (nsplit != 1) return fail("gemm_tc: the persistent kernel takes no split K");
+        if (c_dtype == MHB_F32) return launch_persistent<float, 0>(X, W, C, M, N, K, lda, ldw, ldc, partials, flags, status, stream);
+        return launch_persistent<__nv_bfloat16, 0>(X, W, C, M, N, K, lda, ldw, ldc, partials, flags, status, stream);
     }
     if ((rc = make_map(&ma, X, M, K, lda, BM))) return rc;
     if ((rc = make_map(&mb, W, N, K, ldw, bn))) return rc;
@@ -679,8 +863,8 @@ MHB_EXPORT int mhb_gemm_tc(const void* X, const void* W, void* C, int c_dtype, i
 // act[M, I] = silu(X Wg^T) * (X Wu^T) where W [2 I, K] holds gate and up rows interleaved in
 // blocks of 16 (see the kernel).  I must be a multiple of 16; no split K.
 MHB_EXPORT int mhb_gemm_tc_swiglu(const void* X, const void* W, void* C, int c_dtype, int M, int I, int K,
-                                  long long lda, long long ldw, long long ldc, int swap, int bn, int* status,
-                                  cudaStream_t stream) {
+                                  long long lda, long long ldw, long long ldc, int swap, int bn, float* partials,
+                                  int* flags, int* status, cudaStream_t stream) {
     if (M <= 0 || I <= 0) return 0;
     if (I % 16) return fail("gemm_tc_swiglu: the intermediate size %d must be a multiple of 16", I);
     if (K <= 0 || K % 8 || lda % 8 || ldw % 8) return fail("gemm_tc: K, lda and ldw must be multiples of 8 (K %d, lda %lld, ldw %lld)", K, lda, ldw);
@@ -695,8 +879,8 @@ MHB_EXPORT int mhb_gemm_tc_swiglu(const void* X, const void* W, void* C, int c_d
         if ((rc = make_map(&mb, X, M, K, lda, bn))) return rc;
         return dispatch_bn<true, __nv_bfloat16, 1>(bn, ma, mb, C, N, M, K, ldc, 1, total_kb, 0, 1, status, stream);
     }
-    if (bn == 256 && M >= 256)
-        return launch_persistent<__nv_bfloat16, 1>(X, W, C, M, N, K, lda, ldw, ldc, status, stream);
+    if (bn == 0)
+        return launch_persistent<__nv_bfloat16, 1>(X, W, C, M, N, K, lda, ldw, ldc, partials, flags, status, stream);
     if ((rc = make_map(&ma, X, M, K, lda, BM))) return rc;
     if ((rc = make_map(&mb, W, N, K, ldw, bn))) return rc;
     return dispatch_bn<false, __nv_bfloat16, 1>(bn, ma, mb, C, M, N, K, ldc, 1, total_kb, 0, 2, status, stream);

@@ -136,11 +136,32 @@ def gemm_simt(a, w, out, bias=None, nsplit=1, split_stride=0):
         c_int(nsplit), c_longlong(split_stride), _stream()), "gemm_simt")
 
 
-def gemm_tc(a, w, out, *, swap: bool, bn: int, nsplit=1, split_stride=0, status=None):
+STREAM_K_PARTIAL_FLOATS = 2 * 160 * 128 * 256     # workspace of the persistent product: two tiles per CTA
+STREAM_K_FLAGS = 4 << 16                            # a counter for each quarter of each tile
+
+
+def stream_k_scratch(device):
+    """(partials, flags) for the persistent product: CTAs that share a tile's K range exchange
+    float32 partial tiles through ``partials`` and count in ``flags`` (zero before and after)."""
+    return (torch.empty(STREAM_K_PARTIAL_FLOATS, dtype=torch.float32, device=device),
+            torch.zeros(STREAM_K_FLAGS, dtype=torch.int32, device=device))
+
+
+def _scratch_ptrs(scratch):
+    if scratch is None:
+        return c_void_p(None), c_void_p(None)
+    partials, flags = scratch
+    if partials.numel() < STREAM_K_PARTIAL_FLOATS or flags.numel() < STREAM_K_FLAGS:
+        raise KernelError("gemm_tc: the stream-K scratch is too small")
+    return _ptr(partials), _ptr(flags)
+
+
+def gemm_tc(a, w, out, *, swap: bool, bn: int, nsplit=1, split_stride=0, status=None, scratch=None):
     """out[M, N] = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulate).
 
     ``swap`` streams the weights through the 128-row operand (for few tokens, M <= bn <= 64);
-    ``bn`` is the tile width along the other operand."""
+    ``bn`` is the tile width along the other operand, or 0 for the persistent kernel (more than
+    64 tokens), which balances its CTAs over tiles and K with ``scratch`` from stream_k_scratch()."""
     lib = build.load("gemm_tc")
     M, K = a.shape
     N = w.shape[0]
@@ -155,11 +176,11 @@ def gemm_tc(a, w, out, *, swap: bool, bn: int, nsplit=1, split_stride=0, status=
     _check(lib, lib.mhb_gemm_tc(
         _ptr(a), _ptr(w), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K),
         c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(-2)),
-        c_int(1 if swap else 0), c_int(bn), c_int(nsplit), c_longlong(split_stride), _ptr(status),
-        _stream()), "gemm_tc")
+        c_int(1 if swap else 0), c_int(bn), c_int(nsplit), c_longlong(split_stride),
+        *_scratch_ptrs(scratch), _ptr(status), _stream()), "gemm_tc")
 
 
-def gemm_tc_swiglu(a, w, out, *, swap: bool, bn: int, status=None):
+def gemm_tc_swiglu(a, w, out, *, swap: bool, bn: int, status=None, scratch=None):
     """out[M, I] = silu(a Wg^T) * (a Wu^T); ``w`` [2 I, K] holds gate and up rows interleaved in
     blocks of 16 (rows 32j..32j+15 gate, 32j+16..32j+31 up)."""
     lib = build.load("gemm_tc")
@@ -174,7 +195,7 @@ def gemm_tc_swiglu(a, w, out, *, swap: bool, bn: int, status=None):
     _check(lib, lib.mhb_gemm_tc_swiglu(
         _ptr(a), _ptr(w), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(I), c_int(K),
         c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
-        c_int(1 if swap else 0), c_int(bn), _ptr(status), _stream()), "gemm_tc_swiglu")
+        c_int(1 if swap else 0), c_int(bn), *_scratch_ptrs(scratch), _ptr(status), _stream()), "gemm_tc_swiglu")
 
 
 def attention_simt(q, cache, out, part_acc, part_ml, items, num_items, max_items, positions,

@@ -1,9 +1,10 @@
 """The runtime of each compute dtype: which kernel a part's matrix product runs on.
 
 float32: the CUDA-core product (true 32-bit: FFMA, no tensor core, no reduced-precision mode).
-bfloat16: the tcgen05 tensor-core product; with few tokens the weights stream through the
+bfloat16: the tcgen05 tensor-core product; with up to 64 tokens the weights stream through the
 128-row operand and the K range is split over enough CTAs to fill the GPU (the consumer sums
-the partial matrices in order).  Shapes the tensor-core kernel refuses (K or a row stride not a
+the partial matrices in order); with more, a persistent kernel gives every SM the same share
+of (tile, K block) units.  Shapes the tensor-core kernel refuses (K or a row stride not a
 multiple of 8) go to the CUDA-core product, which takes any shape.
 """
 from __future__ import annotations
@@ -27,6 +28,12 @@ class BFloat16Runtime(Runtime):
         super().__init__(device, dtype)
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.status = None      # set by the runner: kernels report bounded waits that ran out
+        self._scratch = None    # workspace of the persistent product, made at its first use
+
+    def scratch(self):
+        if self._scratch is None:
+            self._scratch = K.stream_k_scratch(self.device)
+        return self._scratch
 
     def kernel_modules(self):
         return ("elementwise", "gemm_simt", "gemm_tc", "attention_simt", "attention_mma", "attention_tma", "attention_tc", "sampling")
@@ -59,10 +66,10 @@ class BFloat16Runtime(Runtime):
         out = ws.get(name, (M, I), self.dtype)
         if block == self.GATE_BLOCK and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0:
             if M <= 64:
-                swap, bn = True, (16 if M <= 16 else 32 if M <= 32 else 64)
+                K.gemm_tc_swiglu(x, weight, out, swap=True, bn=(16 if M <= 16 else 32 if M <= 32 else 64),
+                                 status=self.status)
             else:
-                swap, bn = False, 256
-            K.gemm_tc_swiglu(x, weight, out, swap=swap, bn=bn, status=self.status)
+                K.gemm_tc_swiglu(x, weight, out, swap=False, bn=0, status=self.status, scratch=self.scratch())
             return out
         gu = self.linear(x, weight, ws, name + "_gu")
         K.swiglu(gu.tensor, out, nsplit=gu.nsplit, split_stride=gu.split_stride, block=block)
@@ -81,14 +88,24 @@ class BFloat16Runtime(Runtime):
             K.gemm_simt(x, weight, out, bias=bias)
             return Product(out)
         total_kb = -(-Kd // BK)
+        tiles256 = -(-M // 128) * -(-N // 256)
+        if M > 64 and (2 * tiles256 >= self.sm_count or not allow_split):
+            # the persistent kernel: tiles of 128 tokens x 256, its CTAs share the last tiles' K range
+            out = ws.get(name, (M, N), out_dtype)
+            K.gemm_tc(x, weight, out, swap=False, bn=0, status=self.status, scratch=self.scratch())
+            return Product(out)
         if M <= 64:
             swap, bn = True, (16 if M <= 16 else 32 if M <= 32 else 64)
-            tiles = -(-N // 128)
+            nsplit = self._splits(-(-N // 128), total_kb) if allow_split else 1
         else:
-            swap = False
-            bn = 256 if -(-M // 128) * -(-N // 256) >= self.sm_count or N >= 8192 else 128
-            tiles = -(-M // 128) * -(-N // bn)
-        nsplit = self._splits(tiles, total_kb) if allow_split else 1
+            # too few tiles for the SMs: cut K so that one round of CTAs covers them; up to 256
+            # tokens ride as the narrow operand of one tile
+            swap = M <= 256
+            bn = 128 if M <= 128 else 256
+            tiles = -(-N // 128) if swap else tiles256
+            nsplit = max(1, min(self.sm_count // tiles, total_kb // MIN_KB_PER_SPLIT))
+            kb_per = -(-total_kb // nsplit)
+            nsplit = -(-total_kb // kb_per)
         if nsplit > 1:
             out = ws.get(name, (nsplit, M, N), torch.float32)
             K.gemm_tc(x, weight, out, swap=swap, bn=bn, nsplit=nsplit, split_stride=out.stride(0),

@@ -150,7 +150,39 @@ def test_gemm_tensor_core(M, N, K_, swap, bn, nsplit, out_dtype):
         torch.testing.assert_close(got, ref, atol=1e-2 * float(ref.abs().max()), rtol=1e-2)
 
 
+@pytest.mark.parametrize("M,N,K_", [(65, 64, 64), (128, 128, 64), (200, 300, 136), (333, 1000, 3584), (100, 7168, 1024),
+                                    (2048, 2000, 512), (1024, 520, 13824), (700, 4608, 3584), (129, 40, 8192),
+                                    (2048, 2600, 8192), (1100, 5000, 8256), (2300, 2304, 8960)])
+@pytest.mark.parametrize("shared", [True, False])
+@pytest.mark.parametrize("out_dtype", DTYPES)
+def test_gemm_persistent(M, N, K_, shared, out_dtype):
+    """The persistent product: ragged edges, fewer tiles than SMs, and (the last three shapes: a
+    long K and a last round that fills a part of the SMs) CTAs that share tiles' K ranges through
+    the workspace; the same shapes without a workspace.  Twice in a row: the flags are left zero."""
+    a = rnd(M, K_, dtype=torch.bfloat16, seed=1)
+    w = rnd(N, K_, dtype=torch.bfloat16, seed=2)
+    ref = a.float() @ w.float().T
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scratch = K().stream_k_scratch(DEV) if shared else None
+    outs = []
+    for _ in range(2):
+        out = torch.full((M + 1, N), float("nan"), dtype=out_dtype, device=DEV)
+        K().gemm_tc(a, w, out[:M], swap=False, bn=0, status=status, scratch=scratch)
+        assert bool(out[M].isnan().all())
+        outs.append(out[:M].float())
+    assert int(status) == 0
+    if shared:
+        assert int(scratch[1].abs().sum()) == 0
+    assert torch.equal(outs[0], outs[1])                 # the order of the sums is fixed
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(outs[0], ref, atol=3e-5 * math.sqrt(K_) * 4, rtol=2e-5)
+    else:
+        torch.testing.assert_close(outs[0], ref, atol=1e-2 * float(ref.abs().max()), rtol=1e-2)
+
+
 @pytest.mark.parametrize("M,I,K_,swap,bn", [(200, 176, 64, False, 256), (2048, 1184, 512, False, 256),
+                                              (200, 176, 64, False, 0), (2048, 1184, 512, False, 0), (130, 2000, 3584, False, 0),
+                                              (2048, 1312, 8192, False, 0),
                                               (8, 176, 96, True, 16), (33, 304, 3584, True, 64), (1, 18944, 128, True, 16)])
 def test_gemm_tensor_core_swiglu_epilogue(M, I, K_, swap, bn):
     """silu(x Wg^T) * (x Wu^T) written by the product's epilogue from block-interleaved weights."""
@@ -160,7 +192,8 @@ def test_gemm_tensor_core_swiglu_epilogue(M, I, K_, swap, bn):
     w = torch.stack((gate.view(I // 16, 16, K_), up.view(I // 16, 16, K_)), 1).reshape(2 * I, K_).contiguous()
     out = torch.full((M + 1, I), float("nan"), dtype=torch.bfloat16, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    K().gemm_tc_swiglu(x, w, out[:M], swap=swap, bn=bn, status=status)
+    K().gemm_tc_swiglu(x, w, out[:M], swap=swap, bn=bn, status=status,
+                       scratch=K().stream_k_scratch(DEV) if bn == 0 else None)
     g, u = x.float() @ gate.float().T, x.float() @ up.float().T
     ref = g * torch.sigmoid(g) * u
     assert int(status) == 0 and bool(out[M].isnan().all())
