@@ -9,15 +9,21 @@
 //                    K-major in shared memory (TMA, 128-byte swizzle); S lands in tensor memory.
 //   softmax          four warps, ONE QUERY ROW PER THREAD: tcgen05.ld brings the row's 64 scores into
 //                    registers, so maximum and sum need no shuffles; scores, exponentials and sums
-//                    are float32; P goes to shared memory as bfloat16 (K-major, swizzled).
-//   O += P V         tcgen05.mma, M = 128, N = head_dim, K = 64, accumulated in tensor memory; the
-//                    value tile [keys, head_dim] is the MN-major operand exactly as TMA wrote it.
+//                    are float32; P goes back to tensor memory as bfloat16 (tcgen05.st), over the
+//                    first half of the score buffer it came from.
+//   O += P V         tcgen05.mma with P as the operand in tensor memory, M = 128, N = head_dim,
+//                    K = 64, accumulated in tensor memory; the value tile [keys, head_dim] is the
+//                    MN-major operand exactly as TMA wrote it.
 // The running maximum that the exponentials refer to is only raised when a row's true maximum has
 // grown by more than 2^8 (so p <= 256, exact enough in bfloat16 and float32); only then the row's
 // accumulator in tensor memory is rescaled (tcgen05.ld, multiply, tcgen05.st).  That is rare after
 // the first tiles, so a softmax thread normally touches 64 scores per tile and nothing else.
-// Two S buffers let the MMA warp compute the next tile's scores while the softmax warps work; two
-// CTAs share an SM (tensor memory 2 x 256 columns), so one CTA's softmax overlaps the other's MMAs.
+// Two S buffers let the MMA warp compute the next tile's scores while the softmax warps work, and
+// since each tile's P has a buffer of its own the softmax warps never wait for a P V product
+// (except to rescale).  Keys and values travel in rings of their own (three key tiles, two value
+// tiles): a key tile is free as soon as its scores are done, long before its values are used, so
+// the loads run two tiles ahead.  Two CTAs share an SM (tensor memory 2 x 256 columns), so one
+// CTA's softmax overlaps the other's MMAs.
 // Warp 0 issues the TMA loads, warp 1 owns tensor memory and issues the MMAs, warps 2-5 are the
 // softmax warps.  Every mbarrier wait is bounded (status bit 16 when one runs out).
 //
@@ -33,7 +39,6 @@ MHB_EXPORT const char* mhb_last_error() { return error_buffer(); }
 namespace {
 constexpr int ROWS = 128;
 constexpr int KT = 64;
-constexpr int STAGES = 2;
 constexpr int THREADS = 192;
 constexpr int ITEM_INTS = 8;
 
@@ -48,19 +53,20 @@ struct AttnArgs {
     float scale;
 };
 
+constexpr int K_STAGES = 3;
+constexpr int V_STAGES = 2;
+
 template <int D>
 struct Layout {
     static constexpr int HALVES = D / 64;
     static constexpr int Q_BYTES = HALVES * ROWS * 128;
-    static constexpr int K_BYTES = HALVES * KT * 128;          // also V
-    static constexpr int STAGE_BYTES = 2 * K_BYTES;
-    static constexpr int P_BYTES = ROWS * 128;                 // one P buffer: 128 rows x 64 keys
-    static constexpr int KV_OFFSET = Q_BYTES;
-    static constexpr int P_OFFSET = KV_OFFSET + STAGES * STAGE_BYTES;
-    static constexpr int BAR_OFFSET = P_OFFSET + P_BYTES;
-    static constexpr int NUM_BARS = 2 * STAGES + 1 + 2 + 2 + 1 + 1;   // kv full/empty, q, s full/free, p full, o done
+    static constexpr int K_BYTES = HALVES * KT * 128;          // one key tile; a value tile has the same size
+    static constexpr int K_OFFSET = Q_BYTES;
+    static constexpr int V_OFFSET = K_OFFSET + K_STAGES * K_BYTES;
+    static constexpr int BAR_OFFSET = V_OFFSET + V_STAGES * K_BYTES;
+    static constexpr int NUM_BARS = 2 * K_STAGES + 2 * V_STAGES + 1 + 2 + 2 + 3;   // k, v full/empty, q, s full, p full, o done, o final
     static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16;
-    static constexpr int TMEM_COLS = 256;                      // S: 2 x 64 columns, O tile: D columns from column 128
+    static constexpr int TMEM_COLS = 256;                      // S/P: 2 x 64 columns, O tile: D columns from column 128
 };
 
 // 2^x by the special-function unit (about 2 ulp; the result is rounded to bfloat16 anyway); 2^-inf = 0
@@ -80,24 +86,34 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
     constexpr int HALVES = L::HALVES;
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t base = smem_addr(smem);
-    const uint32_t q_s = base, kv_s = base + L::KV_OFFSET, p_s = base + L::P_OFFSET;
+    const uint32_t q_s = base, k_ring = base + L::K_OFFSET, v_ring = base + L::V_OFFSET;
     const uint32_t bars = base + L::BAR_OFFSET;
-    auto kv_full = [&](int s) { return bars + 8 * s; };
-    auto kv_empty = [&](int s) { return bars + 8 * (STAGES + s); };
-    const uint32_t q_full = bars + 8 * (2 * STAGES);
-    auto s_full = [&](int b) { return bars + 8 * (2 * STAGES + 1 + b); };
-    auto s_free = [&](int b) { return bars + 8 * (2 * STAGES + 3 + b); };
-    const uint32_t p_full = bars + 8 * (2 * STAGES + 5);
-    const uint32_t o_done = bars + 8 * (2 * STAGES + 6);
+    auto k_full = [&](int s) { return bars + 8 * s; };
+    auto k_empty = [&](int s) { return bars + 8 * (K_STAGES + s); };
+    auto v_full = [&](int s) { return bars + 8 * (2 * K_STAGES + s); };
+    auto v_empty = [&](int s) { return bars + 8 * (2 * K_STAGES + V_STAGES + s); };
+    constexpr int B0 = 2 * K_STAGES + 2 * V_STAGES;
+    const uint32_t q_full = bars + 8 * B0;
+    auto s_full = [&](int b) { return bars + 8 * (B0 + 1 + b); };
+    // a softmax warp may be one tile ahead of another, so P(j) and P(j + 1) have barriers of their own
+    auto p_full = [&](int b) { return bars + 8 * (B0 + 3 + b); };
+    // P V(j) has completed: a barrier for even and one for odd tiles, since the waiting threads are
+    // not in step with the value warp and a parity wait cannot tell phases two apart
+    auto o_done = [&](int b) { return bars + 8 * (B0 + 5 + b); };
+    const uint32_t o_final = bars + 8 * (B0 + 7);     // the last P V has completed
     uint32_t* tmem_slot = (uint32_t*)(smem + L::BAR_OFFSET + 8 * L::NUM_BARS);
 
     pdl_launch_dependents();
     pdl_wait();
-    if ((int)blockIdx.x >= a.num_items) return;
-    const int* it = a.items + (size_t)blockIdx.x * ITEM_INTS;
+    // CTAs start in the order of the linear block index: item-major, so that the longest items (the
+    // planner sorts them first) of ALL KV heads start first
+    const int linear = blockIdx.x;
+    const int item = linear / a.nkv;
+    if (item >= a.num_items) return;
+    const int* it = a.items + (size_t)item * ITEM_INTS;
     const int seg = it[0], tok0 = it[1], ntok = it[2], head0 = it[3], nheads = it[4];
     const int kv_begin = it[5], kv_end = it[6];
-    const int kvh = blockIdx.y;
+    const int kvh = linear % a.nkv;
     const int groups = a.nq / a.nkv;
     const int nrows = ntok * nheads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -106,11 +122,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
     const int ntiles = kv_end > kv_begin ? (kv_end - tile_begin + KT - 1) / KT : 0;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
+        for (int s = 0; s < K_STAGES; ++s) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); }
+        for (int s = 0; s < V_STAGES; ++s) { mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1); }
         mbar_init(q_full, 4);
-        for (int b = 0; b < 2; ++b) { mbar_init(s_full(b), 1); mbar_init(s_free(b), 4); }
-        mbar_init(p_full, 4);
-        mbar_init(o_done, 1);
+        for (int b = 0; b < 2; ++b) mbar_init(s_full(b), 1);
+        for (int b = 0; b < 2; ++b) mbar_init(p_full(b), 4);
+        for (int b = 0; b < 2; ++b) mbar_init(o_done(b), 1);
+        mbar_init(o_final, 1);
         mbar_fence_init();
     }
     if (warp == 1) tmem_alloc(smem_addr(tmem_slot), L::TMEM_COLS);
@@ -121,13 +139,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
     bool ok = true;
 
     if (warp == 0) {
-        // ---- TMA warp: one lane per page of a tile; every page slot of a stage is filled ------------
+        // ---- TMA warp: one lane per page of a tile; every page slot of a stage is filled.  Keys run
+        // one tile ahead of values: K(j + 1) is asked for before V(j). -----------------------------
         const int pages_per_tile = KT / a.P;
-        for (int j = 0; j < ntiles && ok; ++j) {
-            const int stage = j % STAGES;
-            if (lane == 0) ok = mbar_wait(kv_empty(stage), ((j / STAGES) & 1) ^ 1);
+        auto load = [&](int j, bool values) {
+            const int stage = values ? j % V_STAGES : j % K_STAGES;
+            const int round = values ? j / V_STAGES : j / K_STAGES;
+            const uint32_t full = values ? v_full(stage) : k_full(stage);
+            if (lane == 0) ok = mbar_wait(values ? v_empty(stage) : k_empty(stage), (round & 1) ^ 1);
             ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
+            if (!ok) return;
             const int kp0 = tile_begin + j * KT + lane * a.P;
             int page = -1;
             if (lane < pages_per_tile) {
@@ -136,25 +157,33 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
                 if (page >= a.num_pages) page = -1;
             }
             const unsigned have = __ballot_sync(0xffffffffu, page >= 0);
-            if (lane == 0) mbar_expect_tx(kv_full(stage), __popc(have) * 2 * a.P * D * 2);
+            if (lane == 0) mbar_expect_tx(full, __popc(have) * a.P * D * 2);
             __syncwarp();
             if (page >= 0) {
-                const int row0 = ((page * 2) * a.nkv + kvh) * a.P;
-                const uint32_t dst = kv_s + stage * L::STAGE_BYTES + lane * a.P * 128;
+                const int row0 = ((page * 2 + (values ? 1 : 0)) * a.nkv + kvh) * a.P;
+                const uint32_t dst = (values ? v_ring : k_ring) + stage * L::K_BYTES + lane * a.P * 128;
 #pragma unroll
-                for (int h = 0; h < HALVES; ++h) {
-                    tma_load_2d(dst + h * KT * 128, &kv_map, h * 64, row0, kv_full(stage));
-                    tma_load_2d(dst + L::K_BYTES + h * KT * 128, &kv_map, h * 64, row0 + a.nkv * a.P, kv_full(stage));
-                }
+                for (int h = 0; h < HALVES; ++h) tma_load_2d(dst + h * KT * 128, &kv_map, h * 64, row0, full);
             }
+        };
+        if (ntiles > 0) load(0, false);
+        for (int j = 0; j < ntiles && ok; ++j) {
+            if (j + 1 < ntiles) load(j + 1, false);
+            if (ok) load(j, true);
         }
     } else if (warp == 1) {
         // ---- MMA warp ----------------------------------------------------------------------------------
+        // One thread issues all products, in the order S(0), S(1), then per tile P V(j), S(j + 2).
+        // S(j + 2) overwrites the columns of S(j) and P(j): the softmax warps have read S(j) (they have
+        // announced P(j)), and P V(j), which reads P(j), was issued before it by the same thread, and
+        // the tensor pipe runs one thread's products in order.  A thread that has issued MMAs pays
+        // some 250 cycles for the first barrier it looks at afterwards and little for the next ones,
+        // so all of a tile's waits come first and its eight to twelve MMAs follow in one go.
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc(KT, false);      // S: N = 64 keys, both operands K-major
             constexpr uint32_t idesc_o = umma_idesc(D, true);        // O tile: N = head_dim, V is MN-major
-            auto issue_s = [&](int j) {          // S(j) = Q K(j)^T into S buffer j & 1
-                const uint32_t k_s = kv_s + (j % STAGES) * L::STAGE_BYTES;
+            auto issue_s = [&](int j) {
+                const uint32_t k_s = k_ring + (j % K_STAGES) * L::K_BYTES;
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
                     const uint64_t da = smem_desc_kmajor(q_s + (k >> 2) * (ROWS * 128) + (k & 3) * 32);
@@ -162,32 +191,29 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
                     umma_bf16(tmem + (j & 1) * KT, da, db, idesc_s, k > 0 ? 1u : 0u);
                 }
                 umma_commit(s_full(j & 1));
+                umma_commit(k_empty(j % K_STAGES));     // the key tile is free once its scores are done
             };
             ok = mbar_wait(q_full, 0);
-            if (ok && ntiles > 0) {
-                ok = mbar_wait(kv_full(0), 0);
-                if (ok) { tc_fence_after(); issue_s(0); }
+            for (int j = 0; j < 2 && j < ntiles && ok; ++j) {
+                ok = mbar_wait(k_full(j), 0);
+                if (ok) { tc_fence_after(); issue_s(j); }
             }
             for (int j = 0; j < ntiles && ok; ++j) {
-                if (j + 1 < ntiles) {
-                    ok = mbar_wait(kv_full((j + 1) % STAGES), ((j + 1) / STAGES) & 1);
-                    if (ok) ok = mbar_wait(s_free((j + 1) & 1), (((j + 1) >> 1) & 1) ^ 1);   // softmax has read S(j - 1)
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_s(j + 1);
-                }
-                ok = mbar_wait(p_full, j & 1);          // P(j) is in shared memory, O is rescaled if needed
+                ok = mbar_wait(p_full(j & 1), (j >> 1) & 1);         // P(j) is in tensor memory, O is rescaled if needed
+                if (ok) ok = mbar_wait(v_full(j % V_STAGES), (j / V_STAGES) & 1);
+                if (ok && j + 2 < ntiles) ok = mbar_wait(k_full((j + 2) % K_STAGES), ((j + 2) / K_STAGES) & 1);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t v_s = kv_s + (j % STAGES) * L::STAGE_BYTES + L::K_BYTES;
+                const uint32_t v_s = v_ring + (j % V_STAGES) * L::K_BYTES;
 #pragma unroll
                 for (int k = 0; k < KT / 16; ++k) {
-                    const uint64_t da = smem_desc_kmajor(p_s + k * 32);
                     const uint64_t db = smem_desc_mnmajor(v_s + k * 16 * 128, KT * 128, 1024);
-                    umma_bf16(tmem + 128, da, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                    umma_bf16_tmem_a(tmem + 128, tmem + (j & 1) * KT + k * 8, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
                 }
-                umma_commit(o_done);                    // P and O are free again when this completes
-                umma_commit(kv_empty(j % STAGES));      // K(j) and V(j) are consumed
+                umma_commit(o_done(j & 1));             // O holds tiles 0..j when this completes
+                umma_commit(v_empty(j % V_STAGES));     // V(j) is consumed
+                if (j + 1 == ntiles) umma_commit(o_final);
+                if (j + 2 < ntiles) issue_s(j + 2);
             }
         }
     } else {
@@ -219,9 +245,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
             uint32_t sr[KT];
             tmem_ld64(lane_addr + (j & 1) * KT, sr);
             tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_free(j & 1));
             const int t0 = tile_begin + j * KT;
             float mx = -INFINITY;
             // most tiles lie wholly inside this row's range of keys: no mask then
@@ -255,14 +278,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
                 psum += p0 + p1;
                 pw[x >> 1] = pack_bf16(p0, p1);
             }
-            // P (one buffer) and O are only ours once the previous tile's P V has completed
-            if (j > 0) {
-                ok = mbar_wait(o_done, (j - 1) & 1);
-                if (!ok) break;
-                tc_fence_after();
-            }
             const bool rescale = raise && m_old > -INFINITY;     // there is an accumulator to rescale
             if (__any_sync(0xffffffffu, rescale)) {
+                // O is only ours once the previous tile's P V has completed
+                ok = mbar_wait(o_done((j - 1) & 1), ((j - 1) >> 1) & 1);
+                if (!ok) break;
+                tc_fence_after();
                 const float alpha = rescale ? exp2f((m_old - m_use) * scale_log2) : 1.f;
                 l_run *= alpha;
 #pragma unroll
@@ -274,20 +295,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
                     for (int x = 0; x < 16; ++x) r[x] = __float_as_uint(__uint_as_float(r[x]) * alpha);
                     tmem_st16(lane_addr + 128 + c, r);
                 }
-                tmem_st_wait();
-                tc_fence_before();
             }
-            const uint32_t prow = p_s + row * 128;
-#pragma unroll
-            for (int ch = 0; ch < KT / 8; ++ch)
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + ((ch ^ (row & 7)) << 4)),
-                             "r"(pw[ch * 4]), "r"(pw[ch * 4 + 1]), "r"(pw[ch * 4 + 2]), "r"(pw[ch * 4 + 3]) : "memory");
+            // P(j) over the first 32 columns of S(j)'s buffer: column i holds keys 2i and 2i + 1
+            tmem_st32(lane_addr + (j & 1) * KT, pw);
+            tmem_st_wait();
             l_run += psum;
-            fence_proxy_async();
+            tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
+            if (lane == 0) mbar_arrive(p_full(j & 1));
         }
-        if (ok && ntiles > 0) ok = mbar_wait(o_done, (ntiles - 1) & 1);
+        if (ok && ntiles > 0) ok = mbar_wait(o_final, 0);
         tc_fence_after();
         if (ok) {
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -335,7 +352,7 @@ int launch(const CUtensorMap& map, const AttnArgs& a, int launch_items, cudaStre
         cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         configured = true;
     }
-    launch_kernel(kern, dim3(launch_items, a.nkv), dim3(THREADS), smem, stream, map, a);
+    launch_kernel(kern, dim3((unsigned)launch_items * a.nkv), dim3(THREADS), smem, stream, map, a);
     return check_launch("attention_tc");
 }
 }  // namespace
