@@ -285,6 +285,92 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, int nsplit, size_
     }
 }
 
+// The same with four elements per thread (head sizes are multiples of 8 and every row, bias and
+// cache row is 16-byte aligned then): 16-byte loads, 8- or 16-byte stores.
+template <typename IT>
+__device__ __forceinline__ float4 load4_split(const IT* p, size_t idx, int nsplit, size_t split_stride) {
+    float4 v = load4<IT>(p + idx);
+    for (int s = 1; s < nsplit; ++s) {
+        const float4 w = load4<IT>(p + idx + (size_t)s * split_stride);
+        v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+    }
+    return v;
+}
+
+template <typename IT, typename QT, typename CT>
+__global__ void rope_append_vec_kernel(const IT* __restrict__ qkv, int nsplit, size_t split_stride,
+                                       const float* __restrict__ bias, const int* __restrict__ positions,
+                                       const int* __restrict__ tok_seg, const int* __restrict__ block_table,
+                                       int table_width, const float* __restrict__ inv_freq,
+                                       QT* __restrict__ q_out, CT* __restrict__ cache, int nq, int nkv,
+                                       int d, int P, int num_pages, int write_kv, int rotate_q_k,
+                                       int heads_per_block, int* __restrict__ status) {
+    extern __shared__ __align__(16) float cs_table[];      // cos[d/2], sin[d/2] of this token's position
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = d >> 1, quarter = d >> 3;             // quarter: groups of 4 in a half
+    const int width = (nq + 2 * nkv) * d;
+    const size_t base = (size_t)t * width;
+    const int head_begin = blockIdx.y * heads_per_block;
+    const int head_end = min(nq + 2 * nkv, head_begin + heads_per_block);
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn = 0.f, cs = 1.f;
+        if (rotate_q_k) sincosf((float)pos * inv_freq[i], &sn, &cs);
+        cs_table[i] = cs;
+        cs_table[half + i] = sn;
+    }
+    int page = -1;
+    if (write_kv && head_end > nq) {
+        page = block_table[(size_t)tok_seg[t] * table_width + pos / P];
+        if (page < 0 || page >= num_pages) {  // never write outside the pool
+            if (threadIdx.x == 0 && status) atomicOr(status, 2);
+            page = -1;
+        }
+    }
+    const int within = pos % P;
+    __syncthreads();
+    const int rot_end = min(head_end, nq + nkv);
+    for (int idx = head_begin * quarter + threadIdx.x; idx < rot_end * quarter; idx += blockDim.x) {
+        const int head = idx / quarter, i = (idx - head * quarter) * 4;
+        const int col = head * d + i;
+        float4 a = load4_split(qkv, base + col, nsplit, split_stride);
+        float4 b = load4_split(qkv, base + col + half, nsplit, split_stride);
+        if (bias) {
+            const float4 ba = *(const float4*)(bias + col), bb = *(const float4*)(bias + col + half);
+            a.x += ba.x; a.y += ba.y; a.z += ba.z; a.w += ba.w;
+            b.x += bb.x; b.y += bb.y; b.z += bb.z; b.w += bb.w;
+        }
+        const float4 cs = *(const float4*)(cs_table + i), sn = *(const float4*)(cs_table + half + i);
+        const float4 oa = make_float4(a.x * cs.x - b.x * sn.x, a.y * cs.y - b.y * sn.y, a.z * cs.z - b.z * sn.z,
+                                      a.w * cs.w - b.w * sn.w);
+        const float4 ob = make_float4(b.x * cs.x + a.x * sn.x, b.y * cs.y + a.y * sn.y, b.z * cs.z + a.z * sn.z,
+                                      b.w * cs.w + a.w * sn.w);
+        if (head < nq) {
+            store4<QT>(q_out + (size_t)t * nq * d + col, oa);
+            store4<QT>(q_out + (size_t)t * nq * d + col + half, ob);
+        } else if (page >= 0) {
+            CT* dst = cache + ((((size_t)page * 2 + 0) * nkv + (head - nq)) * P + within) * d;
+            store4<CT>(dst + i, oa);
+            store4<CT>(dst + i + half, ob);
+        }
+    }
+    if (page >= 0) {
+        const int v_begin = max(head_begin, nq + nkv);
+        const int dq = d >> 2;
+        for (int idx = v_begin * dq + threadIdx.x; idx < head_end * dq; idx += blockDim.x) {
+            const int head = idx / dq, e = (idx - head * dq) * 4;
+            float4 v = load4_split(qkv, base + (size_t)head * d + e, nsplit, split_stride);
+            if (bias) {
+                const float4 bv = *(const float4*)(bias + head * d + e);
+                v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+            }
+            store4<CT>(cache + ((((size_t)page * 2 + 1) * nkv + (head - nq - nkv)) * P + within) * d + e, v);
+        }
+    }
+}
+
 MHB_EXPORT int mhb_rope_append(const void* qkv, int in_dtype, int nsplit, long long split_stride,
                                const float* bias, const int* positions, const int* tok_seg,
                                const int* block_table, int table_width, const float* inv_freq,
@@ -303,6 +389,16 @@ MHB_EXPORT int mhb_rope_append(const void* qkv, int in_dtype, int nsplit, long l
     blocks_y = (heads + hpb - 1) / hpb;
     dim3 grid(T, blocks_y);
     const size_t smem = sizeof(float) * d;
+    const bool aligned = d % 8 == 0 && split_stride % 4 == 0 && (((uintptr_t)qkv | (uintptr_t)bias | (uintptr_t)q_out |
+                                                                  (uintptr_t)cache) & 15) == 0;
+    if (aligned) {
+        MHB_DISPATCH_DTYPE(in_dtype, IT, MHB_DISPATCH_DTYPE(act_dtype, AT,
+            launch_kernel(rope_append_vec_kernel<IT, AT, AT>, dim3(grid), dim3(threads), smem, stream,
+                (const IT*)qkv, nsplit, (size_t)split_stride, bias, positions, tok_seg, block_table,
+                table_width, inv_freq, (AT*)q_out, (AT*)cache, nq, nkv, d, P, num_pages, write_kv,
+                rotate, hpb, status)));
+        return check_launch("rope_append");
+    }
     MHB_DISPATCH_DTYPE(in_dtype, IT, MHB_DISPATCH_DTYPE(act_dtype, AT,
         launch_kernel(rope_append_kernel<IT, AT, AT>, dim3(grid), dim3(threads), smem, stream, 
             (const IT*)qkv, nsplit, (size_t)split_stride, bias, positions, tok_seg, block_table,
