@@ -81,3 +81,33 @@ def test_7b_layer_sizes_all_cuts(folder, reference, dtype):
         assert agree > 0.9
     assert runner.stats["graph_steps"] >= 20
     cache.assert_invariants()
+
+
+def test_7b_layer_sizes_long_prompt_shares_tiles_along_k(folder):
+    """2,304 tokens in one step, bfloat16: the down projection (K = 18944) has 252 tiles for 148 SMs,
+    so the CTAs of the persistent product share the last round's tiles along K and reduce them
+    through the workspace; the prompt also spans 36 key tiles in the tcgen05 attention kernel."""
+    from mini_hisparse_b200 import CacheConfig, CacheManager, load_model
+    from mini_hisparse_b200.engine import ModelRunner, StepEntry
+
+    torch.backends.cuda.matmul.allow_tf32 = False
+    cfg, w = P.load_folder(folder, dtype=torch.float32, device="cuda:0")
+    tokens = random_tokens(CONFIG["vocab_size"], 2304, seed=11)
+    want = list(range(0, 2304, 7)) + [2303]
+    ref = P.forward_logits(cfg, w, tokens)[want].cpu()
+    model = load_model(folder, dtype="bfloat16")
+    cache = CacheManager(model.cache_needs, CacheConfig(num_pages=160, page_size=16, max_requests=2,
+                                                        dtype=model.rt.dtype))
+    runner = ModelRunner(model, cache)
+    cache.open("long")
+    outs = []
+    for _ in range(2):          # twice: the workspace counters are back at zero after a step
+        cache.close("long")
+        cache.open("long")
+        outs.append(runner.step([StepEntry("long", tokens, want)]).float().cpu().clone())
+    runner.check_status()
+    assert int(model.rt.scratch()[1].abs().sum()) == 0
+    assert torch.equal(outs[0], outs[1])
+    torch.testing.assert_close(outs[0], ref, atol=0.03 * float(ref.abs().max()), rtol=0.03)
+    assert (outs[0].argmax(-1) == ref.argmax(-1)).float().mean() > 0.9
+    cache.assert_invariants()
