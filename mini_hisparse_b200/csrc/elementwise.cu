@@ -107,7 +107,9 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
     *(uint2*)p = u;
 }
 
-template <typename DT, typename OT>
+// VC vectors per thread: 4 for many rows; 1 for few rows (a decode step), where the kernel's time is
+// the chain of memory round trips of one thread and more threads make that chain shorter.
+template <typename DT, typename OT, int VC>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const DT* __restrict__ delta, int nsplit,
                                        size_t split_stride, const float* __restrict__ weight, float eps,
                                        const int* __restrict__ rows, OT* __restrict__ out, int H) {
@@ -119,16 +121,23 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const DT* __restri
     float* xr = x + (size_t)s * H;
     const bool write_back = (delta != nullptr) && (rows == nullptr);
     const int nvec = H >> 2;
-    float4 v[VEC_CACHE];
+    float4 v[VC];
     float ss = 0.f;
 #pragma unroll
-    for (int c = 0; c < VEC_CACHE; ++c) {
+    for (int c = 0; c < VC; ++c) {
         const int i = threadIdx.x + c * blockDim.x;
         if (i < nvec) {
             float4 a = *(const float4*)(xr + 4 * i);
             if (delta) {
                 const DT* dp = delta + (size_t)s * H + 4 * i;
                 int sp = 0;
+                for (; sp + 8 <= nsplit; sp += 8) {      // eight loads in flight; summed in order
+                    float4 d[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) d[q] = load4<DT>(dp + (size_t)(sp + q) * split_stride);
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) { a.x += d[q].x; a.y += d[q].y; a.z += d[q].z; a.w += d[q].w; }
+                }
                 for (; sp + 4 <= nsplit; sp += 4) {      // four loads in flight; summed in order
                     const float4 d0 = load4<DT>(dp + (size_t)(sp + 0) * split_stride);
                     const float4 d1 = load4<DT>(dp + (size_t)(sp + 1) * split_stride);
@@ -153,7 +162,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const DT* __restri
     const float rstd = rsqrtf(total / (float)H + eps);
     OT* o = out + (size_t)r * H;
 #pragma unroll
-    for (int c = 0; c < VEC_CACHE; ++c) {
+    for (int c = 0; c < VC; ++c) {
         const int i = threadIdx.x + c * blockDim.x;
         if (i < nvec) {
             const float4 w = *(const float4*)(weight + 4 * i);
@@ -185,9 +194,16 @@ MHB_EXPORT int mhb_add_rmsnorm(float* x, const void* delta, int delta_dtype, int
                          ((uintptr_t)out & 15) == 0 && ((uintptr_t)delta & 15) == 0 && split_stride % 4 == 0;
     int vthreads = ((H / 4 + VEC_CACHE - 1) / VEC_CACHE + 31) / 32 * 32;
     if (vthreads < 64) vthreads = 64;
+    const int wide = (H / 4 + 31) / 32 * 32;          // threads when each takes one vector
+    if (aligned && R <= 128 && wide <= 1024 && wide >= 64) {
+        MHB_DISPATCH_DTYPE(delta_dtype, DT, MHB_DISPATCH_DTYPE(out_dtype, OT,
+            launch_kernel((add_rmsnorm_vec_kernel<DT, OT, 1>), dim3(R), dim3(wide), 0, stream,
+                x, (const DT*)delta, nsplit, (size_t)split_stride, weight, eps, rows, (OT*)out, H)));
+        return check_launch("add_rmsnorm");
+    }
     if (aligned && vthreads <= 1024) {
         MHB_DISPATCH_DTYPE(delta_dtype, DT, MHB_DISPATCH_DTYPE(out_dtype, OT,
-            launch_kernel(add_rmsnorm_vec_kernel<DT, OT>, dim3(R), dim3(vthreads), 0, stream, 
+            launch_kernel((add_rmsnorm_vec_kernel<DT, OT, VEC_CACHE>), dim3(R), dim3(vthreads), 0, stream,
                 x, (const DT*)delta, nsplit, (size_t)split_stride, weight, eps, rows, (OT*)out, H)));
         return check_launch("add_rmsnorm");
     }
@@ -290,7 +306,15 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, int nsplit, size_
 template <typename IT>
 __device__ __forceinline__ float4 load4_split(const IT* p, size_t idx, int nsplit, size_t split_stride) {
     float4 v = load4<IT>(p + idx);
-    for (int s = 1; s < nsplit; ++s) {
+    int s = 1;
+    for (; s + 4 <= nsplit; s += 4) {       // four loads in flight; summed in order
+        float4 w[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) w[q] = load4<IT>(p + idx + (size_t)(s + q) * split_stride);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { v.x += w[q].x; v.y += w[q].y; v.z += w[q].z; v.w += w[q].w; }
+    }
+    for (; s < nsplit; ++s) {
         const float4 w = load4<IT>(p + idx + (size_t)s * split_stride);
         v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
     }
