@@ -41,6 +41,8 @@ struct AttnArgs {
     int* counters;
     int* status;
     int num_items, width, nq, nkv, P, num_pages, window;
+    int fresh;      // keys at positions > positions[tok0] - fresh may have been written by the kernel
+                    // before this one (the append of this step); 0: any key may
     float scale;
 };
 
@@ -77,8 +79,11 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
     __shared__ int row_pos[ROWS];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
 
+    // Programmatic dependent launch: this kernel may start while the append of this step's keys
+    // still runs.  Work items, positions and the block table were copied in before the step's first
+    // kernel, and all keys but the step's own are older still, so everything up to the first tile
+    // that may hold a fresh key (and the queries) is done before waiting for the append.
     pdl_launch_dependents();
-    pdl_wait();
     if ((int)blockIdx.x >= a.num_items) return;
     const int* it = a.items + (size_t)blockIdx.x * ITEM_INTS;
     const int seg = it[0], tok0 = it[1], ntok = it[2], head0 = it[3], nheads = it[4];
@@ -106,10 +111,15 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
     if (warp == CWARPS) {
         // ---- TMA warp: one lane per page of the tile ----------------------------------------------
         const int pages_per_tile = KT / a.P;
-        bool ok = true;
+        bool ok = true, waited = false;
+        const int first_fresh = a.fresh > 0 ? a.positions[tok0] - (a.fresh - 1) : -0x7fffffff;
         for (int itile = 0; itile < ntiles && ok; ++itile) {
             const int stage = itile % STAGES;
             const uint32_t phase = (itile / STAGES) & 1;
+            if (!waited && tile_begin + (itile + 1) * KT > first_fresh) {
+                pdl_wait();
+                waited = true;
+            }
             if (lane == 0) ok = mbar_wait(empty_bar(stage), phase ^ 1);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
@@ -141,6 +151,8 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
     }
 
     // ---- compute warps ---------------------------------------------------------------------------------
+    if (tid < ROWS) row_pos[tid] = tid < nrows ? a.positions[tok0 + tid / nheads] : -1;
+    pdl_wait();         // the queries come from the kernel before this one
     for (int c = tid; c < ROWS * (D / 8); c += CWARPS * 32) {
         const int r = c / (D / 8), ch = c % (D / 8);
         const bool live = r < nrows;
@@ -149,7 +161,6 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
         cp_async16(swz(q_s, ROWS, r, ch * 8), src, live ? 16 : 0);
     }
     cp_async_commit();
-    if (tid < ROWS) row_pos[tid] = tid < nrows ? a.positions[tok0 + tid / nheads] : -1;
     cp_async_wait<0>();
     compute_sync();
 
@@ -392,11 +403,14 @@ MHB_EXPORT int mhb_attention_tma_supports(int d, int P) {
 }
 
 // cache: one layer's pool [num_pages, 2, nkv, P, d] bfloat16; rows = 16 (items of short segments).
+// fresh: the kernel launched before this one may have written the keys of the last `fresh` positions
+// up to an item's first token (and later ones); older keys are loaded without waiting for it.
+// 0: it may have written any key.
 MHB_EXPORT int mhb_attention_tma(const void* q, const void* cache, void* out, float* part_acc, float* part_ml,
                                  const int* items, int num_items, int launch_items, int rows,
                                  const int* positions, const int* block_table, int width,
                                  const int* tok_part_row, const int* tok_nsplit, int* counters, int nq, int nkv,
-                                 int d, int P, int num_pages, int window, float scale, int* status,
+                                 int d, int P, int num_pages, int window, int fresh, float scale, int* status,
                                  cudaStream_t stream) {
     if (launch_items <= 0) return 0;
     if (nkv <= 0 || nq % nkv) return fail("attention: %d query heads over %d KV heads", nq, nkv);
@@ -413,6 +427,7 @@ MHB_EXPORT int mhb_attention_tma(const void* q, const void* cache, void* out, fl
     a.tok_nsplit = tok_nsplit; a.counters = counters; a.status = status; a.num_items = num_items;
     a.width = width; a.nq = nq; a.nkv = nkv; a.P = P; a.num_pages = num_pages; a.window = window;
     a.scale = scale;
+    a.fresh = fresh;
     if (rows == 16) return d == 128 ? launch<128, 16>(map, a, launch_items, stream) : launch<64, 16>(map, a, launch_items, stream);
     return fail("attention_tma: tile height %d", rows);
 }

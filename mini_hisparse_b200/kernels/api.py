@@ -241,8 +241,12 @@ def attention_tma_supports(d: int, page_size: int) -> bool:
 
 def attention_tma(q, cache, out, part_acc, part_ml, items, num_items, rows, positions, block_table,
                   tok_part_row, *, nq, nkv, d, page_size, window=0, scale=None, tok_nsplit=None,
-                  counters=None, status=None):
-    """attention_mma with keys and values staged by TMA through a ring of mbarrier-guarded stages."""
+                  counters=None, status=None, fresh=0):
+    """attention_mma with keys and values staged by TMA through a ring of mbarrier-guarded stages.
+
+    ``fresh``: how many positions before an item's first token the kernel launched just before this
+    one may have written (the append of the step's own keys); older keys are requested while that
+    kernel still runs.  0: it may have written any key."""
     lib = build.load("attention_tma")
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("attention_tma: q and the cache must be bfloat16")
@@ -254,7 +258,7 @@ def attention_tma(q, cache, out, part_acc, part_ml, items, num_items, rows, posi
         _ptr(q), _ptr(cache), _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(items), c_int(num_items),
         c_int(num_items), c_int(rows), _ptr(positions), _ptr(block_table), c_int(block_table.shape[-1]),
         _ptr(tok_part_row), _ptr(tok_nsplit), _ptr(counters), c_int(nq), c_int(nkv), c_int(d),
-        c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(status),
+        c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_int(fresh), c_float(scale), _ptr(status),
         _stream()), "attention_tma")
 
 

@@ -249,7 +249,10 @@ class GQAttention(Mixer):
             if n_small:
                 chunks = -(-(self.nq // self.nkv) // ROW_TILE)
                 counters = ws.get_zeroed("attn_counters", (T * self.nkv * chunks,), torch.int32)
-                kernel(*args, meta["items"], n_small, 16, *tail, **common, **extra,
+                # short segments have at most SPLIT_MAX_TOKENS tokens: only the keys that close to a
+                # token's position can come from this step's append, the kernel launched just before
+                fresh = {"fresh": SPLIT_MAX_TOKENS} if tma else {}
+                kernel(*args, meta["items"], n_small, 16, *tail, **common, **extra, **fresh,
                        tok_nsplit=meta["tok_nsplit"], counters=counters)
             if n_big:
                 big_items = meta["items"][n_small * ITEM_INTS:]
