@@ -40,7 +40,7 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None,
-                    help="timed decode steps (default 32; 4 for the reference arm, whose steps take seconds)")
+                    help="timed decode steps (default 64; 4 for the reference arm, whose steps take seconds)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
@@ -52,7 +52,7 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.steps is None:
-        args.steps = 4 if args.impl == "reference" else 32
+        args.steps = 4 if args.impl == "reference" else 64
     if args.impl == "reference":
         return reference_arm(args)
     args.warmup = max(args.warmup, 3)

@@ -115,12 +115,18 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const DT* __restri
                                        const int* __restrict__ rows, OT* __restrict__ out, int H) {
     __shared__ float scratch[33];
     pdl_launch_dependents();
+    const int nvec = H >> 2;
+    // few rows: the weights (constant) are fetched while the kernel before this one still runs; with
+    // many rows the registers are worth more
+    float4 wv = make_float4(0.f, 0.f, 0.f, 0.f);
+    if constexpr (VC == 1) {
+        if ((int)threadIdx.x < nvec) wv = *(const float4*)(weight + 4 * threadIdx.x);
+    }
     pdl_wait();
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
     float* xr = x + (size_t)s * H;
     const bool write_back = (delta != nullptr) && (rows == nullptr);
-    const int nvec = H >> 2;
     float4 v[VC];
     float ss = 0.f;
 #pragma unroll
@@ -165,7 +171,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const DT* __restri
     for (int c = 0; c < VC; ++c) {
         const int i = threadIdx.x + c * blockDim.x;
         if (i < nvec) {
-            const float4 w = *(const float4*)(weight + 4 * i);
+            const float4 w = VC == 1 ? wv : *(const float4*)(weight + 4 * i);
             float4 a = v[c];
             a.x = (a.x * rstd) * w.x; a.y = (a.y * rstd) * w.y;
             a.z = (a.z * rstd) * w.z; a.w = (a.w * rstd) * w.w;
@@ -330,8 +336,9 @@ __global__ void rope_append_vec_kernel(const IT* __restrict__ qkv, int nsplit, s
                                        int d, int P, int num_pages, int write_kv, int rotate_q_k,
                                        int heads_per_block, int* __restrict__ status) {
     extern __shared__ __align__(16) float cs_table[];      // cos[d/2], sin[d/2] of this token's position
+    // positions, segments and the block table were copied in before the step's first kernel: the
+    // rotation table and the page are worked out while the kernel before this one still runs
     pdl_launch_dependents();
-    pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int half = d >> 1, quarter = d >> 3;             // quarter: groups of 4 in a half
@@ -355,6 +362,7 @@ __global__ void rope_append_vec_kernel(const IT* __restrict__ qkv, int nsplit, s
     }
     const int within = pos % P;
     __syncthreads();
+    pdl_wait();
     const int rot_end = min(head_end, nq + nkv);
     for (int idx = head_begin * quarter + threadIdx.x; idx < rot_end * quarter; idx += blockDim.x) {
         const int head = idx / quarter, i = (idx - head * quarter) * 4;
