@@ -27,7 +27,9 @@
 // Warp 0 issues the TMA loads, warp 1 owns tensor memory and issues the MMAs, warps 2-5 are the
 // softmax warps.  Every mbarrier wait is bounded (status bit 16 when one runs out).
 //
-// Needs head_dim 64 or 128 and a page size that divides 64; items are never split along the keys.
+// Needs head_dim 64 or 128 and a page size that divides 64.  An item may cover a part of its keys
+// (the planner splits long tiles when there are too few of them for the GPU): it then leaves its
+// unnormalised sums for attention_combine.
 #include "mma_helpers.cuh"
 #include "tc_helpers.cuh"
 #include "tma_helpers.cuh"
@@ -48,6 +50,9 @@ struct AttnArgs {
     const int* items;
     const int* positions;
     const int* block_table;
+    const int* tok_part_row;     // for items that cover a part of their keys (split >= 0)
+    float* part_acc;             // [rows, nq, d] unnormalised sums
+    float* part_ml;              // [rows, nq, 2] reference maximum (scaled) and sum of exponentials
     int* status;
     int num_items, width, nq, nkv, P, num_pages, window;
     float scale;
@@ -112,7 +117,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
     if (item >= a.num_items) return;
     const int* it = a.items + (size_t)item * ITEM_INTS;
     const int seg = it[0], tok0 = it[1], ntok = it[2], head0 = it[3], nheads = it[4];
-    const int kv_begin = it[5], kv_end = it[6];
+    const int kv_begin = it[5], kv_end = it[6], split = it[7];
+    if (split >= 0 && (!a.part_acc || !a.part_ml || !a.tok_part_row)) {     // nowhere to put a part: refuse
+        if (threadIdx.x == 0 && a.status) atomicOr(a.status, 16);
+        return;
+    }
     const int kvh = linear % a.nkv;
     const int groups = a.nq / a.nkv;
     const int nrows = ntok * nheads;
@@ -306,7 +315,32 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
         }
         if (ok && ntiles > 0) ok = mbar_wait(o_final, 0);
         tc_fence_after();
-        if (ok) {
+        if (ok && split >= 0) {
+            // a part of the keys: the unnormalised sums, the reference maximum and the sum of the
+            // exponentials go to the partial buffers; attention_combine merges the parts in order
+            const size_t prow = live ? (size_t)a.tok_part_row[t] + split : 0;
+            float* dst = a.part_acc + (prow * a.nq + hq) * D;
+#pragma unroll
+            for (int c = 0; c < D; c += 16) {
+                uint32_t r[16];
+                if (ntiles > 0) {
+                    tmem_ld16(lane_addr + 128 + c, r);      // warp-wide: every lane takes part
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int x = 0; x < 16; ++x) r[x] = 0;
+                }
+                if (live) {
+#pragma unroll
+                    for (int x = 0; x < 16; x += 4) *(uint4*)(dst + c + x) = make_uint4(r[x], r[x + 1], r[x + 2], r[x + 3]);
+                }
+            }
+            if (live) {
+                float* ml = a.part_ml + (prow * a.nq + hq) * 2;
+                ml[0] = (l_run > 0.f && m_ref > -INFINITY) ? m_ref * a.scale : -INFINITY;
+                ml[1] = l_run;
+            }
+        } else if (ok) {
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             __nv_bfloat16* dst = a.out + ((size_t)t * a.nq + hq) * D;
 #pragma unroll
@@ -361,10 +395,13 @@ MHB_EXPORT int mhb_attention_tc_supports(int d, int P) {
     return (d == 64 || d == 128) && P >= 2 && P <= KT && KT % P == 0;
 }
 
-// Items must be planned for tiles of 128 rows and carry split = -1.  cache: one layer's pool
+// Items must be planned for tiles of 128 rows.  An item with split >= 0 covers a part of its keys
+// and writes to row tok_part_row[token] + split of the partial buffers (as the other attention
+// kernels do; attention_combine merges); split = -1 writes the output.  cache: one layer's pool
 // [num_pages, 2, nkv, P, d] bfloat16.
 MHB_EXPORT int mhb_attention_tc(const void* q, const void* cache, void* out, const int* items, int num_items,
-                                const int* positions, const int* block_table, int width, int nq, int nkv, int d,
+                                const int* positions, const int* block_table, int width,
+                                const int* tok_part_row, float* part_acc, float* part_ml, int nq, int nkv, int d,
                                 int P, int num_pages, int window, float scale, int* status, cudaStream_t stream) {
     if (num_items <= 0) return 0;
     if (nkv <= 0 || nq % nkv) return fail("attention: %d query heads over %d KV heads", nq, nkv);
@@ -377,7 +414,8 @@ MHB_EXPORT int mhb_attention_tc(const void* q, const void* cache, void* out, con
     if (rc) return rc;
     AttnArgs a;
     a.q = (const __nv_bfloat16*)q; a.out = (__nv_bfloat16*)out; a.items = items; a.positions = positions;
-    a.block_table = block_table; a.status = status; a.num_items = num_items; a.width = width; a.nq = nq;
+    a.block_table = block_table; a.tok_part_row = tok_part_row; a.part_acc = part_acc; a.part_ml = part_ml;
+    a.status = status; a.num_items = num_items; a.width = width; a.nq = nq;
     a.nkv = nkv; a.P = P; a.num_pages = num_pages; a.window = window; a.scale = scale;
     return d == 128 ? launch<128>(map, a, num_items, stream) : launch<64>(map, a, num_items, stream);
 }

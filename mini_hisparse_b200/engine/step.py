@@ -196,7 +196,7 @@ class BatchBuilder:
             buf[offs["tok_part_row"] : offs["tok_part_row"] + T] = plan.tok_part_row
             buf[offs["tok_nsplit"] : offs["tok_nsplit"] + T] = plan.tok_nsplit
             facts.append({"n_small": plan.n_small, "n_big": plan.n_big, "part_rows": plan.part_rows,
-                          "any_split": bool(plan.part_rows)})
+                          "any_split": bool(plan.part_rows), "big_split": plan.big_split})
         return len(rows), facts
 
     def _fill_decode(self, buf: np.ndarray, layout: _Layout, entries, segments, nsplit):
@@ -242,6 +242,7 @@ class BatchBuilder:
                     "tok_nsplit": v(offs["tok_nsplit"], T),
                     "part_rows_cap": f["part_rows"],
                     "any_split": f["any_split"],
+                    "big_split": f.get("big_split", False),
                 }
             )
         return {

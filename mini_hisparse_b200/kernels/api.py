@@ -263,8 +263,9 @@ def attention_tma(q, cache, out, part_acc, part_ml, items, num_items, rows, posi
 
 
 def attention_tc(q, cache, out, items, num_items, positions, block_table, *, nq, nkv, d, page_size,
-                 window=0, scale=None, status=None):
-    """tcgen05 attention for long portions: ``items`` planned for tiles of 128 rows, never split."""
+                 window=0, scale=None, status=None, part_acc=None, part_ml=None, tok_part_row=None):
+    """tcgen05 attention for long portions: ``items`` planned for tiles of 128 rows; items split
+    along the keys write to the partial buffers (then call attention_combine)."""
     lib = build.load("attention_tc")
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("attention_tc: q and the cache must be bfloat16")
@@ -274,7 +275,8 @@ def attention_tc(q, cache, out, items, num_items, positions, block_table, *, nq,
         scale = float(d) ** -0.5
     _check(lib, lib.mhb_attention_tc(
         _ptr(q), _ptr(cache), _ptr(out), _ptr(items), c_int(num_items), _ptr(positions), _ptr(block_table),
-        c_int(block_table.shape[-1]), c_int(nq), c_int(nkv), c_int(d), c_int(page_size),
+        c_int(block_table.shape[-1]), _ptr(tok_part_row), _ptr(part_acc), _ptr(part_ml),
+        c_int(nq), c_int(nkv), c_int(d), c_int(page_size),
         c_int(cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(status), _stream()), "attention_tc")
 
 

@@ -17,6 +17,10 @@ ITEM_INTS = 8
 MIN_KEYS_PER_SPLIT = 256
 SPLIT_MAX_TOKENS = 16  # only short segments (decode tokens, tiny portions) are split along the keys
 MAX_SPLITS = 64
+MAX_BIG_SPLITS = 8       # key splits of a long portion's tile (tcgen05 kernel only)
+BIG_SPLIT_ITEMS = 1024   # long-portion tiles are only split while their items stay below this
+BIG_SPLIT_ROWS = 4096    # ... and their partial rows (tokens x splits) below this
+MIN_KEYS_PER_BIG_SPLIT = 512
 
 
 @dataclass
@@ -31,6 +35,7 @@ class AttentionPlan:
     tok_part_row: np.ndarray   # [T] int32
     tok_nsplit: np.ndarray     # [T] int32: 0 = written directly
     part_rows: int
+    big_split: bool = False    # some long-portion tiles are split along the keys (merged by attention_combine)
 
 
 def _tiling(groups: int, rows: int):
@@ -50,7 +55,10 @@ def plan_attention(need: PagedKVNeed, segments, T: int, sm_count: int = 148,
     tokens, tiny portions) get tiles of ROW_TILE rows and, when their histories are long, are
     split along the keys so that a small batch still fills the GPU; with ``fixed_nsplit`` every
     short segment gets exactly that many splits (a captured graph needs a fixed launch size),
-    empty ones included.  Long portions get tiles of ``need.tile_rows`` rows and are not split.
+    empty ones included.  Long portions get tiles of ``need.tile_rows`` rows; when there are fewer
+    of them than SMs (a portion of some dozens of tokens far into a long prompt) and the tiles are
+    the tcgen05 kernel's, they are split along the keys too, into the number of parts that fills
+    a round of CTAs best.
     """
     groups = need.q_heads // need.kv_heads
     window = need.window or 0
@@ -100,10 +108,48 @@ def plan_attention(need: PagedKVNeed, segments, T: int, sm_count: int = 148,
             for h0, nh in small_chunks:
                 items.append((si, tok0, nt, h0, nh, b, e, sp))
     n_small = len(items)
+    big_split = False
+    # A CTA alone on its SM walks its key tiles nearly twice as fast as one that shares the SM, so
+    # splitting only pays while there are fewer CTAs than SMs (measured: 160 CTAs of 50 tiles took
+    # 49 us, the same work as 480 CTAs 56 us plus the merge).
+    slots = sm_count
+    n_big_ctas = len(big_items) * need.kv_heads
+    if big_items and need.tile_rows == 128 and fixed_nsplit is None and n_big_ctas < slots:
+        tiles = [-(-(it[6] - it[5]) // KEY_TILE) for it in big_items]
+        avg = sum(tiles) / len(tiles)
+        big_tokens = sum(it[2] for it in big_items) // len(big_chunks)
+        fixed = 3.0                            # a CTA's start and end, in key tiles
+        best, best_cost = 1, -(-n_big_ctas // slots) * (avg + fixed)
+        for sp in range(2, MAX_BIG_SPLITS + 1):
+            if (avg * KEY_TILE / sp < MIN_KEYS_PER_BIG_SPLIT or len(big_items) * sp > BIG_SPLIT_ITEMS
+                    or big_tokens * sp > BIG_SPLIT_ROWS):
+                break
+            cost = -(-n_big_ctas * sp // slots) * (avg / sp + fixed)
+            if cost < 0.9 * best_cost:
+                best, best_cost = sp, cost
+        if best > 1:
+            cut, seen = [], set()
+            for it in big_items:
+                si, tok0, nt, h0, nh, kv_begin, kv_end, _ = it
+                span = kv_end - kv_begin
+                if span < best * MIN_KEYS_PER_BIG_SPLIT // 2:
+                    cut.append(it)
+                    continue
+                if (si, tok0) not in seen:      # the head chunks of a tile share its partial rows
+                    seen.add((si, tok0))
+                    for t in range(tok0, tok0 + nt):
+                        tok_part_row[t] = part_rows
+                        tok_nsplit[t] = best
+                        part_rows += best
+                chunk = -(-(-(-span // best)) // KEY_TILE) * KEY_TILE
+                for sp in range(best):
+                    b = min(kv_end, kv_begin + sp * chunk)
+                    cut.append((si, tok0, nt, h0, nh, b, min(kv_end, b + chunk), sp))
+            big_items, big_split = cut, True
     # long tiles first: the CTAs that walk the most keys must not be the last to start
     big_items.sort(key=lambda it: it[5] - it[6])
     arr = np.asarray(items + big_items, np.int32).reshape(-1, ITEM_INTS)
-    return AttentionPlan(arr, n_small, len(big_items), tok_part_row, tok_nsplit, part_rows)
+    return AttentionPlan(arr, n_small, len(big_items), tok_part_row, tok_nsplit, part_rows, big_split)
 
 
 def plan_decode(need: PagedKVNeed, starts: np.ndarray, nsplit: int) -> AttentionPlan:
@@ -149,10 +195,10 @@ def plan_capacity(need: PagedKVNeed, max_tokens: int, max_segments: int,
     big_chunks, big_tpt = _tiling(groups, need.tile_rows)
     splits = fixed_nsplit or MAX_SPLITS
     # every segment may end with a ragged tile; only short segments are split
-    big = (max_tokens // big_tpt + max_segments) * len(big_chunks)
+    big = (max_tokens // big_tpt + max_segments) * len(big_chunks) + BIG_SPLIT_ITEMS
     short_tokens = min(max_tokens, max_segments * SPLIT_MAX_TOKENS)
     small = (short_tokens // small_tpt + max_segments) * len(small_chunks) * splits
-    return big + small, short_tokens * splits
+    return big + small, short_tokens * splits + BIG_SPLIT_ROWS
 
 
 @register_mixer("gq_attention")
@@ -262,7 +308,11 @@ class GQAttention(Mixer):
                             f"attention: pages of {cache.page_size} keys do not divide 64, which the "
                             f"tensor-core kernels for head_dim {self.d} need")
                     K.attention_tc(q, cache.storage, attn, big_items, n_big, ctx.positions, meta["block_table"],
+                                   part_acc=part_acc, part_ml=part_ml, tok_part_row=meta["tok_part_row"],
                                    status=ctx.status, **common)
+                    if meta.get("big_split"):
+                        K.attention_combine(part_acc, part_ml, meta["tok_part_row"], meta["tok_nsplit"], attn,
+                                            nq=self.nq, d=self.d)
                 else:
                     kernel(*args, big_items, n_big, 64, *tail, **common, **extra)
         elif n_small + n_big:

@@ -354,8 +354,10 @@ def run_attention(nq, nkv, d, P_, seg_specs, dtype, window=None, fixed_nsplit=No
         if plan.n_big and kernel == "tc":
             status = torch.zeros(1, dtype=torch.int32, device=DEV)
             K().attention_tc(q, cache, out, items[plan.n_small * ITEM_INTS:], plan.n_big, positions, table,
-                             status=status, **kw)
+                             status=status, part_acc=part_acc, part_ml=part_ml, tok_part_row=tpr, **kw)
             assert int(status) == 0
+            if plan.big_split:                               # long tiles were split along the keys
+                K().attention_combine(part_acc, part_ml, tpr, tns, out, nq=nq, d=d)
         elif plan.n_big:
             launch(q, cache, out, part_acc, part_ml, items[plan.n_small * ITEM_INTS:], plan.n_big, 64,
                    positions, table, tpr, **kw)
@@ -389,6 +391,18 @@ def test_attention_tcgen05_long_portions(nq, nkv, d, P_):
     specs = [(0, 300), (45, 19), (130, 1), (200, 170), (0, 1), (77, 129)]
     out, ref, plan = run_attention(nq, nkv, d, P_, specs, torch.bfloat16, kernel="tc")
     assert plan.n_small and plan.n_big
+    torch.testing.assert_close(out, ref, **tol(torch.bfloat16, 2))
+
+
+@pytest.mark.parametrize("nq,nkv,d,P_", [(28, 4, 128, 16), (8, 8, 64, 32), (40, 8, 128, 16)])
+def test_attention_tcgen05_long_tiles_split_along_the_keys(nq, nkv, d, P_):
+    """Portions of some dozens of tokens far into long prompts: fewer 128-row tiles than SMs, so the
+    planner splits them along the keys and attention_combine merges the parts; beside them decode
+    tokens whose splits the 16-row kernel merges itself."""
+    specs = [(3000, 100), (2500, 1), (700, 1), (1800, 40)]
+    out, ref, plan = run_attention(nq, nkv, d, P_, specs, torch.bfloat16, kernel="tc")
+    assert plan.big_split and plan.n_small
+    assert int((plan.items[plan.n_small:, 7] >= 0).sum()) > 0
     torch.testing.assert_close(out, ref, **tol(torch.bfloat16, 2))
 
 
