@@ -78,7 +78,12 @@ def plan_attention(need: PagedKVNeed, segments, T: int, sm_count: int = 148,
             else:
                 for h0, nh in big_chunks:
                     big_items.append((si, seg.offset + a, nt, h0, nh, kv_begin, kv_end, -1))
-    base_ctas = (len(small_tiles) * len(small_chunks) + len(big_items)) * need.kv_heads
+    # keys a CTA of a short segment should walk: an even share of all their keys over two CTAs per
+    # SM, so that a long history beside short ones is cut into more parts and no CTA runs alone at
+    # the end
+    small_keys = sum(t[4] - t[3] for t in small_tiles) * len(small_chunks) * need.kv_heads
+    target = max(MIN_KEYS_PER_SPLIT, -(-small_keys // (2 * sm_count)))
+    target = -(-target // KEY_TILE) * KEY_TILE
     items = []
     tok_part_row = np.zeros(T, np.int32)
     tok_nsplit = np.zeros(T, np.int32)
@@ -87,10 +92,9 @@ def plan_attention(need: PagedKVNeed, segments, T: int, sm_count: int = 148,
         nsplit = 1
         if fixed_nsplit is not None:
             nsplit = fixed_nsplit
-        elif base_ctas < 2 * sm_count:
-            want = (2 * sm_count) // max(base_ctas, 1)
+        else:
             fit = max(1, (kv_end - kv_begin) // MIN_KEYS_PER_SPLIT)
-            nsplit = max(1, min(want, fit, MAX_SPLITS))
+            nsplit = max(1, min(-(-(kv_end - kv_begin) // target), fit, MAX_SPLITS))
         if nsplit == 1:
             for h0, nh in small_chunks:
                 items.append((si, tok0, nt, h0, nh, kv_begin, kv_end, -1))
