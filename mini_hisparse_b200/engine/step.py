@@ -357,7 +357,8 @@ class ModelRunner:
     def _forward(self, ws, views, segments, T):
         ctx = self.batch.context(self.rt, ws, self.status, views, segments)
         caches = self._cache_views(views["groups"])
-        return self.model.forward(ctx, caches, views["rows"], observer=self.observer)
+        with K.stream_scope():
+            return self.model.forward(ctx, caches, views["rows"], observer=self.observer)
 
     def _step_graph(self, entries, segments):
         B = len(segments)
