@@ -308,7 +308,7 @@ class ModelRunner:
         self.graphs: dict[tuple[int, int], _DecodeGraph] = {}
         self.observer = None
         self.stats = {"steps": 0, "tokens": 0, "graph_steps": 0}
-        build.build_all(self.rt.kernel_modules())
+        build.build_all(model.kernel_modules())
 
     def _cache_views(self, group_meta) -> list[CacheView | None]:
         return [

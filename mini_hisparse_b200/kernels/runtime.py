@@ -20,7 +20,7 @@ MIN_KB_PER_SPLIT = 4
 
 class Float32Runtime(Runtime):
     def kernel_modules(self):
-        return ("elementwise", "gemm_simt", "attention_simt", "sampling")
+        return ("elementwise", "gemm_simt", "sampling")
 
 
 class BFloat16Runtime(Runtime):
@@ -36,7 +36,7 @@ class BFloat16Runtime(Runtime):
         return self._scratch
 
     def kernel_modules(self):
-        return ("elementwise", "gemm_simt", "gemm_tc", "attention_simt", "attention_mma", "attention_tma", "attention_tc", "sampling")
+        return ("elementwise", "gemm_simt", "gemm_tc", "sampling")
 
     def _splits(self, tiles: int, total_kb: int) -> int:
         """Enough K splits for about two CTAs per SM, none empty, none shorter than 4 K blocks."""

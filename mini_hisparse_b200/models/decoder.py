@@ -50,6 +50,15 @@ class DecoderModel:
         yield self.spec.final_norm_name, self.final_norm
         yield self.spec.head_name, self.head
 
+    def kernel_modules(self) -> tuple[str, ...]:
+        """What this model's steps launch: the runtime's libraries and those of its parts."""
+        mods = list(self.rt.kernel_modules())
+        for _, part in self.named_parts():
+            for m in part.kernel_modules():
+                if m not in mods:
+                    mods.append(m)
+        return tuple(mods)
+
     def expected_tensors(self) -> dict[str, ParamSpec]:
         out = {}
         for prefix, part in self.named_parts():

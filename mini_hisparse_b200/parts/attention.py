@@ -244,6 +244,15 @@ class GQAttention(Mixer):
             return ROW_TILE
         return 128 if self.d in (64, 128) else 64
 
+    def kernel_modules(self):
+        """attention_simt holds the CUDA-core kernel and the merge of key splits; the tensor-core
+        kernels come in for the head sizes they are built for."""
+        if not self.tensor_core_attention:
+            return ("attention_simt",)
+        if self.big_tile_rows == 128:
+            return ("attention_simt", "attention_mma", "attention_tma", "attention_tc")
+        return ("attention_simt", "attention_mma")
+
     def cache_need(self):
         return PagedKVNeed(kv_heads=self.nkv, head_dim=self.d, q_heads=self.nq, window=self.window,
                            tile_rows=self.big_tile_rows)

@@ -104,7 +104,8 @@ class Runtime:
             )
 
     def kernel_modules(self) -> tuple[str, ...]:
-        return ("elementwise", "gemm_simt", "attention_simt", "sampling")
+        """The kernel libraries every model needs in this dtype; parts add their own."""
+        return ("elementwise", "gemm_simt", "sampling")
 
     def linear(self, x: torch.Tensor, weight: torch.Tensor, ws: Workspace, name: str,
                out_dtype: torch.dtype | None = None, bias: torch.Tensor | None = None,
@@ -179,6 +180,11 @@ class Part:
 
     def parameters(self) -> dict[str, ParamSpec]:
         return {}
+
+    def kernel_modules(self) -> tuple[str, ...]:
+        """Kernel libraries (csrc file stems) this part launches beyond the runtime's own: what a
+        model's first step compiles is the union over its parts."""
+        return ()
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         for k, v in tensors.items():
