@@ -351,16 +351,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // One CTA per SM; tiles of 128 tokens x bn features (bn = 256 unless the matrix is narrower: a
 // 128 x N x 16 MMA with N < 256 is issued no faster than it runs, so narrower tiles only lose).
 // Whole rounds of tiles are dealt round-robin, so that the CTAs of a round read neighbouring
-// tiles and share them in L2.  The tiles of the last, incomplete round are not given to some
-// CTAs while the others idle: their (tile, K block) units are cut into one contiguous range per
-// CTA, all of the same length ("stream-K"), walked after the whole rounds so that the CTAs stay
-// roughly in step along K and keep sharing operand tiles in L2.
-// A tile whose K range is shared is written by all its holders as float32 partial tiles to a
-// workspace; when a CTA has gone through all its work it comes back to its shared tiles (two
-// at most), waits (bounded) for the other holders' parts, and reduces ITS share of the tile's
-// columns: the parts are added in the order of their K ranges, so the sum is deterministic.
-// All CTAs reach that point at about the same time, so the waits are short, and all are
-// resident (one per SM), so nobody waits for a CTA that cannot run.
+// tiles at the same K and share them in L2.  The tiles of the last, incomplete round are not given
+// to some CTAs while the others idle: each is cut along K into `ways` equal parts, and the parts
+// are dealt round-robin too, part-major, so that the CTAs on one part still walk the same K
+// blocks together.  (Contiguous "stream-K" ranges balance better on paper but put every CTA at
+// another K: the 7B-shape down projection then read 1.05 GB from memory instead of 0.30 GB.)
+// Every holder of a shared tile writes its float32 partial tile to a workspace; when a CTA has
+// gone through all its work it comes back to its shared tiles (two at most), waits (bounded) for
+// the other holders' parts, and reduces ITS share of the tile's columns: the parts are added in
+// the order of their K ranges, so the sum is deterministic.  All CTAs reach that point at about
+// the same time, so the waits are short, and all are resident (one per SM), so nobody waits for
+// a CTA that cannot run.
 // Tensor memory holds TWO accumulators of 256 columns: while the epilogue warps read one, the MMA
 // warp fills the other.  A = activations [M, K], B = weights [N, K].
 constexpr int P_STAGES = 4;
@@ -376,21 +377,11 @@ struct PSmem {
     static constexpr int TOTAL = BARRIER_OFFSET + (2 * P_STAGES + 4) * 8 + 16 + 1024;
 };
 
-// First unit of CTA c's range: the even cut, moved onto a tile boundary when it falls within
-// `slack` K blocks of one (a sliver of a tile would cost a partial tile for next to no work).
-__host__ __device__ inline long long stream_bound(int c, int grid, long long total_units, int total_kb, int slack) {
-    long long b = (long long)c * total_units / grid;
-    const int r = (int)(b % total_kb);
-    if (r && r <= slack) b -= r;
-    else if (r && total_kb - r <= slack) b += total_kb - r;
-    return b;
-}
-
 template <typename OT, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                           OT* __restrict__ C, int Ra, int Rb, int K, long long ldc, int bn, int tiles_m,
-                          int whole_tiles, int tail_tiles, int slack, float* __restrict__ partials,
+                          int whole_tiles, int tail_tiles, int ways, float* __restrict__ partials,
                           int* __restrict__ flags, int* __restrict__ status) {
     using S = PSmem;
     extern __shared__ uint8_t smem_raw[];
@@ -404,19 +395,20 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     uint32_t* tmem_slot = (uint32_t*)(smem + S::BARRIER_OFFSET + 8 * (2 * P_STAGES + 4));
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_kb = (K + BK - 1) / BK;
-    // tiles [0, whole_tiles) go round-robin; the units of tiles [whole_tiles, + tail_tiles) are shared
-    const long long total_units = (long long)tail_tiles * total_kb;
-    const long long u_begin = stream_bound(blockIdx.x, gridDim.x, total_units, total_kb, slack);
-    const long long u_end = stream_bound(blockIdx.x + 1, gridDim.x, total_units, total_kb, slack);
-    // segment j of this CTA: a tile and a range of its K blocks; false when there is no more
-    auto segment = [&](int j, long long& u, int& t, int& kb0, int& kb1) -> bool {
-        const long long whole = (long long)blockIdx.x + (long long)j * gridDim.x;
-        if (whole < whole_tiles) { t = (int)whole; kb0 = 0; kb1 = total_kb; return true; }
-        if (u >= u_end) return false;
-        t = whole_tiles + (int)(u / total_kb);
-        kb0 = (int)(u % total_kb);
-        kb1 = (u_end - u < total_kb - kb0) ? kb0 + (int)(u_end - u) : total_kb;
-        u += kb1 - kb0;
+    // tiles [0, whole_tiles) go round-robin as whole tiles; then the ways * tail_tiles parts of the
+    // tiles [whole_tiles, + tail_tiles): entry e is part e / tail_tiles of tile e % tail_tiles
+    const int my_whole = whole_tiles > (int)blockIdx.x ? (whole_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int entries = tail_tiles * ways;
+    // segment j of this CTA: a tile, a range of its K blocks and, for a part, its entry (else -1)
+    auto segment = [&](int j, int& t, int& kb0, int& kb1, int& entry) -> bool {
+        if (j < my_whole) { t = (int)blockIdx.x + j * (int)gridDim.x; kb0 = 0; kb1 = total_kb; entry = -1; return true; }
+        const int e = (int)blockIdx.x + (j - my_whole) * (int)gridDim.x;
+        if (e >= entries) return false;
+        const int part = e / tail_tiles;
+        t = whole_tiles + e % tail_tiles;
+        kb0 = (int)((long long)part * total_kb / ways);
+        kb1 = (int)((long long)(part + 1) * total_kb / ways);
+        entry = ways > 1 ? e : -1;
         return true;
     };
     const uint32_t stage_tx = S::A_BYTES + bn * BK * 2;
@@ -440,9 +432,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
             pdl_wait();
-            int it = 0, t, kb0, kb1;
-            long long u = u_begin;
-            for (int j = 0; ok && segment(j, u, t, kb0, kb1); ++j) {
+            int it = 0, t, kb0, kb1, entry;
+            for (int j = 0; ok && segment(j, t, kb0, kb1, entry); ++j) {
                 const int ra0 = (t % tiles_m) * BM, rb0 = (t / tiles_m) * bn;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % P_STAGES;
@@ -463,9 +454,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = make_idesc(bn);
-            int it = 0, t, kb0, kb1;
-            long long u = u_begin;
-            for (int j = 0; ok && segment(j, u, t, kb0, kb1); ++j) {
+            int it = 0, t, kb0, kb1, entry;
+            for (int j = 0; ok && segment(j, t, kb0, kb1, entry); ++j) {
                 const int b = j & 1;
                 ok = mbar_wait(acc_empty_bar(b), ((j >> 1) & 1) ^ 1);     // the epilogue has read this buffer
                 if (!ok) break;
@@ -549,19 +539,18 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             }
         };
         // ---- first pass: every segment; a tile that is shared goes to the workspace ----------------
-        int shared_tile[2], shared_count = 0;
-        int t, kb0, kb1;
-        long long u = u_begin;
-        for (int j = 0; ok && segment(j, u, t, kb0, kb1); ++j) {
+        int shared_entry[2], shared_count = 0;
+        int t, kb0, kb1, entry;
+        for (int j = 0; ok && segment(j, t, kb0, kb1, entry); ++j) {
             const int b = j & 1;
             const int ra0 = (t % tiles_m) * BM, rb0 = (t / tiles_m) * bn;
             ok = mbar_wait(acc_full_bar(b), (j >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
             const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + b * P_BN_MAX;
-            if (kb0 > 0 || kb1 < total_kb) {
-                // slot 1 holds the part that begins the tile, slot 0 a later part
-                float* mine = partials + (size_t)(2 * blockIdx.x + (kb0 == 0 ? 1 : 0)) * P_PARTIAL_FLOATS;
+            if (entry >= 0) {
+                // a part of a shared tile: this CTA's first part goes to its slot 0, its second to slot 1
+                float* mine = partials + (size_t)(2 * blockIdx.x + entry / (int)gridDim.x) * P_PARTIAL_FLOATS;
 #pragma unroll 1
                 for (int c0 = 0; c0 < bn; c0 += 16) {
                     uint32_t r[16];
@@ -578,7 +567,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                     mbar_arrive_plain(acc_empty_bar(b));
                     atomicAdd(flags + 4 * t + quarter, 1);      // this quarter of the rows has landed
                 }
-                if (shared_count < 2) shared_tile[shared_count++] = t;
+                if (shared_count < 2) shared_entry[shared_count++] = entry;
                 continue;
             }
 #pragma unroll 1
@@ -596,15 +585,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         // ---- second pass: the shared tiles.  The CTAs that hold parts of a tile divide its columns
         // among themselves; each adds the parts in the order of their K ranges and stores. ---------
         for (int i = 0; i < shared_count && ok; ++i) {
-            const int ts = shared_tile[i];
-            const long long u_lo = (long long)(ts - whole_tiles) * total_kb, u_hi = u_lo + total_kb - 1;
-            auto cta_of = [&](long long unit) {
-                int c = (int)(unit * gridDim.x / total_units);
-                while (c + 1 < (int)gridDim.x && stream_bound(c + 1, gridDim.x, total_units, total_kb, slack) <= unit) ++c;
-                while (c > 0 && stream_bound(c, gridDim.x, total_units, total_kb, slack) > unit) --c;
-                return c;
-            };
-            const int c_first = cta_of(u_lo), parts = cta_of(u_hi) - c_first + 1, rank = blockIdx.x - c_first;
+            const int tail_index = shared_entry[i] % tail_tiles, rank = shared_entry[i] / tail_tiles;
+            const int ts = whole_tiles + tail_index, parts = ways;
             const volatile int* flag = flags + 4 * ts + quarter;
             uint32_t spins = 0;
             while (*flag < parts && ++spins < WAIT_LIMIT) __nanosleep(32);
@@ -623,7 +605,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 #pragma unroll
                     for (int q = 0; q < BATCH; ++q) {
                         const int p = p0 + q < parts ? p0 + q : parts - 1;
-                        const float* src = partials + (size_t)(2 * (c_first + p) + (p == 0 ? 1 : 0)) * P_PARTIAL_FLOATS;
+                        const int e = p * tail_tiles + tail_index;        // part p of this tile: its CTA and slot
+                        const float* src = partials + (size_t)(2 * (e % (int)gridDim.x) + e / (int)gridDim.x) * P_PARTIAL_FLOATS;
                         const uint4* a = (const uint4*)(src + ((size_t)(c0 >> 4) * BM + row_in_tile) * 16);
 #pragma unroll
                         for (int x = 0; x < 4; ++x) v[q][x] = __ldcg(a + x);
@@ -784,28 +767,31 @@ int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K
     const int total_kb = (K + BK - 1) / BK;
     if (num_tiles > INT_MAX / 2) return fail("gemm_tc: too many tiles (%lld)", num_tiles);
     long long whole_tiles = num_tiles, tail_tiles = 0;
-    int slack = 0;
+    int ways = 1;
     const long long rest = num_tiles % sms;
-    // Share the K range of the tiles of the last round when it would leave a fifth or more of
-    // the SMs idle.  Sharing puts the CTAs out of step along K, so operand tiles are read from
-    // memory more often, and the exchange costs some 15 us: it pays for a long K only.
-    bool share = false;
-    if (partials && flags && num_tiles <= P_FLAG_CAP && num_tiles > sms && rest > 0 &&
-        rest * 5 <= (long long)sms * 4 && total_kb >= 128) {
-        const long long per_cta = rest * total_kb / sms;
-        if (per_cta >= 2) {
-            share = true;
+    // Cut the tiles of the last round along K when that round would leave SMs idle: into the number
+    // of parts (two per CTA at most, eight K blocks a part at least) that makes the parts' rounds
+    // shortest.  The exchange of the partial tiles costs some 15 us, so the gain must be worth it
+    // (a K block takes about 0.36 us).
+    if (partials && flags && num_tiles <= P_FLAG_CAP && num_tiles > sms && rest > 0) {
+        double best = 1.0;
+        for (int w = 2; w <= 8 && rest * w <= 2LL * sms && total_kb / w >= 8; ++w) {
+            const double rounds = (double)((rest * w + sms - 1) / sms) / w;
+            if (rounds < best - 1e-9) { best = rounds; ways = w; }
+        }
+        if ((1.0 - best) * total_kb * 0.36 < 25.0) ways = 1;
+        if (ways > 1) {
             tail_tiles = rest;
             whole_tiles = num_tiles - rest;
-            slack = (int)(per_cta / 4 < 8 ? per_cta / 4 : 8);
         }
     }
+    const bool share = ways > 1;
     if (!share && N >= P_BN_MAX) {
         // whole tiles only: a narrower tile may fill the last round better
         bn = choose_persistent_bn(tiles_m, N, sms, step);
         num_tiles = whole_tiles = (long long)tiles_m * ((N + bn - 1) / bn);
     }
-    const long long grid = share ? sms : (num_tiles < sms ? num_tiles : sms);
+    const long long grid = num_tiles < sms ? num_tiles : sms;
     CUtensorMap ma, mb;
     int rc;
     if ((rc = make_map(&ma, X, M, K, lda, BM))) return rc;
@@ -818,7 +804,7 @@ int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K
         configured = true;
     }
     launch_kernel(kern, dim3((unsigned)grid), dim3(THREADS), PSmem::TOTAL, stream, ma, mb, (OT*)C, M, N, K, ldc, bn,
-                  tiles_m, (int)whole_tiles, (int)tail_tiles, slack, partials, flags, status);
+                  tiles_m, (int)whole_tiles, (int)tail_tiles, ways, partials, flags, status);
     return check_launch("gemm_tc_persistent");
 }
 }  // namespace
