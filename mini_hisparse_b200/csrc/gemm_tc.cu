@@ -779,7 +779,7 @@ int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K
             const double rounds = (double)((rest * w + sms - 1) / sms) / w;
             if (rounds < best - 1e-9) { best = rounds; ways = w; }
         }
-        if ((1.0 - best) * total_kb * 0.36 < 25.0) ways = 1;
+        if ((1.0 - best) * total_kb * 0.36 < 40.0) ways = 1;
         if (ways > 1) {
             tail_tiles = rest;
             whole_tiles = num_tiles - rest;

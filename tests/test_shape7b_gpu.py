@@ -84,16 +84,17 @@ def test_7b_layer_sizes_all_cuts(folder, reference, dtype):
 
 
 def test_7b_layer_sizes_long_prompt_shares_tiles_along_k(folder):
-    """2,304 tokens in one step, bfloat16: the down projection (K = 18944) has 252 tiles for 148 SMs,
-    so the CTAs of the persistent product share the last round's tiles along K and reduce them
-    through the workspace; the prompt also spans 36 key tiles in the tcgen05 attention kernel."""
+    """1,400 tokens in one step, bfloat16: the down projection (K = 18944) has 11 x 14 = 154 tiles for
+    148 SMs, so the persistent product cuts the six tiles of its last round along K into eight parts
+    each and reduces them through the workspace; the prompt also spans 22 key tiles in the tcgen05
+    attention kernel."""
     from mini_hisparse_b200 import CacheConfig, CacheManager, load_model
     from mini_hisparse_b200.engine import ModelRunner, StepEntry
 
     torch.backends.cuda.matmul.allow_tf32 = False
     cfg, w = P.load_folder(folder, dtype=torch.float32, device="cuda:0")
-    tokens = random_tokens(CONFIG["vocab_size"], 2304, seed=11)
-    want = list(range(0, 2304, 7)) + [2303]
+    tokens = random_tokens(CONFIG["vocab_size"], 1400, seed=11)
+    want = list(range(0, 1400, 7)) + [1399]
     ref = P.forward_logits(cfg, w, tokens)[want].cpu()
     model = load_model(folder, dtype="bfloat16")
     cache = CacheManager(model.cache_needs, CacheConfig(num_pages=160, page_size=16, max_requests=2,
