@@ -321,34 +321,57 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
             }
             compute_sync();
             if (is_last) {
+                // The merge is a chain of round trips to L2 on the kernel's critical path: every load
+                // that does not depend on another is issued at once.
                 __threadfence();
-                __shared__ float wgt_s[16][MAX_MERGE_SPLITS];
-                __shared__ float inv_s[16];
+                // scratch in the ring, which nobody reads any more (12 KB + 64 bytes)
+                float (*wgt_s)[MAX_MERGE_SPLITS] = (float (*)[MAX_MERGE_SPLITS])smem;
+                float2 (*ml_s)[MAX_MERGE_SPLITS] = (float2 (*)[MAX_MERGE_SPLITS])(smem + 16 * MAX_MERGE_SPLITS * 4);
+                float* inv_s = (float*)(smem + 16 * MAX_MERGE_SPLITS * 12);
                 const int ns = min(a.tok_nsplit[tok0], MAX_MERGE_SPLITS);
+                for (int idx = tid; idx < nrows * ns; idx += CWARPS * 32) {     // all (maximum, sum) pairs at once
+                    const int row = idx / ns, sp = idx - row * ns;
+                    const int t = tok0 + row / nheads, hq = kvh * groups + head0 + row % nheads;
+                    ml_s[row][sp] = __ldcg((const float2*)(a.part_ml + (((size_t)a.tok_part_row[t] + sp) * a.nq + hq) * 2));
+                }
+                compute_sync();
                 if (tid < nrows) {
-                    const int t = tok0 + tid / nheads, hq = kvh * groups + head0 + tid % nheads;
-                    const size_t row0 = a.tok_part_row[t];
                     float M = -INFINITY;
-                    for (int sp = 0; sp < ns; ++sp) M = fmaxf(M, __ldcg(a.part_ml + ((row0 + sp) * a.nq + hq) * 2));
+                    for (int sp = 0; sp < ns; ++sp) M = fmaxf(M, ml_s[tid][sp].x);
                     float lsum = 0.f;
                     for (int sp = 0; sp < ns; ++sp) {
-                        const float ms = __ldcg(a.part_ml + ((row0 + sp) * a.nq + hq) * 2);
+                        const float ms = ml_s[tid][sp].x;
                         const float w = ms > -INFINITY ? expf(ms - M) : 0.f;
                         wgt_s[tid][sp] = w;
-                        lsum += w * __ldcg(a.part_ml + ((row0 + sp) * a.nq + hq) * 2 + 1);
+                        lsum += w * ml_s[tid][sp].y;
                     }
                     inv_s[tid] = lsum > 0.f ? 1.f / lsum : 0.f;
                 }
                 compute_sync();
-                for (int idx = tid; idx < nrows * D; idx += CWARPS * 32) {
-                    const int row = idx / D, e = idx - row * D;
+                // four elements per thread and step, eight splits in flight; summed in the splits' order
+                for (int idx = tid; idx < nrows * (D / 4); idx += CWARPS * 32) {
+                    const int row = idx / (D / 4), e = (idx - row * (D / 4)) * 4;
                     const int t = tok0 + row / nheads, hq = kvh * groups + head0 + row % nheads;
                     const float* src = a.part_acc + ((size_t)a.tok_part_row[t] * a.nq + hq) * D + e;
                     const size_t step = (size_t)a.nq * D;
-                    float acc = 0.f;
-#pragma unroll 4
-                    for (int sp = 0; sp < ns; ++sp) acc += wgt_s[row][sp] * __ldcg(src + sp * step);
-                    a.out[((size_t)t * a.nq + hq) * D + e] = __float2bfloat16_rn(acc * inv_s[row]);
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int s0 = 0; s0 < ns; s0 += 8) {
+                        float4 v[8];
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) v[q] = __ldcg((const float4*)(src + (size_t)min(s0 + q, ns - 1) * step));
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            if (s0 + q < ns) {
+                                const float w = wgt_s[row][s0 + q];
+                                acc.x += w * v[q].x; acc.y += w * v[q].y; acc.z += w * v[q].z; acc.w += w * v[q].w;
+                            }
+                        }
+                    }
+                    const float inv = inv_s[row];
+                    uint2 packed;
+                    packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+                    packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+                    *(uint2*)(a.out + ((size_t)t * a.nq + hq) * D + e) = packed;
                 }
             }
         }

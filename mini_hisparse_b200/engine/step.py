@@ -142,6 +142,9 @@ class BatchBuilder:
         groups = need.q_heads // need.kv_heads
         chunks = 1 if groups <= ROW_TILE else -(-groups // ROW_TILE)
         ctas = B * need.kv_heads * chunks
+        import os
+        if os.environ.get("MHB_DECODE_SPLITS"):
+            return int(os.environ["MHB_DECODE_SPLITS"])
         return max(1, min(MAX_SPLITS, (2 * self.sm_count) // ctas, max_keys // MIN_KEYS_PER_SPLIT))
 
     def segments(self, entries: list[StepEntry]) -> tuple[list[Segment], int]:
