@@ -142,9 +142,6 @@ class BatchBuilder:
         groups = need.q_heads // need.kv_heads
         chunks = 1 if groups <= ROW_TILE else -(-groups // ROW_TILE)
         ctas = B * need.kv_heads * chunks
-        import os
-        if os.environ.get("MHB_DECODE_SPLITS"):
-            return int(os.environ["MHB_DECODE_SPLITS"])
         return max(1, min(MAX_SPLITS, (2 * self.sm_count) // ctas, max_keys // MIN_KEYS_PER_SPLIT))
 
     def segments(self, entries: list[StepEntry]) -> tuple[list[Segment], int]:
@@ -329,6 +326,12 @@ class ModelRunner:
             return None
         vocab = self.model.spec.vocab_size
         for e in entries:
+            if len(e.tokens) > 32:          # a prompt portion: one pass in numpy
+                arr = np.asarray(e.tokens)
+                bad = np.flatnonzero((arr < 0) | (arr >= vocab))
+                if bad.size:
+                    raise StepError(f"request {e.request!r}: token {int(arr[bad[0]])} is outside the vocabulary of {vocab}")
+                continue
             for t in e.tokens:
                 if not 0 <= t < vocab:
                     raise StepError(f"request {e.request!r}: token {t} is outside the vocabulary of {vocab}")
