@@ -1,0 +1,111 @@
+"""The attention plan (host only): whatever the mix of segments, every (token, query head, key) that
+causal attention needs is covered by exactly one work item, parts of a split tile are numbered
+0..n-1 and own distinct partial rows, and capacity bounds hold."""
+import numpy as np
+import pytest
+
+from mini_hisparse_b200.parts.attention import (ITEM_INTS, MAX_SPLITS, ROW_TILE, plan_attention, plan_capacity,
+                                                plan_decode)
+from mini_hisparse_b200.parts.base import Segment
+from mini_hisparse_b200.parts.spec import PagedKVNeed
+
+
+def segments_of(specs):
+    """specs: (cached tokens, new tokens) per request."""
+    out, off = [], 0
+    for i, (hist, n) in enumerate(specs):
+        out.append(Segment(f"r{i}", i, hist, n, off))
+        off += n
+    return out, off
+
+
+def check_cover(need, specs, plan):
+    segments, T = segments_of(specs)
+    groups = need.q_heads // need.kv_heads
+    window = need.window or 0
+    pos = np.concatenate([np.arange(h, h + n) for h, n in specs])
+    covered = {}                                  # (token, head in group) -> list of (begin, end, split)
+    for it in plan.items:
+        si, tok0, nt, h0, nh, b, e, sp = (int(v) for v in it)
+        seg = segments[si]
+        assert seg.offset <= tok0 and tok0 + nt <= seg.offset + seg.count
+        assert 0 <= h0 and h0 + nh <= groups and nt * nh <= max(ROW_TILE, need.tile_rows)
+        for t in range(tok0, tok0 + nt):
+            for h in range(h0, h0 + nh):
+                covered.setdefault((t, h), []).append((b, e, sp))
+    assert len(covered) == T * groups             # every token and head has items
+    for (t, h), parts in covered.items():
+        lo = max(0, int(pos[t]) - window + 1) if window else 0
+        hi = int(pos[t]) + 1                      # keys [lo, hi) are what the token may see
+        parts.sort()
+        splits = [p[2] for p in parts]
+        if len(parts) == 1 and splits[0] < 0:
+            assert plan.tok_nsplit[t] == 0
+        else:
+            assert sorted(splits) == list(range(len(parts))) == list(range(int(plan.tok_nsplit[t])))
+        # the parts tile a range that contains [lo, hi) without gap or overlap (the kernels mask
+        # per token inside an item, so an item may reach beyond a token's own range)
+        for (b0, e0, _), (b1, e1, _) in zip(parts, parts[1:]):
+            assert e0 == b1 or e0 >= hi           # later parts may be empty past the end
+        assert parts[0][0] <= lo and max(p[1] for p in parts) >= hi
+    # partial rows: each split token owns tok_nsplit consecutive rows, nobody shares
+    rows = set()
+    for t in range(T):
+        n = int(plan.tok_nsplit[t])
+        for r in range(int(plan.tok_part_row[t]), int(plan.tok_part_row[t]) + n):
+            assert r not in rows and r < plan.part_rows
+            rows.add(r)
+    assert plan.n_small + plan.n_big == plan.items.shape[0]
+
+
+CASES = [
+    [(0, 300), (45, 19), (130, 1), (200, 170), (0, 1), (77, 129)],
+    [(3000, 100), (2500, 1), (700, 1), (1800, 40)],
+    [(4000, 1)] * 8,
+    [(100 + 61 * i, 1) for i in range(30)] + [(3000, 482)],
+    [(0, 2048)],
+    [(16000, 100)],
+    [(0, 1), (0, 2), (0, 16), (0, 17)],
+]
+
+
+@pytest.mark.parametrize("specs", CASES)
+@pytest.mark.parametrize("need", [
+    PagedKVNeed(4, 128, 28, None, tile_rows=128), PagedKVNeed(8, 128, 40, None, tile_rows=128),
+    PagedKVNeed(1, 32, 3, None, tile_rows=64), PagedKVNeed(2, 16, 4, None, tile_rows=16),
+    PagedKVNeed(2, 128, 512, None, tile_rows=128), PagedKVNeed(4, 64, 4, 100, tile_rows=128),
+])
+def test_every_key_is_covered_once(need, specs):
+    segments, T = segments_of(specs)
+    plan = plan_attention(need, segments, T, 148)
+    check_cover(need, specs, plan)
+    items, rows = plan_capacity(need, T, len(specs))
+    assert plan.items.shape[0] <= items and plan.part_rows <= rows
+
+
+def test_long_tiles_are_split_only_when_they_are_fewer_than_sms():
+    need = PagedKVNeed(4, 128, 28, None, tile_rows=128)
+    few = plan_attention(need, segments_of([(16000, 100)])[0], 100, 148)
+    assert few.big_split and (few.items[few.n_small:, 7] >= 0).all()
+    many = plan_attention(need, segments_of([(0, 2048)])[0], 2048, 148)
+    assert not many.big_split and (many.items[:, 7] == -1).all()
+    spans = many.items[:, 6] - many.items[:, 5]
+    assert (np.diff(spans) <= 0).all()            # longest tiles first
+
+
+def test_a_long_history_beside_short_ones_gets_more_parts():
+    need = PagedKVNeed(8, 128, 40, None, tile_rows=128)
+    specs = [(4000, 1)] + [(200, 1)] * 29
+    plan = plan_attention(need, segments_of(specs)[0], 30, 148)
+    assert plan.tok_nsplit[0] >= 2 and (plan.tok_nsplit[1:] <= 1).all()
+    assert plan.tok_nsplit.max() <= MAX_SPLITS
+
+
+@pytest.mark.parametrize("nsplit", [1, 3, 16])
+def test_decode_plan_for_a_captured_graph(nsplit):
+    need = PagedKVNeed(4, 128, 28, None, tile_rows=128)
+    starts = np.array([4000, 17, 0, 999], np.int64)
+    plan = plan_decode(need, starts, nsplit)
+    assert plan.items.shape == (4 * nsplit, ITEM_INTS)
+    assert plan.part_rows == (4 * nsplit if nsplit > 1 else 0)
+    check_cover(need, [(int(s), 1) for s in starts], plan)
