@@ -439,6 +439,31 @@ MHB_EXPORT int mhb_rope_append(const void* qkv, int in_dtype, int nsplit, long l
     return check_launch("rope_append");
 }
 
+// cos and sin of every token's rotation angles, [T, d]: cos[d/2] then sin[d/2]; once per step for
+// all layers (the matrix product's q/k/v epilogue reads it).  Float32 angles as in rope_append.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float* __restrict__ table, int T, int half, int rotate) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= T * half) return;
+    const int t = idx / half, i = idx - t * half;
+    float sn = 0.f, cs = 1.f;
+    if (rotate) sincosf((float)positions[t] * inv_freq[i], &sn, &cs);
+    table[(size_t)t * 2 * half + i] = cs;
+    table[(size_t)t * 2 * half + half + i] = sn;
+}
+
+MHB_EXPORT int mhb_rope_table(const int* positions, const float* inv_freq, float* table, int T, int d, int rotate,
+                              cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (d % 2) return fail("rope_table: head_dim %d must be even", d);
+    const int half = d / 2, threads = 256;
+    launch_kernel(rope_table_kernel, dim3((T * half + threads - 1) / threads), dim3(threads), 0, stream, positions,
+                  inv_freq, table, T, half, rotate);
+    return check_launch("rope_table");
+}
+
 // ---- SwiGLU gate ------------------------------------------------------------------------------
 // out[t, i] = silu(gate_i) * up_i   (mini_hisparse/model.py:70-71).  gu[t] holds 2 I values in
 // blocks: `block` gate values, then the `block` up values of the same indices (block = I is the

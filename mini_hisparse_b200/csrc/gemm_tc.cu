@@ -377,12 +377,28 @@ struct PSmem {
     static constexpr int TOTAL = BARRIER_OFFSET + (2 * P_STAGES + 4) * 8 + 16 + 1024;
 };
 
+// Epilogue 2: the tile is a run of tokens x two (head size 128) or four (head size 64) heads of the
+// stacked q/k/v product.  Instead of storing it, the epilogue adds the bias, rotates q and k heads
+// (half-split pairs i, i + d/2, mini_hisparse/model.py:141-151) by the token's row of a cos/sin
+// table, and writes q as bfloat16 and k, v into the token's page of the KV cache
+// (model.py:169-170): no float32 q/k/v matrix goes to memory and no separate pass reads it back.
+struct QkvRopeArgs {
+    const float* bias;          // [(nq + 2 nkv) d] or null
+    const float* cos_sin;       // [T, d]: cos of the d/2 angles, then sin
+    const int* positions;       // [T]
+    const int* tok_seg;         // [T]
+    const int* block_table;     // [segments, table_width]
+    __nv_bfloat16* q_out;       // [T, nq d]
+    __nv_bfloat16* cache;       // [pages, 2, nkv, P, d]
+    int table_width, nq, nkv, d, P, num_pages, write_kv;
+};
+
 template <typename OT, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                           OT* __restrict__ C, int Ra, int Rb, int K, long long ldc, int bn, int tiles_m,
                           int whole_tiles, int tail_tiles, int ways, float* __restrict__ partials,
-                          int* __restrict__ flags, int* __restrict__ status) {
+                          int* __restrict__ flags, int* __restrict__ status, const QkvRopeArgs qr) {
     using S = PSmem;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -570,13 +586,116 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 if (shared_count < 2) shared_entry[shared_count++] = entry;
                 continue;
             }
+            if constexpr (EPI == 2) {
+                const int ra = ra0 + row_in_tile;
+                const bool live = ra < Ra;
+                const int d = qr.d, half = d >> 1;
+                const int pos = live ? qr.positions[ra] : 0;
+                const float* cs = qr.cos_sin + (size_t)(live ? ra : 0) * d;
+                const int head0 = rb0 / d;
+                int page = -1;
+                if (live && qr.write_kv && head0 + bn / d > qr.nq) {        // the tile holds k or v heads
+                    page = qr.block_table[(size_t)qr.tok_seg[ra] * qr.table_width + pos / qr.P];
+                    if (page < 0 || page >= qr.num_pages) {                 // never write outside the pool
+                        if (status) atomicOr(status, 2);
+                        page = -1;
+                    }
+                }
+                const int within = pos % qr.P;
+                const int total_heads = qr.nq + 2 * qr.nkv;
+                // rotated heads: the chunk of 16 angles is the outer loop, so that a row's cos and
+                // sin are fetched once (16-byte loads) for all heads of the tile
 #pragma unroll 1
-            for (int c0 = 0; c0 < bn; c0 += UNIT) {
-                uint32_t r[16], r2[16];
-                tmem_ld16(acc + c0, r);
-                if constexpr (EPI == 1) tmem_ld16(acc + c0 + 16, r2);
-                tmem_ld_wait();
-                emit(ra0 + row_in_tile, rb0, c0, r, r2);
+                for (int c = 0; c < half; c += 16) {
+                    float4 cs4[4], sn4[4];
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        cs4[x] = *(const float4*)(cs + c + 4 * x);
+                        sn4[x] = *(const float4*)(cs + half + c + 4 * x);
+                    }
+                    const float* cf = (const float*)cs4;
+                    const float* sf = (const float*)sn4;
+#pragma unroll 1
+                    for (int hh = 0; hh < bn / d; ++hh) {
+                        const int head = head0 + hh;
+                        if (head >= qr.nq + qr.nkv) break;               // value heads and the edge: below
+                        const int col0 = head * d;
+                        const bool is_q = head < qr.nq;
+                        uint32_t ra16[16], rb16[16];
+                        tmem_ld16(acc + hh * d + c, ra16);
+                        tmem_ld16(acc + hh * d + half + c, rb16);
+                        tmem_ld_wait();
+                        if (!live || (!is_q && page < 0)) continue;
+                        __nv_bfloat16* dst = is_q ? qr.q_out + (size_t)ra * qr.nq * d + col0
+                                                  : qr.cache + ((((size_t)page * 2 + 0) * qr.nkv + (head - qr.nq)) * qr.P + within) * d;
+                        float ba[16], bb[16];
+                        if (qr.bias) {
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) {
+                                *(float4*)(ba + 4 * x) = *(const float4*)(qr.bias + col0 + c + 4 * x);
+                                *(float4*)(bb + 4 * x) = *(const float4*)(qr.bias + col0 + half + c + 4 * x);
+                            }
+                        } else {
+#pragma unroll
+                            for (int x = 0; x < 16; ++x) ba[x] = bb[x] = 0.f;
+                        }
+                        uint32_t pa[8], pb[8];
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) {
+                            const float a0 = __uint_as_float(ra16[2 * x]) + ba[2 * x], a1 = __uint_as_float(ra16[2 * x + 1]) + ba[2 * x + 1];
+                            const float b0 = __uint_as_float(rb16[2 * x]) + bb[2 * x], b1 = __uint_as_float(rb16[2 * x + 1]) + bb[2 * x + 1];
+                            __nv_bfloat162 ta = __floats2bfloat162_rn(a0 * cf[2 * x] - b0 * sf[2 * x], a1 * cf[2 * x + 1] - b1 * sf[2 * x + 1]);
+                            __nv_bfloat162 tb = __floats2bfloat162_rn(b0 * cf[2 * x] + a0 * sf[2 * x], b1 * cf[2 * x + 1] + a1 * sf[2 * x + 1]);
+                            pa[x] = *(uint32_t*)&ta;
+                            pb[x] = *(uint32_t*)&tb;
+                        }
+                        *(uint4*)(dst + c) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
+                        *(uint4*)(dst + c + 8) = make_uint4(pa[4], pa[5], pa[6], pa[7]);
+                        *(uint4*)(dst + half + c) = make_uint4(pb[0], pb[1], pb[2], pb[3]);
+                        *(uint4*)(dst + half + c + 8) = make_uint4(pb[4], pb[5], pb[6], pb[7]);
+                    }
+                }
+                // value heads: bias, no rotation
+#pragma unroll 1
+                for (int hh = 0; hh < bn / d; ++hh) {
+                    const int head = head0 + hh;
+                    if (head < qr.nq + qr.nkv) continue;
+                    if (head >= total_heads) break;
+                    const int col0 = head * d;
+                    __nv_bfloat16* dst = qr.cache + ((((size_t)(page < 0 ? 0 : page) * 2 + 1) * qr.nkv + (head - qr.nq - qr.nkv)) * qr.P + within) * d;
+#pragma unroll 1
+                    for (int c = 0; c < d; c += 16) {
+                        uint32_t r[16];
+                        tmem_ld16(acc + hh * d + c, r);
+                        tmem_ld_wait();
+                        if (page < 0) continue;
+                        float bv[16];
+                        if (qr.bias) {
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) *(float4*)(bv + 4 * x) = *(const float4*)(qr.bias + col0 + c + 4 * x);
+                        } else {
+#pragma unroll
+                            for (int x = 0; x < 16; ++x) bv[x] = 0.f;
+                        }
+                        uint32_t pk[8];
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) {
+                            __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(r[2 * x]) + bv[2 * x], __uint_as_float(r[2 * x + 1]) + bv[2 * x + 1]);
+                            pk[x] = *(uint32_t*)&t2;
+                        }
+                        *(uint4*)(dst + c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                        *(uint4*)(dst + c + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = 0; c0 < bn; c0 += UNIT) {
+                    uint32_t r[16], r2[16];
+                    tmem_ld16(acc + c0, r);
+                    if constexpr (EPI == 1) tmem_ld16(acc + c0 + 16, r2);
+                    tmem_ld_wait();
+                    emit(ra0 + row_in_tile, rb0, c0, r, r2);
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -751,7 +870,8 @@ int choose_persistent_bn(int tiles_m, int N, int sms, int step) {
 // boundaries only.
 template <typename OT, int EPI>
 int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
-                      long long ldc, float* partials, int* flags, int* status, cudaStream_t stream) {
+                      long long ldc, float* partials, int* flags, int* status, cudaStream_t stream,
+                      const QkvRopeArgs* qr = nullptr) {
     static int sms = 0;
     if (!sms) {
         int dev = 0;
@@ -773,7 +893,7 @@ int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K
     // of parts (two per CTA at most, eight K blocks a part at least) that makes the parts' rounds
     // shortest.  The exchange of the partial tiles costs some 15 us, so the gain must be worth it
     // (a K block takes about 0.36 us).
-    if (partials && flags && num_tiles <= P_FLAG_CAP && num_tiles > sms && rest > 0) {
+    if (EPI != 2 && partials && flags && num_tiles <= P_FLAG_CAP && num_tiles > sms && rest > 0) {
         double best = 1.0;
         for (int w = 2; w <= 8 && rest * w <= 2LL * sms && total_kb / w >= 8; ++w) {
             const double rounds = (double)((rest * w + sms - 1) / sms) / w;
@@ -786,7 +906,7 @@ int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K
         }
     }
     const bool share = ways > 1;
-    if (!share && N >= P_BN_MAX) {
+    if (EPI != 2 && !share && N >= P_BN_MAX) {     // (epilogue 2 needs tiles that begin and end on heads)
         // whole tiles only: a narrower tile may fill the last round better
         bn = choose_persistent_bn(tiles_m, N, sms, step);
         num_tiles = whole_tiles = (long long)tiles_m * ((N + bn - 1) / bn);
@@ -803,8 +923,9 @@ int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K
         if (e != cudaSuccess) return fail("gemm_tc: cannot set %d bytes of shared memory: %s", PSmem::TOTAL, cudaGetErrorString(e));
         configured = true;
     }
+    QkvRopeArgs none = {};
     launch_kernel(kern, dim3((unsigned)grid), dim3(THREADS), PSmem::TOTAL, stream, ma, mb, (OT*)C, M, N, K, ldc, bn,
-                  tiles_m, (int)whole_tiles, (int)tail_tiles, ways, partials, flags, status);
+                  tiles_m, (int)whole_tiles, (int)tail_tiles, ways, partials, flags, status, qr ? *qr : none);
     return check_launch("gemm_tc_persistent");
 }
 }  // namespace
@@ -844,6 +965,28 @@ MHB_EXPORT int mhb_gemm_tc(const void* X, const void* W, void* C, int c_dtype, i
     if ((rc = make_map(&mb, W, N, K, ldw, bn))) return rc;
     if (c_dtype == MHB_F32) return dispatch_bn<false, float, 0>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
     return dispatch_bn<false, __nv_bfloat16, 0>(bn, ma, mb, C, M, N, K, ldc, nsplit, kbps, split_stride, swap ? 1 : 2, status, stream);
+}
+
+// The stacked q/k/v product of more than 64 tokens with bias, rotation and the append to the paged
+// KV cache done by its epilogue (see QkvRopeArgs): q_out [M, nq d] bfloat16, cache one layer's pool
+// [pages, 2, nkv, P, d] bfloat16, cos_sin [M, d] float32 (mhb_rope_table).  Head size 64 or 128.
+MHB_EXPORT int mhb_gemm_tc_qkv_rope(const void* X, const void* W, int M, int K, long long lda, long long ldw,
+                                    const float* bias, const float* cos_sin, const int* positions,
+                                    const int* tok_seg, const int* block_table, int table_width, void* q_out,
+                                    void* cache, int nq, int nkv, int d, int P, int num_pages, int write_kv,
+                                    int* status, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (d != 64 && d != 128) return fail("gemm_tc_qkv_rope: head size %d (64 or 128)", d);
+    if (K <= 0 || K % 8 || lda % 8 || ldw % 8) return fail("gemm_tc: K, lda and ldw must be multiples of 8 (K %d, lda %lld, ldw %lld)", K, lda, ldw);
+    if (((uintptr_t)X & 15) || ((uintptr_t)W & 15) || ((uintptr_t)q_out & 15) || ((uintptr_t)cache & 15))
+        return fail("gemm_tc_qkv_rope: operands must be 16-byte aligned");
+    if (nq <= 0 || nkv <= 0 || P <= 0) return fail("gemm_tc_qkv_rope: bad head counts or page size");
+    QkvRopeArgs qr;
+    qr.bias = bias; qr.cos_sin = cos_sin; qr.positions = positions; qr.tok_seg = tok_seg; qr.block_table = block_table;
+    qr.q_out = (__nv_bfloat16*)q_out; qr.cache = (__nv_bfloat16*)cache; qr.table_width = table_width;
+    qr.nq = nq; qr.nkv = nkv; qr.d = d; qr.P = P; qr.num_pages = num_pages; qr.write_kv = write_kv;
+    const int N = (nq + 2 * nkv) * d;
+    return launch_persistent<__nv_bfloat16, 2>(X, W, nullptr, M, N, K, lda, ldw, 0, nullptr, nullptr, status, stream, &qr);
 }
 
 // act[M, I] = silu(X Wg^T) * (X Wu^T) where W [2 I, K] holds gate and up rows interleaved in

@@ -218,6 +218,33 @@ def gemm_tc_swiglu(a, w, out, *, swap: bool, bn: int, status=None, scratch=None)
         c_int(1 if swap else 0), c_int(bn), *_scratch_ptrs(scratch), _ptr(status), _stream()), "gemm_tc_swiglu")
 
 
+def rope_table(positions, inv_freq, table, *, d: int, rotate: bool = True):
+    """table[t] = cos of token t's d/2 rotation angles, then their sin (float32), for the q/k/v
+    product's rotating epilogue."""
+    lib = build.load("elementwise")
+    _check(lib, lib.mhb_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(table), c_int(positions.shape[0]),
+                                   c_int(d), c_int(1 if rotate else 0), _stream()), "rope_table")
+
+
+def gemm_tc_qkv_rope(x, w, bias, cos_sin, positions, tok_seg, block_table, q_out, cache, *, nq, nkv, d,
+                     page_size, write_kv=True, status=None):
+    """The stacked q/k/v product of more than 64 tokens whose epilogue adds the bias, rotates q and k
+    and writes q to ``q_out`` and k, v into the pages of ``cache`` (one layer's pool)."""
+    lib = build.load("gemm_tc")
+    M, K = x.shape
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or q_out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc_qkv_rope: operands, q and the cache must be bfloat16")
+    if tuple(w.shape) != ((nq + 2 * nkv) * d, K) or not cache.is_contiguous() or not q_out.is_contiguous():
+        raise KernelError(f"gemm_tc_qkv_rope: w is {list(w.shape)}, expected [{(nq + 2 * nkv) * d}, {K}]; q and the pool must be contiguous")
+    if cos_sin.shape != (M, d) or cos_sin.dtype != torch.float32:
+        raise KernelError("gemm_tc_qkv_rope: the cos/sin table must be float32 [tokens, head_dim]")
+    _check(lib, lib.mhb_gemm_tc_qkv_rope(
+        _ptr(x), _ptr(w), c_int(M), c_int(K), c_longlong(x.stride(0)), c_longlong(w.stride(0)), _ptr(bias),
+        _ptr(cos_sin), _ptr(positions), _ptr(tok_seg), _ptr(block_table), c_int(block_table.shape[-1]), _ptr(q_out),
+        _ptr(cache), c_int(nq), c_int(nkv), c_int(d), c_int(page_size), c_int(cache.shape[0]),
+        c_int(1 if write_kv else 0), _ptr(status), _stream()), "gemm_tc_qkv_rope")
+
+
 def attention_simt(q, cache, out, part_acc, part_ml, items, num_items, max_items, positions,
                    block_table, tok_part_row, *, nq, nkv, d, page_size, window=0, scale=None):
     lib = build.load("attention_simt")

@@ -284,14 +284,18 @@ class GQAttention(Mixer):
     def forward(self, h, ctx: StepContext, cache: CacheView) -> Product:
         rt, ws, T = ctx.rt, ctx.ws, h.shape[0]
         meta = cache.meta
-        qkv = rt.linear(h, self.qkv_weight, ws, "qkv", out_dtype=torch.float32)
         q = ws.get("q", (T, self.nq * self.d), rt.dtype)
-        K.rope_append(
-            qkv.tensor, self.qkv_bias_vec, ctx.positions, ctx.tok_seg, meta["block_table"],
-            self.position.inv_freq, q, cache.storage, nq=self.nq, nkv=self.nkv, d=self.d,
-            page_size=cache.page_size, write_kv=cache.writable, rotate=self.position.rotates,
-            nsplit=qkv.nsplit, split_stride=qkv.split_stride, status=ctx.status,
-        )
+        fused = rt.qkv_rope_append(h, self.qkv_weight, self.qkv_bias_vec, ctx, self.position, meta["block_table"],
+                                   q, cache.storage, nq=self.nq, nkv=self.nkv, d=self.d,
+                                   page_size=cache.page_size, write_kv=cache.writable)
+        if not fused:
+            qkv = rt.linear(h, self.qkv_weight, ws, "qkv", out_dtype=torch.float32)
+            K.rope_append(
+                qkv.tensor, self.qkv_bias_vec, ctx.positions, ctx.tok_seg, meta["block_table"],
+                self.position.inv_freq, q, cache.storage, nq=self.nq, nkv=self.nkv, d=self.d,
+                page_size=cache.page_size, write_kv=cache.writable, rotate=self.position.rotates,
+                nsplit=qkv.nsplit, split_stride=qkv.split_stride, status=ctx.status,
+            )
         attn = ws.get("attn", (T, self.nq * self.d), rt.dtype)
         part_rows = max(1, meta["part_rows_cap"])
         part_acc = ws.get("attn_part_acc", (part_rows, self.nq, self.d), torch.float32)

@@ -123,6 +123,13 @@ class Runtime:
         gate are followed by the same rows of up.  Here: one block, [gate | up]."""
         return torch.cat((gate, up), 0).contiguous(), gate.shape[0]
 
+    def qkv_rope_append(self, x, weight, bias, ctx, position, block_table, q_out, cache_storage, *,
+                        nq: int, nkv: int, d: int, page_size: int, write_kv: bool) -> bool:
+        """The stacked q/k/v product with bias, rotation and the append to the cache in ONE kernel,
+        if this runtime has one for these sizes: then q_out and the cache are written and True is
+        returned.  False: the caller runs the product and the rotary kernel one after the other."""
+        return False
+
     def linear_swiglu(self, x, weight, block: int, ws: Workspace, name: str) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) in the compute dtype."""
         gu = self.linear(x, weight, ws, name + "_gu")

@@ -214,6 +214,56 @@ def test_gemm_tensor_core_refuses_unaligned_k():
         K().gemm_tc(a, w, torch.empty(4, 9, device=DEV), swap=True, bn=16)
 
 
+@pytest.mark.parametrize("nq,nkv,d,P_,T,Kd", [(28, 4, 128, 16, 300, 3584), (3, 1, 64, 32, 70, 192), (5, 5, 128, 8, 129, 256),
+                                               (2, 1, 64, 16, 2100, 64)])
+@pytest.mark.parametrize("rotate", [True, False])
+def test_gemm_qkv_epilogue_rotates_and_appends(nq, nkv, d, P_, T, Kd, rotate):
+    """The q/k/v product whose epilogue adds the bias, rotates and appends to the paged cache,
+    against the product followed by the rotary kernel (which has its own test against the plain
+    formulas): two segments, one of which starts inside a page."""
+    N = (nq + 2 * nkv) * d
+    x = rnd(T, Kd, dtype=torch.bfloat16, seed=1)
+    w = rnd(N, Kd, dtype=torch.bfloat16, seed=2, scale=1.0 / math.sqrt(Kd))
+    bias = rnd(N, seed=3) * 0.1
+    theta = 10000.0
+    inv = (theta ** (-torch.arange(0, d, 2).float() / d)).to(DEV)
+    n0 = T // 3
+    positions = torch.tensor(list(range(37, 37 + n0)) + list(range(0, T - n0)), dtype=torch.int32, device=DEV)
+    tok_seg = torch.tensor([0] * n0 + [1] * (T - n0), dtype=torch.int32, device=DEV)
+    pages0, pages1 = -(-(37 + n0) // P_), -(-(T - n0) // P_)
+    num_pages = pages0 + pages1 + 3
+    perm = torch.randperm(num_pages, generator=torch.Generator().manual_seed(5)).tolist()
+    table = torch.full((2, max(pages0, pages1)), -1, dtype=torch.int32)
+    table[0, :pages0] = torch.tensor(perm[:pages0])
+    table[1, :pages1] = torch.tensor(perm[pages0:pages0 + pages1])
+    table = table.to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    # reference: float32 product, then the rotary kernel
+    qkv = torch.empty(T, N, device=DEV)
+    K().gemm_simt(x.float(), w.float(), qkv)
+    q_ref = torch.empty(T, nq * d, dtype=torch.bfloat16, device=DEV)
+    cache_ref = torch.zeros(num_pages, 2, nkv, P_, d, dtype=torch.bfloat16, device=DEV)
+    K().rope_append(qkv, bias, positions, tok_seg, table, inv, q_ref, cache_ref, nq=nq, nkv=nkv, d=d, page_size=P_,
+                    rotate=rotate, status=status)
+    cs = torch.empty(T, d, device=DEV)
+    K().rope_table(positions, inv, cs, d=d, rotate=rotate)
+    q = torch.full((T, nq * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    cache = torch.zeros(num_pages, 2, nkv, P_, d, dtype=torch.bfloat16, device=DEV)
+    K().gemm_tc_qkv_rope(x, w, bias, cs, positions, tok_seg, table, q, cache, nq=nq, nkv=nkv, d=d, page_size=P_,
+                         status=status)
+    assert int(status) == 0
+    scale = float(qkv.abs().max())
+    torch.testing.assert_close(q.float(), q_ref.float(), atol=1e-2 * scale, rtol=1.6e-2)
+    torch.testing.assert_close(cache.float(), cache_ref.float(), atol=1e-2 * scale, rtol=1.6e-2)
+    written, written_ref = cache.abs().sum(-1) > 0, cache_ref.abs().sum(-1) > 0          # per (page, plane, head, slot)
+    assert bool(written_ref.any()) and bool((written == written_ref).all())            # the same slots were written
+    # without write access nothing is appended
+    cache2 = torch.zeros_like(cache)
+    K().gemm_tc_qkv_rope(x, w, bias, cs, positions, tok_seg, table, q, cache2, nq=nq, nkv=nkv, d=d, page_size=P_,
+                         write_kv=False, status=status)
+    assert int(cache2.abs().sum()) == 0
+
+
 # ---- rotary + append -----------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,d,P_", [(4, 2, 16, 16), (3, 1, 32, 32), (10, 2, 48, 16), (7, 7, 128, 8)])
