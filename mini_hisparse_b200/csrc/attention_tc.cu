@@ -24,8 +24,8 @@
 // tiles): a key tile is free as soon as its scores are done, long before its values are used, so
 // the loads run two tiles ahead.  Two CTAs share an SM (tensor memory 2 x 256 columns), so one
 // CTA's softmax overlaps the other's MMAs.
-// Warp 0 issues the TMA loads, warp 1 owns tensor memory and issues the MMAs, warps 2-5 are the
-// softmax warps.  Every mbarrier wait is bounded (status bit 16 when one runs out).
+// Warps 0 and 6 issue the TMA loads (keys, values), warp 1 owns tensor memory and issues the MMAs,
+// warps 2-5 are the softmax warps.  Every mbarrier wait is bounded (status bit 16 when one runs out).
 //
 // Needs head_dim 64 or 128 and a page size that divides 64.  An item may cover a part of its keys
 // (the planner splits long tiles when there are too few of them for the GPU): it then leaves its
@@ -41,7 +41,7 @@ MHB_EXPORT const char* mhb_last_error() { return error_buffer(); }
 namespace {
 constexpr int ROWS = 128;
 constexpr int KT = 64;
-constexpr int THREADS = 192;
+constexpr int THREADS = 224;
 constexpr int ITEM_INTS = 8;
 
 struct AttnArgs {
@@ -147,17 +147,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
     const uint32_t tmem = *tmem_slot;
     bool ok = true;
 
-    if (warp == 0) {
-        // ---- TMA warp: one lane per page of a tile; every page slot of a stage is filled.  Keys run
-        // one tile ahead of values: K(j + 1) is asked for before V(j). -----------------------------
+    if (warp == 0 || warp == 6) {
+        // ---- TMA warps: warp 0 brings the key tiles, warp 6 the value tiles, one lane per page of a
+        // tile; every page slot of a stage is filled.  Two warps because each waits for its own ring:
+        // a key tile is free as soon as its scores are done, a value tile only after P V two tiles
+        // later, and one warp doing both in turn held every key tile back behind a value tile (the MMA
+        // thread then waited over a thousand cycles per tile for keys).
+        const bool values = warp == 6;
         const int pages_per_tile = KT / a.P;
-        auto load = [&](int j, bool values) {
-            const int stage = values ? j % V_STAGES : j % K_STAGES;
-            const int round = values ? j / V_STAGES : j / K_STAGES;
+        const int stages = values ? V_STAGES : K_STAGES;
+        for (int j = 0; j < ntiles && ok; ++j) {
+            const int stage = j % stages;
             const uint32_t full = values ? v_full(stage) : k_full(stage);
-            if (lane == 0) ok = mbar_wait(values ? v_empty(stage) : k_empty(stage), (round & 1) ^ 1);
+            if (lane == 0) ok = mbar_wait(values ? v_empty(stage) : k_empty(stage), ((j / stages) & 1) ^ 1);
             ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) return;
+            if (!ok) break;
             const int kp0 = tile_begin + j * KT + lane * a.P;
             int page = -1;
             if (lane < pages_per_tile) {
@@ -174,11 +178,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h) tma_load_2d(dst + h * KT * 128, &kv_map, h * 64, row0, full);
             }
-        };
-        if (ntiles > 0) load(0, false);
-        for (int j = 0; j < ntiles && ok; ++j) {
-            if (j + 1 < ntiles) load(j + 1, false);
-            if (ok) load(j, true);
         }
     } else if (warp == 1) {
         // ---- MMA warp ----------------------------------------------------------------------------------
@@ -241,7 +240,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
             __syncwarp();
             if (lane == 0) mbar_arrive(q_full);
         }
-        const int qp = live ? a.positions[t] : -1;
+        // a row beyond the tile's rows sees every key (its queries are zeros and nothing of it is
+        // stored): it must not drag its warp through the masked path on every tile
+        const int qp = live ? a.positions[t] : 0x3fffffff;
         const float scale_log2 = a.scale * 1.4426950408889634f;
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
         float m_ref = -INFINITY;      // the maximum the exponentials refer to (at most 2^8 below the true one)
@@ -255,21 +256,24 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
             tmem_ld64(lane_addr + (j & 1) * KT, sr);
             tmem_ld_wait();
             const int t0 = tile_begin + j * KT;
-            float mx = -INFINITY;
             // most tiles lie wholly inside this row's range of keys: no mask then
             const int lo = max(kv_begin, a.window > 0 ? qp - a.window + 1 : 0), hi = min(kv_end - 1, qp);
-            if (t0 >= lo && t0 + KT - 1 <= hi) {
-#pragma unroll
-                for (int x = 0; x < KT; ++x) mx = fmaxf(mx, __uint_as_float(sr[x]));
-            } else {
+            if (!(t0 >= lo && t0 + KT - 1 <= hi)) {
 #pragma unroll
                 for (int x = 0; x < KT; ++x) {
                     const int kp = t0 + x;
-                    const float v = (kp >= lo && kp <= hi) ? __uint_as_float(sr[x]) : -INFINITY;
-                    sr[x] = __float_as_uint(v);
-                    mx = fmaxf(mx, v);
+                    if (!(kp >= lo && kp <= hi)) sr[x] = __float_as_uint(-INFINITY);
                 }
             }
+            // the maximum as four independent chains (one chain of 64 dependent operations was a
+            // quarter of this thread's time per tile)
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int x = 0; x < KT; x += 4) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) mx4[q] = fmaxf(mx4[q], __uint_as_float(sr[x + q]));
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // raise the reference maximum only when the row's maximum outgrew it by more than 2^8
             const bool raise = mx > -INFINITY && (m_ref == -INFINITY || (mx - m_ref) * scale_log2 > 8.f);
             const float m_old = m_ref;
@@ -278,15 +282,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
             // the exponentials (2^(s * c - m * c): one FMA and one ex2 each), packed to bfloat16, while
             // the previous tile's P V may still run
             const float m_scaled = m_use * scale_log2;
-            float psum = 0.f;
+            float ps4[4] = {0.f, 0.f, 0.f, 0.f};       // four independent chains again
             uint32_t pw[KT / 2];
 #pragma unroll
             for (int x = 0; x < KT; x += 2) {
                 const float p0 = fast_exp2(fmaf(__uint_as_float(sr[x]), scale_log2, -m_scaled));
                 const float p1 = fast_exp2(fmaf(__uint_as_float(sr[x + 1]), scale_log2, -m_scaled));
-                psum += p0 + p1;
+                ps4[(x >> 1) & 3] += p0 + p1;
                 pw[x >> 1] = pack_bf16(p0, p1);
             }
+            const float psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
             const bool rescale = raise && m_old > -INFINITY;     // there is an accumulator to rescale
             if (__any_sync(0xffffffffu, rescale)) {
                 // O is only ours once the previous tile's P V has completed
