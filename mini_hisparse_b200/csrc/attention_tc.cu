@@ -59,7 +59,7 @@ struct AttnArgs {
 };
 
 constexpr int K_STAGES = 3;
-constexpr int V_STAGES = 2;
+constexpr int V_STAGES = 2;      // value tile j shares its barriers with P(j): both are indexed by j & 1
 
 template <int D>
 struct Layout {
@@ -69,7 +69,7 @@ struct Layout {
     static constexpr int K_OFFSET = Q_BYTES;
     static constexpr int V_OFFSET = K_OFFSET + K_STAGES * K_BYTES;
     static constexpr int BAR_OFFSET = V_OFFSET + V_STAGES * K_BYTES;
-    static constexpr int NUM_BARS = 2 * K_STAGES + 2 * V_STAGES + 1 + 2 + 2 + 3;   // k, v full/empty, q, s full, p full, o done, o final
+    static constexpr int NUM_BARS = 2 * K_STAGES + 1 + 2 + 2 + 3;   // k full/empty, q, s full, p+v full, o done, o final
     static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16;
     static constexpr int TMEM_COLS = 256;                      // S/P: 2 x 64 columns, O tile: D columns from column 128
 };
@@ -95,13 +95,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
     const uint32_t bars = base + L::BAR_OFFSET;
     auto k_full = [&](int s) { return bars + 8 * s; };
     auto k_empty = [&](int s) { return bars + 8 * (K_STAGES + s); };
-    auto v_full = [&](int s) { return bars + 8 * (2 * K_STAGES + s); };
-    auto v_empty = [&](int s) { return bars + 8 * (2 * K_STAGES + V_STAGES + s); };
-    constexpr int B0 = 2 * K_STAGES + 2 * V_STAGES;
+    constexpr int B0 = 2 * K_STAGES;
     const uint32_t q_full = bars + 8 * B0;
     auto s_full = [&](int b) { return bars + 8 * (B0 + 1 + b); };
-    // a softmax warp may be one tile ahead of another, so P(j) and P(j + 1) have barriers of their own
-    auto p_full = [&](int b) { return bars + 8 * (B0 + 3 + b); };
+    // P(j) is in tensor memory AND V(j) has landed: one barrier (four softmax warps and the value
+    // producer arrive on it), because every barrier the MMA thread looks at costs it some 290 cycles.
+    // A softmax warp may be one tile ahead of another, so even and odd tiles have barriers of their own;
+    // V(j + 2) is only asked for when P V(j) has completed, so nothing of a later tile arrives early.
+    auto pv_full = [&](int b) { return bars + 8 * (B0 + 3 + b); };
     // P V(j) has completed: a barrier for even and one for odd tiles, since the waiting threads are
     // not in step with the value warp and a parity wait cannot tell phases two apart
     auto o_done = [&](int b) { return bars + 8 * (B0 + 5 + b); };
@@ -132,10 +133,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < K_STAGES; ++s) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); }
-        for (int s = 0; s < V_STAGES; ++s) { mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1); }
         mbar_init(q_full, 4);
         for (int b = 0; b < 2; ++b) mbar_init(s_full(b), 1);
-        for (int b = 0; b < 2; ++b) mbar_init(p_full(b), 4);
+        for (int b = 0; b < 2; ++b) mbar_init(pv_full(b), 5);
         for (int b = 0; b < 2; ++b) mbar_init(o_done(b), 1);
         mbar_init(o_final, 1);
         mbar_fence_init();
@@ -158,8 +158,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
         const int stages = values ? V_STAGES : K_STAGES;
         for (int j = 0; j < ntiles && ok; ++j) {
             const int stage = j % stages;
-            const uint32_t full = values ? v_full(stage) : k_full(stage);
-            if (lane == 0) ok = mbar_wait(values ? v_empty(stage) : k_empty(stage), ((j / stages) & 1) ^ 1);
+            const uint32_t full = values ? pv_full(stage) : k_full(stage);
+            // a value stage is free when P V two tiles back has completed (o_done of the same parity)
+            if (lane == 0) ok = mbar_wait(values ? o_done(stage) : k_empty(stage), ((j / stages) & 1) ^ 1);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             const int kp0 = tile_begin + j * KT + lane * a.P;
@@ -207,8 +208,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
                 if (ok) { tc_fence_after(); issue_s(j); }
             }
             for (int j = 0; j < ntiles && ok; ++j) {
-                ok = mbar_wait(p_full(j & 1), (j >> 1) & 1);         // P(j) is in tensor memory, O is rescaled if needed
-                if (ok) ok = mbar_wait(v_full(j % V_STAGES), (j / V_STAGES) & 1);
+                ok = mbar_wait(pv_full(j & 1), (j >> 1) & 1);        // P(j) is in tensor memory, O is rescaled if needed, V(j) has landed
                 if (ok && j + 2 < ntiles) ok = mbar_wait(k_full((j + 2) % K_STAGES), ((j + 2) / K_STAGES) & 1);
                 if (!ok) break;
                 tc_fence_after();
@@ -218,8 +218,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
                     const uint64_t db = smem_desc_mnmajor(v_s + k * 16 * 128, KT * 128, 1024);
                     umma_bf16_tmem_a(tmem + 128, tmem + (j & 1) * KT + k * 8, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
                 }
-                umma_commit(o_done(j & 1));             // O holds tiles 0..j when this completes
-                umma_commit(v_empty(j % V_STAGES));     // V(j) is consumed
+                umma_commit(o_done(j & 1));             // O holds tiles 0..j and V(j) is consumed when this completes
                 if (j + 1 == ntiles) umma_commit(o_final);
                 if (j + 2 < ntiles) issue_s(j + 2);
             }
@@ -316,7 +315,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
             l_run += psum;
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full(j & 1));
+            if (lane == 0) mbar_arrive(pv_full(j & 1));
         }
         if (ok && ntiles > 0) ok = mbar_wait(o_final, 0);
         tc_fence_after();
