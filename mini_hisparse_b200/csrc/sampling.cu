@@ -40,9 +40,11 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V,
     const int c0 = min(V, tid * chunk), c1 = min(V, c0 + chunk);
 
     // ---- argmax (lowest index on ties; NaN never wins) ----
+    // Consecutive threads read consecutive values (a thread sees its own indices in rising order, so
+    // it keeps the first of equal values; the reduction below prefers the lower index on ties).
     float best = -INFINITY;
-    int best_i = c0 < V ? c0 : V - 1;
-    for (int i = c0; i < c1; ++i) {
+    int best_i = tid < V ? tid : V - 1;
+    for (int i = tid; i < V; i += THREADS) {
         const float v = row[i];
         if (v > best) { best = v; best_i = i; }
     }
