@@ -307,7 +307,9 @@ class ModelRunner:
         self.use_graphs = use_graphs and model.graph_safe
         self.graphs: dict[tuple[int, int], _DecodeGraph] = {}
         self.observer = None
-        self.stats = {"steps": 0, "tokens": 0, "graph_steps": 0}
+        self.side_stream = None
+        self.side_events = None
+        self.stats = {"steps": 0, "tokens": 0, "graph_steps": 0, "two_stream_layers": 0}
         build.build_all(model.kernel_modules())
 
     def _cache_views(self, group_meta) -> list[CacheView | None]:
@@ -358,13 +360,23 @@ class ModelRunner:
 
     def _step_eager(self, entries, segments, T):
         views = self.batch.eager(entries, segments)
-        return self._forward(self.ws, views, segments, T)
+        return self._forward(self.ws, views, segments, T, side=True)
 
-    def _forward(self, ws, views, segments, T):
+    def _forward(self, ws, views, segments, T, side: bool = False):
         ctx = self.batch.context(self.rt, ws, self.status, views, segments)
+        if side:
+            # a second stream for parts that have two independent kernels to run (attention over long
+            # portions beside attention over decode tokens); never inside a graph capture
+            if self.side_stream is None:
+                self.side_stream = torch.cuda.Stream(self.device)
+                self.side_events = (torch.cuda.Event(), torch.cuda.Event())
+            ctx.extras["side_stream"] = self.side_stream
+            ctx.extras["side_events"] = self.side_events
         caches = self._cache_views(views["groups"])
         with K.stream_scope():
-            return self.model.forward(ctx, caches, views["rows"], observer=self.observer)
+            out = self.model.forward(ctx, caches, views["rows"], observer=self.observer)
+        self.stats["two_stream_layers"] += ctx.extras.get("two_stream_layers", 0)
+        return out
 
     def _step_graph(self, entries, segments):
         B = len(segments)

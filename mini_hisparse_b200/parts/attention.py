@@ -309,7 +309,7 @@ class GQAttention(Mixer):
             tma = K.attention_tma_supports(self.d, cache.page_size)
             kernel = K.attention_tma if tma else K.attention_mma
             extra = {"status": ctx.status} if tma else {}
-            if n_small:
+            def short_segments():
                 chunks = -(-(self.nq // self.nkv) // ROW_TILE)
                 counters = ws.get_zeroed("attn_counters", (T * self.nkv * chunks,), torch.int32)
                 # short segments have at most SPLIT_MAX_TOKENS tokens: only the keys that close to a
@@ -317,7 +317,8 @@ class GQAttention(Mixer):
                 fresh = {"fresh": SPLIT_MAX_TOKENS} if tma else {}
                 kernel(*args, meta["items"], n_small, 16, *tail, **common, **extra, **fresh,
                        tok_nsplit=meta["tok_nsplit"], counters=counters)
-            if n_big:
+
+            def long_portions():
                 big_items = meta["items"][n_small * ITEM_INTS:]
                 if self.big_tile_rows == 128:
                     if not tma:
@@ -332,6 +333,27 @@ class GQAttention(Mixer):
                                             nq=self.nq, d=self.d)
                 else:
                     kernel(*args, big_items, n_big, 64, *tail, **common, **extra)
+
+            side = ctx.extras.get("side_stream") if (n_small >= 8 and n_big >= 8 and not meta.get("big_split")) else None
+            if side is not None:
+                # The two kernels touch different tokens: the long portions run on a second stream beside
+                # the short segments (a mixed serving step has some dozens of decode tokens beside a
+                # prompt portion, and neither kernel fills the GPU for as long as the other runs).
+                ctx.extras["two_stream_layers"] = ctx.extras.get("two_stream_layers", 0) + 1
+                main = torch.cuda.current_stream()
+                fork, join = ctx.extras["side_events"]
+                fork.record(main)
+                side.wait_event(fork)
+                with torch.cuda.stream(side), K.stream_scope():
+                    long_portions()
+                    join.record(side)
+                short_segments()
+                main.wait_event(join)
+            else:
+                if n_small:
+                    short_segments()
+                if n_big:
+                    long_portions()
         elif n_small + n_big:
             K.attention_simt(*args, meta["items"], n_small + n_big, n_small + n_big, *tail, **common)
         if meta["any_split"] and not self.tensor_core_attention:

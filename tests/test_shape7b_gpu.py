@@ -112,3 +112,43 @@ def test_7b_layer_sizes_long_prompt_shares_tiles_along_k(folder):
     torch.testing.assert_close(outs[0], ref, atol=0.03 * float(ref.abs().max()), rtol=0.03)
     assert (outs[0].argmax(-1) == ref.argmax(-1)).float().mean() > 0.9
     cache.assert_invariants()
+
+
+def test_7b_layer_sizes_decode_tokens_beside_a_long_portion(folder):
+    """One step with eight decode tokens and a 300-token portion, bfloat16: the attention of the long
+    portion (tcgen05 kernel) runs on a second stream beside the attention of the decode tokens; every
+    row is compared with the plain implementation of its own request."""
+    from mini_hisparse_b200 import CacheConfig, CacheManager, load_model
+    from mini_hisparse_b200.engine import ModelRunner, StepEntry
+
+    torch.backends.cuda.matmul.allow_tf32 = False
+    cfg, w = P.load_folder(folder, dtype=torch.float32, device="cuda:0")
+    model = load_model(folder, dtype="bfloat16")
+    cache = CacheManager(model.cache_needs, CacheConfig(num_pages=120, page_size=16, max_requests=10,
+                                                        dtype=model.rt.dtype))
+    runner = ModelRunner(model, cache)
+    short = [random_tokens(CONFIG["vocab_size"], 20 + 9 * i, seed=30 + i) for i in range(8)]
+    long_prompt = random_tokens(CONFIG["vocab_size"], 420, seed=50)
+    for i, toks in enumerate(short):                       # prefill all but the last token of the short ones
+        cache.open(f"s{i}")
+        runner.step([StepEntry(f"s{i}", toks[:-1], [])])
+    cache.open("long")
+    runner.step([StepEntry("long", long_prompt[:120], [])])
+    assert runner.stats["two_stream_layers"] == 0
+    entries = [StepEntry(f"s{i}", [toks[-1]], [0]) for i, toks in enumerate(short)]
+    entries.insert(3, StepEntry("long", long_prompt[120:], [0, 150, 299]))
+    out = runner.step(entries).float().cpu()
+    runner.check_status()
+    assert runner.stats["two_stream_layers"] == CONFIG["num_hidden_layers"]     # the step took the two-stream path
+    rows, r = [], 0
+    for e in entries:
+        if e.request == "long":
+            ref = P.forward_logits(cfg, w, long_prompt)[[120, 270, 419]].cpu()
+        else:
+            ref = P.forward_logits(cfg, w, short[int(e.request[1:])])[-1:].cpu()
+        got = out[r : r + ref.shape[0]]
+        r += ref.shape[0]
+        torch.testing.assert_close(got, ref, atol=0.03 * float(ref.abs().max()), rtol=0.03)
+        rows.append((got.argmax(-1) == ref.argmax(-1)).float())
+    assert torch.cat(rows).mean() > 0.8
+    cache.assert_invariants()
