@@ -21,9 +21,11 @@
 // Two S buffers let the MMA warp compute the next tile's scores while the softmax warps work, and
 // since each tile's P has a buffer of its own the softmax warps never wait for a P V product
 // (except to rescale).  Keys and values travel in rings of their own (three key tiles, two value
-// tiles): a key tile is free as soon as its scores are done, long before its values are used, so
-// the loads run two tiles ahead.  Two CTAs share an SM (tensor memory 2 x 256 columns), so one
-// CTA's softmax overlaps the other's MMAs.
+// tiles), each fed by a producer warp of its own: a key tile is free as soon as its scores are
+// done, long before its values are used, so the key loads run two tiles ahead.  Two CTAs share an
+// SM (tensor memory 2 x 256 columns).  What sets the pace is the thread that issues the MMAs: every
+// barrier it looks at costs it some 290 cycles, so it looks at two per tile (P and V together, the
+// key tile) and commits three times (scores, key ring, P V).
 // Warps 0 and 6 issue the TMA loads (keys, values), warp 1 owns tensor memory and issues the MMAs,
 // warps 2-5 are the softmax warps.  Every mbarrier wait is bounded (status bit 16 when one runs out).
 //

@@ -5,15 +5,22 @@
 // back with tcgen05.ld for the epilogue.
 //
 // Both operands are row-major with K contiguous (nn.Linear layout, mini_hisparse/model.py:57-60:
-// y = x W^T).  Two shapes of use:
-//   * many tokens (prefill): A = activations [M, K], B = weights [N, K]; C[m, n] row-major.
+// y = x W^T).  Three shapes of use:
 //   * few tokens (decode):   A = weights [N, K] (the 128-row operand streams the weights),
-//     B = activations [M <= 64, K]; the tile is written transposed, C[m, n] again.
-// With nsplit > 1 the K range is cut; split z writes a float32 partial matrix at
-// C + z * split_stride and the consumer sums the parts in order.
+//     B = activations [M <= 256, K]; the tile is written transposed, C[m, n] row-major again.
+//     One tile per CTA, two CTAs per SM for tiles of up to 64 tokens.
+//   * tokens in between:     the same one-tile kernel with A = activations, B = weights.
+//     With nsplit > 1 the K range is cut; split z writes a float32 partial matrix at
+//     C + z * split_stride and the consumer sums the parts in order.
+//   * many tokens (prefill): a persistent kernel, one CTA per SM (further down), with the plain,
+//     the SwiGLU and the rotate-and-append epilogue.
 //
 // Warp roles (192 threads): warp 0 issues TMA loads, warp 1 owns tensor memory and issues the
 // MMAs, warps 2-5 read the accumulator (warp w may touch lanes 32*(w%4) .. +31) and store.
+// The thread that issues MMAs pays some 250-290 cycles for every mbarrier it looks at afterwards
+// (measured: a loop of MMAs alone runs at 128 cycles per 128 x 256 x 16 MMA and 64 for N = 128,
+// but a K block of four MMAs costs 480 cycles as soon as the loop waits on a barrier, whatever
+// N): tiles narrower than 256 are not faster per K block, only their last round may fit better.
 // Every wait on an mbarrier is bounded; a wait that runs out sets bit 4 of *status and the CTA
 // leaves through the common exit, which frees its tensor memory.
 #include <cuda.h>
