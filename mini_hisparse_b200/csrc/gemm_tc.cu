@@ -418,20 +418,26 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     uint32_t* tmem_slot = (uint32_t*)(smem + S::BARRIER_OFFSET + 8 * (2 * P_STAGES + 4));
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_kb = (K + BK - 1) / BK;
-    // tiles [0, whole_tiles) go round-robin as whole tiles; then the ways * tail_tiles parts of the
-    // tiles [whole_tiles, + tail_tiles): entry e is part e / tail_tiles of tile e % tail_tiles
-    const int my_whole = whole_tiles > (int)blockIdx.x ? (whole_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    // First the ways * tail_tiles parts of the tiles [whole_tiles, + tail_tiles) (entry e is part
+    // e / tail_tiles of tile e % tail_tiles), then the tiles [0, whole_tiles) as whole tiles, both
+    // round-robin.  The parts come first so that their exchange and reduction (the epilogue warps'
+    // business) happen while the MMA warp is busy with the whole tiles, not at the kernel's end.
     const int entries = tail_tiles * ways;
+    const int my_parts = entries > (int)blockIdx.x ? (entries - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
     // segment j of this CTA: a tile, a range of its K blocks and, for a part, its entry (else -1)
     auto segment = [&](int j, int& t, int& kb0, int& kb1, int& entry) -> bool {
-        if (j < my_whole) { t = (int)blockIdx.x + j * (int)gridDim.x; kb0 = 0; kb1 = total_kb; entry = -1; return true; }
-        const int e = (int)blockIdx.x + (j - my_whole) * (int)gridDim.x;
-        if (e >= entries) return false;
-        const int part = e / tail_tiles;
-        t = whole_tiles + e % tail_tiles;
-        kb0 = (int)((long long)part * total_kb / ways);
-        kb1 = (int)((long long)(part + 1) * total_kb / ways);
-        entry = ways > 1 ? e : -1;
+        if (j < my_parts) {
+            const int e = (int)blockIdx.x + j * (int)gridDim.x;
+            const int part = e / tail_tiles;
+            t = whole_tiles + e % tail_tiles;
+            kb0 = (int)((long long)part * total_kb / ways);
+            kb1 = (int)((long long)(part + 1) * total_kb / ways);
+            entry = ways > 1 ? e : -1;
+            return true;
+        }
+        const long long whole = (long long)blockIdx.x + (long long)(j - my_parts) * gridDim.x;
+        if (whole >= whole_tiles) return false;
+        t = (int)whole; kb0 = 0; kb1 = total_kb; entry = -1;
         return true;
     };
     const uint32_t stage_tx = S::A_BYTES + bn * BK * 2;
@@ -561,10 +567,82 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 }
             }
         };
+        // ---- second pass: the shared tiles.  The CTAs that hold parts of a tile divide its columns
+        // among themselves; each adds the parts in the order of their K ranges and stores. ---------
+        auto reduce_shared = [&](const int (&shared_entry)[2], int shared_count) {
+        for (int i = 0; i < shared_count && ok; ++i) {
+            const int tail_index = shared_entry[i] % tail_tiles, rank = shared_entry[i] / tail_tiles;
+            const int ts = whole_tiles + tail_index, parts = ways;
+            const volatile int* flag = flags + 4 * ts + quarter;
+            uint32_t spins = 0;
+            while (*flag < parts && ++spins < WAIT_LIMIT) __nanosleep(32);
+            if (spins >= WAIT_LIMIT) { ok = false; break; }
+            __threadfence();
+            const int ra0 = (ts % tiles_m) * BM, rb0 = (ts / tiles_m) * bn;
+#pragma unroll 1
+            for (int c0 = rank * UNIT; c0 < bn; c0 += parts * UNIT) {
+                float s[16], s2[16];
+#pragma unroll
+                for (int x = 0; x < 16; ++x) s[x] = s2[x] = 0.f;
+                // the loads of several parts are in flight together; the sums stay in the parts' order
+                constexpr int BATCH = EPI == 1 ? 2 : 4;
+                for (int p0 = 0; p0 < parts; p0 += BATCH) {
+                    uint4 v[BATCH][4], w[EPI == 1 ? BATCH : 1][4];
+#pragma unroll
+                    for (int q = 0; q < BATCH; ++q) {
+                        const int p = p0 + q < parts ? p0 + q : parts - 1;
+                        const int e = p * tail_tiles + tail_index;        // part p of this tile: its CTA and slot
+                        const float* src = partials + (size_t)(2 * (e % (int)gridDim.x) + e / (int)gridDim.x) * P_PARTIAL_FLOATS;
+                        const uint4* a = (const uint4*)(src + ((size_t)(c0 >> 4) * BM + row_in_tile) * 16);
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) v[q][x] = __ldcg(a + x);
+                        if constexpr (EPI == 1) {
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) w[q][x] = __ldcg(a + BM * 4 + x);    // the next 16 columns: the up half
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < BATCH; ++q) {
+                        if (p0 + q < parts) {
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) {
+                                s[4 * x] += __uint_as_float(v[q][x].x); s[4 * x + 1] += __uint_as_float(v[q][x].y);
+                                s[4 * x + 2] += __uint_as_float(v[q][x].z); s[4 * x + 3] += __uint_as_float(v[q][x].w);
+                            }
+                            if constexpr (EPI == 1) {
+#pragma unroll
+                                for (int x = 0; x < 4; ++x) {
+                                    s2[4 * x] += __uint_as_float(w[q][x].x); s2[4 * x + 1] += __uint_as_float(w[q][x].y);
+                                    s2[4 * x + 2] += __uint_as_float(w[q][x].z); s2[4 * x + 3] += __uint_as_float(w[q][x].w);
+                                }
+                            }
+                        }
+                    }
+                }
+                uint32_t r[16], r2[16];
+#pragma unroll
+                for (int x = 0; x < 16; ++x) { r[x] = __float_as_uint(s[x]); r2[x] = __float_as_uint(s2[x]); }
+                emit(ra0 + row_in_tile, rb0, c0, r, r2);
+            }
+            __syncwarp();
+            // the last quarter-warp to have read puts the counter back to zero for the next launch
+            if (lane == 0 && atomicAdd(flags + 4 * ts + quarter, 1) == 2 * parts - 1) flags[4 * ts + quarter] = 0;
+        }
+        };
         // ---- first pass: every segment; a tile that is shared goes to the workspace ----------------
         int shared_entry[2], shared_count = 0;
+        bool reduced = false;
         int t, kb0, kb1, entry;
-        for (int j = 0; ok && segment(j, t, kb0, kb1, entry); ++j) {
+        for (int j = 0; ok && (j < my_parts || !reduced || segment(j, t, kb0, kb1, entry)); ++j) {
+            if (j >= my_parts && !reduced) {
+                // all of this CTA's parts are in the workspace: reduce its share of the shared tiles
+                // now, while the MMA warp works on the first whole tile
+                reduce_shared(shared_entry, shared_count);
+                reduced = true;
+                --j;
+                continue;
+            }
+            if (j < my_parts) segment(j, t, kb0, kb1, entry);
             const int b = j & 1;
             const int ra0 = (t % tiles_m) * BM, rb0 = (t / tiles_m) * bn;
             ok = mbar_wait(acc_full_bar(b), (j >> 1) & 1);
@@ -708,66 +786,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             __syncwarp();
             if (lane == 0) mbar_arrive_plain(acc_empty_bar(b));    // this warp has read its quarter
         }
-        // ---- second pass: the shared tiles.  The CTAs that hold parts of a tile divide its columns
-        // among themselves; each adds the parts in the order of their K ranges and stores. ---------
-        for (int i = 0; i < shared_count && ok; ++i) {
-            const int tail_index = shared_entry[i] % tail_tiles, rank = shared_entry[i] / tail_tiles;
-            const int ts = whole_tiles + tail_index, parts = ways;
-            const volatile int* flag = flags + 4 * ts + quarter;
-            uint32_t spins = 0;
-            while (*flag < parts && ++spins < WAIT_LIMIT) __nanosleep(32);
-            if (spins >= WAIT_LIMIT) { ok = false; break; }
-            __threadfence();
-            const int ra0 = (ts % tiles_m) * BM, rb0 = (ts / tiles_m) * bn;
-#pragma unroll 1
-            for (int c0 = rank * UNIT; c0 < bn; c0 += parts * UNIT) {
-                float s[16], s2[16];
-#pragma unroll
-                for (int x = 0; x < 16; ++x) s[x] = s2[x] = 0.f;
-                // the loads of several parts are in flight together; the sums stay in the parts' order
-                constexpr int BATCH = EPI == 1 ? 2 : 4;
-                for (int p0 = 0; p0 < parts; p0 += BATCH) {
-                    uint4 v[BATCH][4], w[EPI == 1 ? BATCH : 1][4];
-#pragma unroll
-                    for (int q = 0; q < BATCH; ++q) {
-                        const int p = p0 + q < parts ? p0 + q : parts - 1;
-                        const int e = p * tail_tiles + tail_index;        // part p of this tile: its CTA and slot
-                        const float* src = partials + (size_t)(2 * (e % (int)gridDim.x) + e / (int)gridDim.x) * P_PARTIAL_FLOATS;
-                        const uint4* a = (const uint4*)(src + ((size_t)(c0 >> 4) * BM + row_in_tile) * 16);
-#pragma unroll
-                        for (int x = 0; x < 4; ++x) v[q][x] = __ldcg(a + x);
-                        if constexpr (EPI == 1) {
-#pragma unroll
-                            for (int x = 0; x < 4; ++x) w[q][x] = __ldcg(a + BM * 4 + x);    // the next 16 columns: the up half
-                        }
-                    }
-#pragma unroll
-                    for (int q = 0; q < BATCH; ++q) {
-                        if (p0 + q < parts) {
-#pragma unroll
-                            for (int x = 0; x < 4; ++x) {
-                                s[4 * x] += __uint_as_float(v[q][x].x); s[4 * x + 1] += __uint_as_float(v[q][x].y);
-                                s[4 * x + 2] += __uint_as_float(v[q][x].z); s[4 * x + 3] += __uint_as_float(v[q][x].w);
-                            }
-                            if constexpr (EPI == 1) {
-#pragma unroll
-                                for (int x = 0; x < 4; ++x) {
-                                    s2[4 * x] += __uint_as_float(w[q][x].x); s2[4 * x + 1] += __uint_as_float(w[q][x].y);
-                                    s2[4 * x + 2] += __uint_as_float(w[q][x].z); s2[4 * x + 3] += __uint_as_float(w[q][x].w);
-                                }
-                            }
-                        }
-                    }
-                }
-                uint32_t r[16], r2[16];
-#pragma unroll
-                for (int x = 0; x < 16; ++x) { r[x] = __float_as_uint(s[x]); r2[x] = __float_as_uint(s2[x]); }
-                emit(ra0 + row_in_tile, rb0, c0, r, r2);
-            }
-            __syncwarp();
-            // the last quarter-warp to have read puts the counter back to zero for the next launch
-            if (lane == 0 && atomicAdd(flags + 4 * ts + quarter, 1) == 2 * parts - 1) flags[4 * ts + quarter] = 0;
-        }
     }
     if (!ok && status) atomicOr(status, 4);
     tc_fence_before();
@@ -898,8 +916,9 @@ int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K
     const long long rest = num_tiles % sms;
     // Cut the tiles of the last round along K when that round would leave SMs idle: into the number
     // of parts (two per CTA at most, eight K blocks a part at least) that makes the parts' rounds
-    // shortest.  The exchange of the partial tiles costs some 15 us, so the gain must be worth it
-    // (a K block takes about 0.36 us).
+    // shortest.  Measured, the parts cost some 15-20 us more than their K blocks (short segments:
+    // each has its own start-up, partial store and exchange), so the gain must be worth it
+    // (a K block takes about 0.36 us): in practice K of 8192 and more.
     if (EPI != 2 && partials && flags && num_tiles <= P_FLAG_CAP && num_tiles > sms && rest > 0) {
         double best = 1.0;
         for (int w = 2; w <= 8 && rest * w <= 2LL * sms && total_kb / w >= 8; ++w) {
