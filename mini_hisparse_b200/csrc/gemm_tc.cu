@@ -460,16 +460,29 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+            // The weights are constant: the weight tiles of the first stages are asked for while the
+            // kernel before this one still runs; the activations only after it has finished.
+            int it = 0, t, kb0, kb1, entry, early = 0;
+            if (segment(0, t, kb0, kb1, entry)) {
+                const int rb0 = (t / tiles_m) * bn;
+                for (int kb = kb0; kb < kb1 && early < P_STAGES; ++kb, ++early) {
+                    mbar_expect_tx(full_bar(early), stage_tx);
+                    tma_load_2d(smem_base + early * S::STAGE_BYTES + S::A_BYTES, &map_b, kb * BK, rb0, full_bar(early));
+                }
+            }
             pdl_wait();
-            int it = 0, t, kb0, kb1, entry;
             for (int j = 0; ok && segment(j, t, kb0, kb1, entry); ++j) {
                 const int ra0 = (t % tiles_m) * BM, rb0 = (t / tiles_m) * bn;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % P_STAGES;
+                    const uint32_t a_dst = smem_base + s * S::STAGE_BYTES;
+                    if (it < early) {                   // the weight tile is on its way already
+                        tma_load_2d(a_dst, &map_a, kb * BK, ra0, full_bar(s));
+                        continue;
+                    }
                     ok = mbar_wait(empty_bar(s), ((it / P_STAGES) & 1) ^ 1);
                     if (!ok) break;
                     mbar_expect_tx(full_bar(s), stage_tx);
-                    const uint32_t a_dst = smem_base + s * S::STAGE_BYTES;
                     tma_load_2d(a_dst, &map_a, kb * BK, ra0, full_bar(s));
                     tma_load_2d(a_dst + S::A_BYTES, &map_b, kb * BK, rb0, full_bar(s));
                 }
