@@ -315,6 +315,8 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
                 const int chunks = (groups + 15) / 16;
                 int* counter = a.counters + ((size_t)tok0 * a.nkv + kvh) * chunks + head0 / 16;
                 const int ns = a.tok_nsplit[tok0];
+                // more parts than the merge below has scratch for: say so rather than merge a part of them
+                if (ns > MAX_MERGE_SPLITS && a.status) atomicOr(a.status, 32);
                 const int prev = atomicAdd(counter, 1);
                 is_last = prev == ns - 1;
                 if (is_last) *counter = 0;

@@ -440,4 +440,6 @@ class ModelRunner:
                 what.append("a bounded wait in the TMA-fed attention kernel ran out")
             if bits & 16:
                 what.append("a bounded wait in the tcgen05 attention kernel ran out")
+            if bits & 32:
+                what.append("a token's keys were split into more parts than the attention kernel merges")
             raise StepError("; ".join(what) or f"kernel status {bits}")

@@ -52,6 +52,7 @@ def check_cover(need, specs, plan):
     rows = set()
     for t in range(T):
         n = int(plan.tok_nsplit[t])
+        assert n <= MAX_SPLITS                    # what the attention kernels' merge has scratch for
         for r in range(int(plan.tok_part_row[t]), int(plan.tok_part_row[t]) + n):
             assert r not in rows and r < plan.part_rows
             rows.add(r)
