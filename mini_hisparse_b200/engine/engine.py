@@ -106,12 +106,19 @@ class Engine:
         if logits is not None:
             self.runner.queue_status()
             rs = [p.request for p in planned if p.sample]
-            sampled = self.sampler.sample(
+            self.sampler.launch(
                 logits,
                 [r.params.temperature for r in rs],
                 [r.params.seed for r in rs],
                 [len(r.generated) for r in rs],
             )
+            # While the GPU works: if this was a step of decode tokens only and every request has
+            # tokens left beyond the one being drawn, the next step decodes the same requests (unless
+            # one draws its end token): its index arrays are packed now.
+            if all(p.kind == "decode" and len(p.request.generated) + 1 < p.request.max_new_tokens
+                   for p in planned):
+                self.runner.prepare_decode_ahead([p.request.request_id for p in planned])
+            sampled = self.sampler.collect()
             self.runner.check_status(queued=True)    # the status word is sticky: a step without
                                                      # samples is checked with the next one
         emitted = self.scheduler.commit(planned, sampled)

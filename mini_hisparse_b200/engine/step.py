@@ -309,7 +309,8 @@ class ModelRunner:
         self.observer = None
         self.side_stream = None
         self.side_events = None
-        self.stats = {"steps": 0, "tokens": 0, "graph_steps": 0, "two_stream_layers": 0}
+        self.stats = {"steps": 0, "tokens": 0, "graph_steps": 0, "two_stream_layers": 0, "prepared_steps": 0}
+        self._ahead = None      # index arrays of the next decode step, packed while the GPU ran this one
         build.build_all(model.kernel_modules())
 
     def _cache_views(self, group_meta) -> list[CacheView | None]:
@@ -348,8 +349,9 @@ class ModelRunner:
         for s in segments:
             self.cache.ensure(s.request, s.start + s.count)
         decode_only = all(s.count == 1 for s in segments) and all(e.want == [0] for e in entries)
+        ahead, self._ahead = self._ahead, None       # what was packed ahead serves this step or none
         if self.use_graphs and decode_only:
-            logits = self._step_graph(entries, segments)
+            logits = self._step_graph(entries, segments, ahead)
         else:
             logits = self._step_eager(entries, segments, T)
         for s in segments:
@@ -378,19 +380,22 @@ class ModelRunner:
         self.stats["two_stream_layers"] += ctx.extras.get("two_stream_layers", 0)
         return out
 
-    def _step_graph(self, entries, segments):
+    def _step_graph(self, entries, segments, ahead=None):
         B = len(segments)
-        # block-table width in powers of two: a graph is re-captured only when contexts double
-        pages = max(-(-(s.start + 1) // self.cache.cfg.page_size) for s in segments)
-        width = 16
-        while width < pages:
-            width *= 2
+        width = self._table_width(segments)
         g = self.graphs.get((B, width))
         if g is None:
             g = self.graphs[(B, width)] = _DecodeGraph(self, B, width)
         layout = g.layout
-        stage, turn = self.batch.staging.next(layout.total)
-        self.batch._fill_decode(stage.numpy(), layout, entries, segments, g.nsplit)
+        if (ahead is not None and ahead["graph"] is g and g.graph is not None
+                and ahead["who"] == [(s.request, s.slot, s.start) for s in segments]):
+            # everything but the token ids was packed while the GPU ran the step before this one
+            stage, turn = ahead["stage"], ahead["turn"]
+            stage.numpy()[layout.tokens : layout.tokens + B] = [e.tokens[0] for e in entries]
+            self.stats["prepared_steps"] += 1
+        else:
+            stage, turn = self.batch.staging.next(layout.total)
+            self.batch._fill_decode(stage.numpy(), layout, entries, segments, g.nsplit)
         g.meta.copy_(stage[: layout.total], non_blocking=True)
         self.batch.staging.mark(turn)
         if g.graph is None:
@@ -418,6 +423,42 @@ class ModelRunner:
         K.launches += g.launches
         self.stats["graph_steps"] += 1
         return g.logits
+
+    def prepare_decode_ahead(self, requests: list) -> None:
+        """Pack the index arrays of the NEXT step, assuming that it decodes one token for each of
+        ``requests`` (in this order) and for nobody else.  Called between a decode step's launch and
+        the wait for its result: the host would idle meanwhile, and positions, block tables and the
+        attention plan of the next step do not depend on the tokens still being computed.  If the
+        next step turns out differently (a request finished, another arrived), what was packed is
+        dropped and the step is packed as usual.  Pages the next positions need are taken now: a
+        request that ends after all gives them back with its others."""
+        self._ahead = None
+        if not self.use_graphs or not requests:
+            return
+        maxpos = self.model.spec.max_positions
+        entries = [StepEntry(r, [0], [0]) for r in requests]
+        for e in entries:
+            length = self.cache.length(e.request)
+            if maxpos is not None and length + 1 > maxpos:
+                return
+            self.cache.ensure(e.request, length + 1)
+        segments, _ = self.batch.segments(entries)
+        g = self.graphs.get((len(segments), self._table_width(segments)))
+        if g is None or g.graph is None:
+            return              # that step will capture its graph: nothing to gain
+        stage, turn = self.batch.staging.next(g.layout.total)
+        self.batch._fill_decode(stage.numpy(), g.layout, entries, segments, g.nsplit)
+        self._ahead = {"graph": g, "stage": stage, "turn": turn,
+                       "who": [(s.request, s.slot, s.start) for s in segments]}
+
+    def _table_width(self, segments) -> int:
+        """Block-table width of a decode graph: a power of two, so a graph is re-captured only when
+        contexts double."""
+        pages = max(-(-(s.start + 1) // self.cache.cfg.page_size) for s in segments)
+        width = 16
+        while width < pages:
+            width *= 2
+        return width
 
     def queue_status(self) -> None:
         """Start the copy of the status word to the host; read it with check_status(queued=True)

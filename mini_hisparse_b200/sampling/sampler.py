@@ -47,6 +47,11 @@ class Sampler:
 
     def sample(self, logits: torch.Tensor, temperatures, seeds, counters) -> list[int]:
         """One token per row of ``logits`` [R, V]; host lists in, host list out (one sync)."""
+        self.launch(logits, temperatures, seeds, counters)
+        return self.collect()
+
+    def launch(self, logits: torch.Tensor, temperatures, seeds, counters) -> None:
+        """Start the sampling kernel and the copy of its result to the host; collect() waits for them."""
         R = logits.shape[0]
         if R > self._cap:
             self._grow(max(R, 2 * self._cap))
@@ -60,5 +65,8 @@ class Sampler:
             self.draw.copy_(self.draw_host, non_blocking=True)
             K.sample(logits, self.temp, self.draw[0], self.draw[1], self.out[:R])
         self.out_host[:R].copy_(self.out[:R], non_blocking=True)
+        self._rows = R
+
+    def collect(self) -> list[int]:
         torch.cuda.current_stream().synchronize()
-        return self.out_host[:R].tolist()
+        return self.out_host[: self._rows].tolist()

@@ -47,6 +47,7 @@ def test_greedy_generation_equals_plain(folders, name, dtype):
         r = engine.requests[rid]
         assert r.prefill_count == 1 and r.decode_count == 15 and r.finished
     assert engine.runner.stats["graph_steps"] > 0        # decoding went through captured graphs
+    assert engine.runner.stats["prepared_steps"] > 0     # and some steps' index arrays were packed ahead
     engine.cache.assert_invariants()
     assert not engine.cache.requests
     assert engine.cache.page_groups[0].allocator.free_pages == 64
