@@ -18,6 +18,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
+from ..cache.allocator import CapacityError
 from ..cache.manager import CacheManager
 from ..kernels import api as K
 from ..kernels import build
@@ -441,7 +442,10 @@ class ModelRunner:
             length = self.cache.length(e.request)
             if maxpos is not None and length + 1 > maxpos:
                 return
-            self.cache.ensure(e.request, length + 1)
+            try:
+                self.cache.ensure(e.request, length + 1)
+            except CapacityError:
+                return          # the step itself will say so, if it comes to that
         segments, _ = self.batch.segments(entries)
         g = self.graphs.get((len(segments), self._table_width(segments)))
         if g is None or g.graph is None:
