@@ -27,6 +27,7 @@ CONFIG_7B = json.loads((ROOT / "mini_hisparse_b200" / "configs" / "qwen2.5-7b-sh
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 PAGE = 16
+SAMPLED = 64       # untimed decode steps under the clock sampler before the timed ones
 
 
 def reference_arm(args) -> int:
@@ -79,11 +80,13 @@ def main() -> int:
     settle = max(warmup, 32)
 
     def decode_point(batch: int, warm: int = warmup) -> dict:
-        start_ctx = CONTEXT - steps - warm - 1      # the timed steps end at the context length
+        # SAMPLED more untimed steps run before the timed ones with the clock sampler on, so that a
+        # short timed region still has clock samples of its load
+        start_ctx = CONTEXT - steps - warm - SAMPLED - 1      # the timed steps end at the context length
         engine = Engine(model, num_pages=batch * (CONTEXT // PAGE + 1), page_size=PAGE, max_requests=batch)
         names = measure.synthetic_context(engine, batch, start_ctx)
-        r = measure.time_decode(engine, names, steps, warm, vocab)
-        live = batch * (start_ctx + warm + steps // 2)
+        r = measure.time_decode(engine, names, steps, warm, vocab, sampled_warmup=SAMPLED)
+        live = batch * (start_ctx + warm + SAMPLED + steps // 2)
         r["bytes"] = measure.decode_bytes(model, engine.cache, live)
         del engine
         gc.collect()

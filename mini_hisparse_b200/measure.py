@@ -150,8 +150,12 @@ def synthetic_context(engine, batch: int, tokens: int, seed: int = 0) -> list[st
     return names
 
 
-def time_decode(engine, names, steps: int, warmup: int, vocab: int) -> dict:
-    """Device time of ``steps`` decode steps of the step function (one token per request)."""
+def time_decode(engine, names, steps: int, warmup: int, vocab: int, sampled_warmup: int = 0) -> dict:
+    """Device time of ``steps`` decode steps of the step function (one token per request).
+
+    The clocks are sampled every 100 ms (more often disturbs the timing), so a short timed region may
+    see no sample: ``sampled_warmup`` further untimed steps of the same load run between the warm-up
+    and the timed steps with the sampler already on."""
     from .engine.step import StepEntry
 
     B = len(names)
@@ -165,6 +169,9 @@ def time_decode(engine, names, steps: int, warmup: int, vocab: int) -> dict:
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = K.launches
     with ClockSampler() as clocks:
+        for _ in range(sampled_warmup):
+            engine.runner.step(entries())
+        launches0 = K.launches
         torch.cuda.synchronize()
         start.record()
         for _ in range(steps):
