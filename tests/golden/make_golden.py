@@ -35,7 +35,7 @@ NEW_TOKENS = 12
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="a checkout of KiritoHugh/mini-hisparse")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     from mini_hisparse.engine import Engine
