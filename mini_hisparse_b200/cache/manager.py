@@ -1,9 +1,10 @@
 """The cache manager: page pools with a block table per request, and fixed-size state slots.
 
 Cache entries (one per owning entry of the model's run order) are sorted into groups by what
-they need.  Entries that need keys and values in pages and agree on geometry and window form a
-*page group*: one pool ``[entries, pages, 2, kv_heads, page_size, head_dim]``, one allocator,
-one block table per request, so a page id is valid in every layer of the group.  Entries that
+they need.  Entries that need per-position memory in pages and whose needs compare equal form a
+*page group*: one pool ``[entries, pages, *need.page_shape(page_size)]`` (for keys and values:
+``[2, kv_heads, page_size, head_dim]``), one allocator, one block table per request, so a page
+id is valid in every layer of the group.  Entries that
 need a fixed-size state form a *state group*: a tensor ``[entries, slots, *shape]`` indexed by
 the request's slot.  The reference has one homogeneous pool per (layer, page)
 (mini_hisparse/allocator.py:18-22) and keeps per-request bookkeeping in
@@ -20,7 +21,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
-from ..parts.spec import CacheNeed, PagedKVNeed, StateNeed
+from ..parts.spec import CacheNeed, PagedNeed, StateNeed
 from .allocator import CapacityError, PageAllocator
 
 _TORCH_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
@@ -38,6 +39,12 @@ class CacheConfig:
     dtype: torch.dtype = torch.bfloat16
     device: str = "cuda:0"
     allocate_storage: bool = True
+    # Debugging aid: a page that is given back is overwritten with POISON in every layer, so that
+    # a kernel that reads a stale page (through an old block-table entry, or beyond its keys)
+    # produces numbers far outside anything a model computes instead of plausible ones.  The
+    # value is finite on purpose: kernels load whole pages and multiply masked positions by
+    # zero, which a NaN would survive.
+    debug_poison: bool = False
 
     def __post_init__(self):
         for name in ("num_pages", "page_size", "max_requests"):
@@ -47,6 +54,9 @@ class CacheConfig:
             raise ValueError("KV dtype must be float32 or bfloat16")
 
 
+POISON = 1.0e30
+
+
 @dataclass
 class _RequestPages:
     pages: list[int] = field(default_factory=list)   # logical page index -> page id or -1
@@ -54,7 +64,7 @@ class _RequestPages:
 
 
 class PageGroup:
-    def __init__(self, gid: int, need: PagedKVNeed, entries: list[int], cfg: CacheConfig):
+    def __init__(self, gid: int, need: PagedNeed, entries: list[int], cfg: CacheConfig):
         self.gid, self.need, self.entries, self.cfg = gid, need, entries, cfg
         self.allocator = PageAllocator(cfg.num_pages)
         # the table is indexed by logical page: a full group never needs more entries than the
@@ -66,18 +76,32 @@ class PageGroup:
         # the block tables as one array [slot, logical page], -1 where no page is held; kept in
         # step with ``tables`` so that a step copies rows instead of walking Python lists
         self.table_np = np.full((cfg.max_requests, self.width), -1, np.int32)
-        shape = (len(entries), cfg.num_pages, 2, need.kv_heads, cfg.page_size, need.head_dim)
+        self.page_shape = tuple(int(n) for n in need.page_shape(cfg.page_size))
+        shape = (len(entries), cfg.num_pages, *self.page_shape)
         self.storage = (
             torch.zeros(shape, dtype=cfg.dtype, device=cfg.device) if cfg.allocate_storage else None
         )
+        self.poisoned = 0
+
+    def give_back(self, owner, pages: list[int]) -> None:
+        """Free pages; with debug_poison their old content is destroyed first (stream order makes
+        that safe: kernels launched earlier have read them, later ones see the poison)."""
+        if pages and self.cfg.debug_poison and self.storage is not None:
+            index = torch.as_tensor(pages, dtype=torch.long, device=self.storage.device)
+            self.storage.index_fill_(1, index, POISON)
+            self.poisoned += len(pages)
+        self.allocator.free(owner, pages)
 
     @property
     def window(self):
         return self.need.window
 
     def page_bytes(self) -> int:
-        n = self.need
-        return len(self.entries) * 2 * n.kv_heads * self.cfg.page_size * n.head_dim * self.cfg.dtype.itemsize
+        """Bytes of one page id: one page in every entry of the group."""
+        n = 1
+        for extent in self.page_shape:
+            n *= extent
+        return len(self.entries) * n * self.cfg.dtype.itemsize
 
     def pages_for(self, total_tokens: int, max_step_tokens: int | None = None) -> int:
         """Pages a request of total_tokens can hold at once."""
@@ -120,7 +144,7 @@ class CacheManager:
             if need is not None:
                 by_need.setdefault(need, []).append(i)
         for need, entries in by_need.items():
-            if isinstance(need, PagedKVNeed):
+            if isinstance(need, PagedNeed):
                 g = PageGroup(len(self.page_groups), need, entries, cfg)
                 self.page_groups.append(g)
                 for j, e in enumerate(entries):
@@ -211,6 +235,12 @@ class CacheManager:
                 g.table_np[req.slot, len(rp.pages): len(rp.pages) + len(pages)] = pages
             rp.pages.extend(pages)
 
+    def has_pages(self, request, new_length: int) -> bool:
+        """True if every position below new_length already has a page in every group."""
+        req = self.requests[request]
+        need_pages = -(-new_length // self.cfg.page_size)
+        return all(len(g.tables[req.slot].pages) >= need_pages for g in self.page_groups)
+
     def advance(self, request, count: int) -> None:
         """The request's first ``length + count`` positions are now cached; windows move on."""
         req = self.requests[request]
@@ -225,7 +255,7 @@ class CacheManager:
             dead = min(first_needed // P, len(rp.pages))
             if dead > rp.first_live:
                 pages = [p for p in rp.pages[rp.first_live:dead] if p >= 0]
-                g.allocator.free(request, pages)
+                g.give_back(request, pages)
                 for i in range(rp.first_live, dead):
                     rp.pages[i] = -1
                 g.table_np[req.slot, rp.first_live:dead] = -1
@@ -238,7 +268,7 @@ class CacheManager:
         for g in self.page_groups:
             rp = g.tables.pop(req.slot)
             g.table_np[req.slot, : len(rp.pages)] = -1
-            g.allocator.free(request, [p for p in rp.pages if p >= 0])
+            g.give_back(request, [p for p in rp.pages if p >= 0])
             g.allocator.release_owner(request)
         self._free_slots.append(req.slot)
         self.stats["closed"] += 1
@@ -292,6 +322,7 @@ class CacheManager:
                     "pages_free": g.allocator.free_pages,
                     "pages_peak": g.allocator.peak_in_use,
                     "pages_reused": g.allocator.reuses,
+                    "pages_poisoned": g.poisoned,
                     "credits_available": g.allocator.available_credits(),
                     "page_bytes": g.page_bytes(),
                 }

@@ -58,9 +58,6 @@ def build_parser() -> argparse.ArgumentParser:
             c.add_argument("--prompt-tokens", type=int, default=1024)
             c.add_argument("--steps", type=int, default=20)
             c.add_argument("--layers", type=int, help="run fewer layers than the config has")
-            c.add_argument("--leave-out", default="", help="profiling aid: comma-separated kernels whose launches "
-                           "are skipped (add_rmsnorm, rope_append, attention, gate_up, qkv, o_proj, down, lm_head); "
-                           "prints the step time without them")
     return parser
 
 
@@ -111,8 +108,7 @@ def main(argv=None) -> int:
         result = decode_benchmark(json.loads(args.config.read_text()), batch=args.requests,
                                   prompt_tokens=args.prompt_tokens, steps=args.steps, dtype=args.dtype,
                                   device=args.device, page_size=args.page_size, weight_seed=args.weight_seed,
-                                  layers=args.layers,
-                                  leave_out_kernels=[n for n in args.leave_out.split(",") if n])
+                                  layers=args.layers)
     else:
         if args.command == "generate":
             model = load_model(args.model, device=args.device, dtype=args.dtype)

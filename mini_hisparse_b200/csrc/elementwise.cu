@@ -234,36 +234,45 @@ MHB_EXPORT int mhb_residual_add(float* x, const void* delta, int delta_dtype, in
 
 // ---- rotary positions + paged KV append -----------------------------------------------------
 // qkv[t] = [q heads | k heads | v heads], each head `d` wide, plus an optional float32 bias.
-// q and k are rotated by the half-split rule of mini_hisparse/model.py:141-151:
-//   angle = float(position) * inv_freq[i],  out[j] = t[j]*cos + (j < d/2 ? -t[j+d/2] : t[j-d/2])*sin
+// The first `rdim` elements of every q and k head are rotated, the rest pass unchanged; v is never
+// rotated.  angle_i = float(position) * inv_freq[i], i < rdim / 2, and the pair that angle i turns is
+//   half-split (mini_hisparse/model.py:141-151, "rotate_half"):  (i, i + rdim/2)
+//   interleaved:                                                  (2 i, 2 i + 1)
+// with (a, b) -> (a cos - b sin, b cos + a sin).  The reference has the half-split rule over the
+// whole head only (rdim = d); the other two are parameters of the position part.
 // Rotated q goes to q_out [T, nq*d]; rotated k and plain v go into the cache page of the
 // token's position (the append happens before attention, model.py:169-170, 201):
 //   cache[page][0 or 1][kv head][position % P][d],  page = block_table[seg][position / P].
 // With write_kv == 0 nothing is appended (a layer that reads another layer's cache).
+struct RopeStyle {
+    int rdim;          // rotated elements per head: even, <= d; 0 = no rotation
+    int interleaved;   // 0: pairs (i, i + rdim/2); 1: pairs (2 i, 2 i + 1)
+};
+
 template <typename IT, typename QT, typename CT>
 __global__ void rope_append_kernel(const IT* __restrict__ qkv, int nsplit, size_t split_stride,
                                    const float* __restrict__ bias, const int* __restrict__ positions,
                                    const int* __restrict__ tok_seg, const int* __restrict__ block_table,
                                    int table_width, const float* __restrict__ inv_freq,
                                    QT* __restrict__ q_out, CT* __restrict__ cache, int nq, int nkv,
-                                   int d, int P, int num_pages, int write_kv, int rotate_q_k,
+                                   int d, int P, int num_pages, int write_kv, RopeStyle style,
                                    int heads_per_block, int* __restrict__ status) {
-    extern __shared__ float cs_table[];      // cos[d/2], sin[d/2] of this token's position
+    extern __shared__ float cs_table[];      // cos[rdim/2], sin[rdim/2] of this token's position
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
-    const int half = d >> 1;
+    const int rhalf = style.rdim >> 1;
     const int width = (nq + 2 * nkv) * d;
     const size_t base = (size_t)t * width;
     // heads are numbered q heads, then k heads, then v heads; this block takes a run of them
     const int head_begin = blockIdx.y * heads_per_block;
     const int head_end = min(nq + 2 * nkv, head_begin + heads_per_block);
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        float sn = 0.f, cs = 1.f;
-        if (rotate_q_k) sincosf((float)pos * inv_freq[i], &sn, &cs);
+    for (int i = threadIdx.x; i < rhalf; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
         cs_table[i] = cs;
-        cs_table[half + i] = sn;
+        cs_table[rhalf + i] = sn;
     }
     int page = -1;
     if (write_kv && head_end > nq) {
@@ -275,25 +284,29 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, int nsplit, size_
     }
     const int within = pos % P;
     __syncthreads();
-    // q and k heads: one thread per (head, i < d/2) pair
+    // q and k heads: one thread per unit; a head has rdim/2 rotated pairs and d - rdim plain elements
     const int rot_end = min(head_end, nq + nkv);
-    for (int idx = head_begin * half + threadIdx.x; idx < rot_end * half; idx += blockDim.x) {
-        const int head = idx / half, i = idx - head * half;
-        const int col = head * d + i;
-        float a = load_split(qkv, base + col, nsplit, split_stride);
-        float b = load_split(qkv, base + col + half, nsplit, split_stride);
-        if (bias) { a += bias[col]; b += bias[col + half]; }
-        const float cs = cs_table[i], sn = cs_table[half + i];
-        const float oa = a * cs - b * sn;
-        const float ob = b * cs + a * sn;
-        if (head < nq) {
-            q_out[(size_t)t * nq * d + col] = from_float<QT>(oa);
-            q_out[(size_t)t * nq * d + col + half] = from_float<QT>(ob);
-        } else if (page >= 0) {
-            const int kh = head - nq;
-            CT* dst = cache + ((((size_t)page * 2 + 0) * nkv + kh) * P + within) * d;
-            dst[i] = from_float<CT>(oa);
-            dst[i + half] = from_float<CT>(ob);
+    const int units = rhalf + (d - style.rdim);
+    for (int idx = head_begin * units + threadIdx.x; idx < rot_end * units; idx += blockDim.x) {
+        const int head = idx / units, u = idx - head * units;
+        QT* qdst = head < nq ? q_out + (size_t)t * nq * d + head * d : nullptr;
+        CT* kdst = (head >= nq && page >= 0) ? cache + ((((size_t)page * 2 + 0) * nkv + (head - nq)) * P + within) * d : nullptr;
+        if (u < rhalf) {
+            const int ea = style.interleaved ? 2 * u : u, eb = style.interleaved ? 2 * u + 1 : u + rhalf;
+            float a = load_split(qkv, base + head * d + ea, nsplit, split_stride);
+            float b = load_split(qkv, base + head * d + eb, nsplit, split_stride);
+            if (bias) { a += bias[head * d + ea]; b += bias[head * d + eb]; }
+            const float cs = cs_table[u], sn = cs_table[rhalf + u];
+            const float oa = a * cs - b * sn;
+            const float ob = b * cs + a * sn;
+            if (qdst) { qdst[ea] = from_float<QT>(oa); qdst[eb] = from_float<QT>(ob); }
+            else if (kdst) { kdst[ea] = from_float<CT>(oa); kdst[eb] = from_float<CT>(ob); }
+        } else {
+            const int e = style.rdim + (u - rhalf);
+            float a = load_split(qkv, base + head * d + e, nsplit, split_stride);
+            if (bias) a += bias[head * d + e];
+            if (qdst) qdst[e] = from_float<QT>(a);
+            else if (kdst) kdst[e] = from_float<CT>(a);
         }
     }
     if (page >= 0) {
@@ -307,8 +320,8 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, int nsplit, size_
     }
 }
 
-// The same with four elements per thread (head sizes are multiples of 8 and every row, bias and
-// cache row is 16-byte aligned then): 16-byte loads, 8- or 16-byte stores.
+// The same with four elements per thread (head size and rotated width are multiples of 8 and every
+// row, bias and cache row is 16-byte aligned then): 16-byte loads, 8- or 16-byte stores.
 template <typename IT>
 __device__ __forceinline__ float4 load4_split(const IT* p, size_t idx, int nsplit, size_t split_stride) {
     float4 v = load4<IT>(p + idx);
@@ -326,6 +339,7 @@ __device__ __forceinline__ float4 load4_split(const IT* p, size_t idx, int nspli
     }
     return v;
 }
+__device__ __forceinline__ void add4(float4& a, const float4 b) { a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
 
 template <typename IT, typename QT, typename CT>
 __global__ void rope_append_vec_kernel(const IT* __restrict__ qkv, int nsplit, size_t split_stride,
@@ -333,24 +347,24 @@ __global__ void rope_append_vec_kernel(const IT* __restrict__ qkv, int nsplit, s
                                        const int* __restrict__ tok_seg, const int* __restrict__ block_table,
                                        int table_width, const float* __restrict__ inv_freq,
                                        QT* __restrict__ q_out, CT* __restrict__ cache, int nq, int nkv,
-                                       int d, int P, int num_pages, int write_kv, int rotate_q_k,
+                                       int d, int P, int num_pages, int write_kv, RopeStyle style,
                                        int heads_per_block, int* __restrict__ status) {
-    extern __shared__ __align__(16) float cs_table[];      // cos[d/2], sin[d/2] of this token's position
+    extern __shared__ __align__(16) float cs_table[];      // cos[rdim/2], sin[rdim/2] of this token's position
     // positions, segments and the block table were copied in before the step's first kernel: the
     // rotation table and the page are worked out while the kernel before this one still runs
     pdl_launch_dependents();
     const int t = blockIdx.x;
     const int pos = positions[t];
-    const int half = d >> 1, quarter = d >> 3;             // quarter: groups of 4 in a half
+    const int rhalf = style.rdim >> 1;
     const int width = (nq + 2 * nkv) * d;
     const size_t base = (size_t)t * width;
     const int head_begin = blockIdx.y * heads_per_block;
     const int head_end = min(nq + 2 * nkv, head_begin + heads_per_block);
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        float sn = 0.f, cs = 1.f;
-        if (rotate_q_k) sincosf((float)pos * inv_freq[i], &sn, &cs);
+    for (int i = threadIdx.x; i < rhalf; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
         cs_table[i] = cs;
-        cs_table[half + i] = sn;
+        cs_table[rhalf + i] = sn;
     }
     int page = -1;
     if (write_kv && head_end > nq) {
@@ -363,29 +377,40 @@ __global__ void rope_append_vec_kernel(const IT* __restrict__ qkv, int nsplit, s
     const int within = pos % P;
     __syncthreads();
     pdl_wait();
+    // q and k heads: a unit is four angles (eight rotated elements) or four plain elements
     const int rot_end = min(head_end, nq + nkv);
-    for (int idx = head_begin * quarter + threadIdx.x; idx < rot_end * quarter; idx += blockDim.x) {
-        const int head = idx / quarter, i = (idx - head * quarter) * 4;
-        const int col = head * d + i;
-        float4 a = load4_split(qkv, base + col, nsplit, split_stride);
-        float4 b = load4_split(qkv, base + col + half, nsplit, split_stride);
-        if (bias) {
-            const float4 ba = *(const float4*)(bias + col), bb = *(const float4*)(bias + col + half);
-            a.x += ba.x; a.y += ba.y; a.z += ba.z; a.w += ba.w;
-            b.x += bb.x; b.y += bb.y; b.z += bb.z; b.w += bb.w;
-        }
-        const float4 cs = *(const float4*)(cs_table + i), sn = *(const float4*)(cs_table + half + i);
-        const float4 oa = make_float4(a.x * cs.x - b.x * sn.x, a.y * cs.y - b.y * sn.y, a.z * cs.z - b.z * sn.z,
-                                      a.w * cs.w - b.w * sn.w);
-        const float4 ob = make_float4(b.x * cs.x + a.x * sn.x, b.y * cs.y + a.y * sn.y, b.z * cs.z + a.z * sn.z,
-                                      b.w * cs.w + a.w * sn.w);
-        if (head < nq) {
-            store4<QT>(q_out + (size_t)t * nq * d + col, oa);
-            store4<QT>(q_out + (size_t)t * nq * d + col + half, ob);
-        } else if (page >= 0) {
-            CT* dst = cache + ((((size_t)page * 2 + 0) * nkv + (head - nq)) * P + within) * d;
-            store4<CT>(dst + i, oa);
-            store4<CT>(dst + i + half, ob);
+    const int runits = style.rdim >> 3, units = runits + ((d - style.rdim) >> 2);
+    for (int idx = head_begin * units + threadIdx.x; idx < rot_end * units; idx += blockDim.x) {
+        const int head = idx / units, u = idx - head * units;
+        const int col0 = head * d;
+        QT* qdst = head < nq ? q_out + (size_t)t * nq * d + col0 : nullptr;
+        CT* kdst = (head >= nq && page >= 0) ? cache + ((((size_t)page * 2 + 0) * nkv + (head - nq)) * P + within) * d : nullptr;
+        if (u < runits) {
+            // the two vectors of inputs: half-split (4u .., rhalf + 4u ..), interleaved (8u .., 8u + 4 ..)
+            const int ea = style.interleaved ? 8 * u : 4 * u, eb = style.interleaved ? 8 * u + 4 : rhalf + 4 * u;
+            float4 a = load4_split(qkv, base + col0 + ea, nsplit, split_stride);
+            float4 b = load4_split(qkv, base + col0 + eb, nsplit, split_stride);
+            if (bias) {
+                add4(a, *(const float4*)(bias + col0 + ea));
+                add4(b, *(const float4*)(bias + col0 + eb));
+            }
+            const float4 cs = *(const float4*)(cs_table + 4 * u), sn = *(const float4*)(cs_table + rhalf + 4 * u);
+            float4 oa, ob;
+            if (style.interleaved) {     // pairs (a.x, a.y) (a.z, a.w) (b.x, b.y) (b.z, b.w)
+                oa = make_float4(a.x * cs.x - a.y * sn.x, a.y * cs.x + a.x * sn.x, a.z * cs.y - a.w * sn.y, a.w * cs.y + a.z * sn.y);
+                ob = make_float4(b.x * cs.z - b.y * sn.z, b.y * cs.z + b.x * sn.z, b.z * cs.w - b.w * sn.w, b.w * cs.w + b.z * sn.w);
+            } else {                     // pairs (a.x, b.x) ...
+                oa = make_float4(a.x * cs.x - b.x * sn.x, a.y * cs.y - b.y * sn.y, a.z * cs.z - b.z * sn.z, a.w * cs.w - b.w * sn.w);
+                ob = make_float4(b.x * cs.x + a.x * sn.x, b.y * cs.y + a.y * sn.y, b.z * cs.z + a.z * sn.z, b.w * cs.w + a.w * sn.w);
+            }
+            if (qdst) { store4<QT>(qdst + ea, oa); store4<QT>(qdst + eb, ob); }
+            else if (kdst) { store4<CT>(kdst + ea, oa); store4<CT>(kdst + eb, ob); }
+        } else {
+            const int e = style.rdim + 4 * (u - runits);
+            float4 a = load4_split(qkv, base + col0 + e, nsplit, split_stride);
+            if (bias) add4(a, *(const float4*)(bias + col0 + e));
+            if (qdst) store4<QT>(qdst + e, a);
+            else if (kdst) store4<CT>(kdst + e, a);
         }
     }
     if (page >= 0) {
@@ -394,23 +419,23 @@ __global__ void rope_append_vec_kernel(const IT* __restrict__ qkv, int nsplit, s
         for (int idx = v_begin * dq + threadIdx.x; idx < head_end * dq; idx += blockDim.x) {
             const int head = idx / dq, e = (idx - head * dq) * 4;
             float4 v = load4_split(qkv, base + (size_t)head * d + e, nsplit, split_stride);
-            if (bias) {
-                const float4 bv = *(const float4*)(bias + head * d + e);
-                v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
-            }
+            if (bias) add4(v, *(const float4*)(bias + head * d + e));
             store4<CT>(cache + ((((size_t)page * 2 + 1) * nkv + (head - nq - nkv)) * P + within) * d + e, v);
         }
     }
 }
 
+// rotary_dim: rotated elements per head (0: none; else even and <= d); interleaved: the pairing.
 MHB_EXPORT int mhb_rope_append(const void* qkv, int in_dtype, int nsplit, long long split_stride,
                                const float* bias, const int* positions, const int* tok_seg,
                                const int* block_table, int table_width, const float* inv_freq,
                                void* q_out, void* cache, int act_dtype, int T, int nq, int nkv,
-                               int d, int P, int num_pages, int write_kv, int rotate,
+                               int d, int P, int num_pages, int write_kv, int rotary_dim, int interleaved,
                                int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (d % 2) return fail("rope_append: head_dim %d must be even", d);
+    if (rotary_dim < 0 || rotary_dim > d || rotary_dim % 2)
+        return fail("rope_append: %d rotated elements in a head of %d (even, at most the head size)", rotary_dim, d);
+    if (rotary_dim > 0 && inv_freq == nullptr) return fail("rope_append: a rotation needs its frequencies");
     if (nsplit > 1 && in_dtype != MHB_F32) return fail("rope_append: split partials must be float32");
     const int threads = 128;
     // few tokens: spread the heads of a token over several blocks so that the GPU is not idle
@@ -420,47 +445,48 @@ MHB_EXPORT int mhb_rope_append(const void* qkv, int in_dtype, int nsplit, long l
     const int hpb = (heads + blocks_y - 1) / blocks_y;
     blocks_y = (heads + hpb - 1) / hpb;
     dim3 grid(T, blocks_y);
-    const size_t smem = sizeof(float) * d;
-    const bool aligned = d % 8 == 0 && split_stride % 4 == 0 && (((uintptr_t)qkv | (uintptr_t)bias | (uintptr_t)q_out |
-                                                                  (uintptr_t)cache) & 15) == 0;
+    const size_t smem = sizeof(float) * (rotary_dim > 0 ? rotary_dim : 2);
+    RopeStyle style = {rotary_dim, interleaved ? 1 : 0};
+    const bool aligned = d % 8 == 0 && rotary_dim % 8 == 0 && split_stride % 4 == 0 &&
+                         (((uintptr_t)qkv | (uintptr_t)bias | (uintptr_t)q_out | (uintptr_t)cache) & 15) == 0;
     if (aligned) {
         MHB_DISPATCH_DTYPE(in_dtype, IT, MHB_DISPATCH_DTYPE(act_dtype, AT,
             launch_kernel(rope_append_vec_kernel<IT, AT, AT>, dim3(grid), dim3(threads), smem, stream,
                 (const IT*)qkv, nsplit, (size_t)split_stride, bias, positions, tok_seg, block_table,
                 table_width, inv_freq, (AT*)q_out, (AT*)cache, nq, nkv, d, P, num_pages, write_kv,
-                rotate, hpb, status)));
+                style, hpb, status)));
         return check_launch("rope_append");
     }
     MHB_DISPATCH_DTYPE(in_dtype, IT, MHB_DISPATCH_DTYPE(act_dtype, AT,
         launch_kernel(rope_append_kernel<IT, AT, AT>, dim3(grid), dim3(threads), smem, stream, 
             (const IT*)qkv, nsplit, (size_t)split_stride, bias, positions, tok_seg, block_table,
             table_width, inv_freq, (AT*)q_out, (AT*)cache, nq, nkv, d, P, num_pages, write_kv,
-            rotate, hpb, status)));
+            style, hpb, status)));
     return check_launch("rope_append");
 }
 
-// cos and sin of every token's rotation angles, [T, d]: cos[d/2] then sin[d/2]; once per step for
-// all layers (the matrix product's q/k/v epilogue reads it).  Float32 angles as in rope_append.
+// cos and sin of every token's rotation angles, [T, rdim]: cos[rdim/2] then sin[rdim/2]; once per step
+// for all layers (the matrix product's q/k/v epilogue reads it).  Float32 angles as in rope_append.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                                  float* __restrict__ table, int T, int half, int rotate) {
+                                  float* __restrict__ table, int T, int half) {
     pdl_launch_dependents();
     pdl_wait();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= T * half) return;
     const int t = idx / half, i = idx - t * half;
-    float sn = 0.f, cs = 1.f;
-    if (rotate) sincosf((float)positions[t] * inv_freq[i], &sn, &cs);
+    float sn, cs;
+    sincosf((float)positions[t] * inv_freq[i], &sn, &cs);
     table[(size_t)t * 2 * half + i] = cs;
     table[(size_t)t * 2 * half + half + i] = sn;
 }
 
-MHB_EXPORT int mhb_rope_table(const int* positions, const float* inv_freq, float* table, int T, int d, int rotate,
+MHB_EXPORT int mhb_rope_table(const int* positions, const float* inv_freq, float* table, int T, int rotary_dim,
                               cudaStream_t stream) {
-    if (T <= 0) return 0;
-    if (d % 2) return fail("rope_table: head_dim %d must be even", d);
-    const int half = d / 2, threads = 256;
+    if (T <= 0 || rotary_dim <= 0) return 0;
+    if (rotary_dim % 2) return fail("rope_table: %d rotated elements (must be even)", rotary_dim);
+    const int half = rotary_dim / 2, threads = 256;
     launch_kernel(rope_table_kernel, dim3((T * half + threads - 1) / threads), dim3(threads), 0, stream, positions,
-                  inv_freq, table, T, half, rotate);
+                  inv_freq, table, T, half);
     return check_launch("rope_table");
 }
 

@@ -99,6 +99,8 @@ MHB_EXPORT int mhb_gemm_simt(const void* A, int a_dtype, const void* W, int w_dt
 
 
 // ---- the same product for callers that cannot allocate (see gemm_simt_noalloc.h) -----------------
+#include <mutex>
+
 #include "gemm_simt_noalloc.h"
 
 namespace {
@@ -109,6 +111,7 @@ static __device__ __align__(256) float g_noalloc_scratch[MHB_NOALLOC_SCRATCH_FLO
 
 constexpr int MAX_DEVICES = 64;
 float* g_noalloc_ptr[MAX_DEVICES] = {nullptr};
+std::mutex g_noalloc_mutex;      // host threads may make their first calls at the same time
 
 // C[m, n] = sum over the splits, in split order
 __global__ void sum_partials_kernel(const float* __restrict__ parts, float* __restrict__ C, int M, int N,
@@ -128,6 +131,7 @@ int noalloc_scratch(float** out) {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return fail("gemm_simt_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
     if (dev < 0 || dev >= MAX_DEVICES) return fail("gemm_simt_noalloc: device %d is beyond the %d this library tracks", dev, MAX_DEVICES);
+    std::lock_guard<std::mutex> guard(g_noalloc_mutex);
     if (g_noalloc_ptr[dev] == nullptr) {
         float* p = nullptr;
         e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
@@ -146,6 +150,8 @@ MHB_EXPORT int mhb_gemm_simt_noalloc(const void* A, int a_dtype, const void* W, 
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return fail("gemm_simt_noalloc: K must be positive");
     if (nsplit < 1) nsplit = 1;
+    if (nsplit > 65535) return fail("gemm_simt_noalloc: %d splits; at most 65535 (the grid's third extent)", nsplit);
+    if (ldc < N) return fail("gemm_simt_noalloc: the output's row stride %lld is shorter than its %d columns", ldc, N);
     const long long need = (long long)nsplit * M * N;
     if (need > (long long)MHB_NOALLOC_SCRATCH_FLOATS)
         return fail("gemm_simt_noalloc: %d splits of a %d x %d product need %lld floats of scratch; the built-in "

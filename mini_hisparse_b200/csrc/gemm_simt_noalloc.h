@@ -21,7 +21,10 @@
 //     float32 or bfloat16 (dtype codes 0 / 1), row-major with K contiguous.  Inputs and the output
 //     are the caller's; the entry point calls no cudaMalloc, cudaFree or any allocating routine.
 //   * nsplit * M * N must not exceed MHB_NOALLOC_SCRATCH_FLOATS; larger products are refused with
-//     an error text (mhb_last_error) and nothing is launched.
+//     an error text (mhb_last_error) and nothing is launched.  So are more than 65535 splits and
+//     an output row stride shorter than N.  Splits beyond the K range are allowed: they add zeros.
+//   * Host threads may call at the same time as far as the address look-up goes (it is locked);
+//     the rule on overlapping kernels below holds for them as for streams.
 //   * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
 //     that device current).  Make that first call before any stream capture begins.
 //   * All calls share the one array, and it keeps whatever the last call left in it.  The product

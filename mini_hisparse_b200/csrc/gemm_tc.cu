@@ -385,13 +385,15 @@ struct PSmem {
 };
 
 // Epilogue 2: the tile is a run of tokens x two (head size 128) or four (head size 64) heads of the
-// stacked q/k/v product.  Instead of storing it, the epilogue adds the bias, rotates q and k heads
-// (half-split pairs i, i + d/2, mini_hisparse/model.py:141-151) by the token's row of a cos/sin
-// table, and writes q as bfloat16 and k, v into the token's page of the KV cache
-// (model.py:169-170): no float32 q/k/v matrix goes to memory and no separate pass reads it back.
+// stacked q/k/v product.  Instead of storing it, the epilogue adds the bias, rotates the first
+// `rdim` elements of q and k heads by the token's row of a cos/sin table (half-split pairs
+// i, i + rdim/2 as in mini_hisparse/model.py:141-151, or interleaved pairs 2i, 2i + 1), and writes
+// q as bfloat16 and k, v into the token's page of the KV cache (model.py:169-170): no float32
+// q/k/v matrix goes to memory and no separate pass reads it back.
 struct QkvRopeArgs {
     const float* bias;          // [(nq + 2 nkv) d] or null
-    const float* cos_sin;       // [T, d]: cos of the d/2 angles, then sin
+    const float* cos_sin;       // [T, rdim]: cos of the rdim/2 angles, then sin (unused if rdim == 0)
+    int rdim, interleaved;      // rotated elements per head (multiple of 32, or of 16 if interleaved)
     const int* positions;       // [T]
     const int* tok_seg;         // [T]
     const int* block_table;     // [segments, table_width]
@@ -687,9 +689,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             if constexpr (EPI == 2) {
                 const int ra = ra0 + row_in_tile;
                 const bool live = ra < Ra;
-                const int d = qr.d, half = d >> 1;
+                const int d = qr.d, rdim = qr.rdim, half = rdim >> 1;
                 const int pos = live ? qr.positions[ra] : 0;
-                const float* cs = qr.cos_sin + (size_t)(live ? ra : 0) * d;
+                const float* cs = qr.cos_sin + (size_t)(live ? ra : 0) * rdim;
                 const int head0 = rb0 / d;
                 int page = -1;
                 if (live && qr.write_kv && head0 + bn / d > qr.nq) {        // the tile holds k or v heads
@@ -701,56 +703,114 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 }
                 const int within = pos % qr.P;
                 const int total_heads = qr.nq + 2 * qr.nkv;
-                // rotated heads: the chunk of 16 angles is the outer loop, so that a row's cos and
-                // sin are fetched once (16-byte loads) for all heads of the tile
-#pragma unroll 1
-                for (int c = 0; c < half; c += 16) {
-                    float4 cs4[4], sn4[4];
+                auto head_dst = [&](int head) -> __nv_bfloat16* {
+                    return head < qr.nq ? qr.q_out + (size_t)ra * qr.nq * d + head * d
+                                        : qr.cache + ((((size_t)page * 2 + 0) * qr.nkv + (head - qr.nq)) * qr.P + within) * d;
+                };
+                auto load_bias16 = [&](float (&b)[16], int col) {
+                    if (qr.bias) {
 #pragma unroll
-                    for (int x = 0; x < 4; ++x) {
-                        cs4[x] = *(const float4*)(cs + c + 4 * x);
-                        sn4[x] = *(const float4*)(cs + half + c + 4 * x);
+                        for (int x = 0; x < 4; ++x) *(float4*)(b + 4 * x) = *(const float4*)(qr.bias + col + 4 * x);
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < 16; ++x) b[x] = 0.f;
                     }
-                    const float* cf = (const float*)cs4;
-                    const float* sf = (const float*)sn4;
+                };
+                auto store16 = [&](__nv_bfloat16* dst, const float (&v)[16]) {
+                    uint32_t pk[8];
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) {
+                        __nv_bfloat162 t2 = __floats2bfloat162_rn(v[2 * x], v[2 * x + 1]);
+                        pk[x] = *(uint32_t*)&t2;
+                    }
+                    *(uint4*)(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    *(uint4*)(dst + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                };
+                // rotated heads: the chunk of angles is the outer loop, so that a row's cos and
+                // sin are fetched once (16-byte loads) for all heads of the tile
+                if (!qr.interleaved) {
+#pragma unroll 1
+                    for (int c = 0; c < half; c += 16) {
+                        float4 cs4[4], sn4[4];
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) {
+                            cs4[x] = *(const float4*)(cs + c + 4 * x);
+                            sn4[x] = *(const float4*)(cs + half + c + 4 * x);
+                        }
+                        const float* cf = (const float*)cs4;
+                        const float* sf = (const float*)sn4;
+#pragma unroll 1
+                        for (int hh = 0; hh < bn / d; ++hh) {
+                            const int head = head0 + hh;
+                            if (head >= qr.nq + qr.nkv) break;               // value heads and the edge: below
+                            const bool is_q = head < qr.nq;
+                            uint32_t ra16[16], rb16[16];
+                            tmem_ld16(acc + hh * d + c, ra16);
+                            tmem_ld16(acc + hh * d + half + c, rb16);
+                            tmem_ld_wait();
+                            if (!live || (!is_q && page < 0)) continue;
+                            __nv_bfloat16* dst = head_dst(head);
+                            float ba[16], bb[16], oa[16], ob[16];
+                            load_bias16(ba, head * d + c);
+                            load_bias16(bb, head * d + half + c);
+#pragma unroll
+                            for (int x = 0; x < 16; ++x) {
+                                const float a0 = __uint_as_float(ra16[x]) + ba[x], b0 = __uint_as_float(rb16[x]) + bb[x];
+                                oa[x] = a0 * cf[x] - b0 * sf[x];
+                                ob[x] = b0 * cf[x] + a0 * sf[x];
+                            }
+                            store16(dst + c, oa);
+                            store16(dst + half + c, ob);
+                        }
+                    }
+                } else {
+#pragma unroll 1
+                    for (int c = 0; c < rdim; c += 16) {        // 16 columns = 8 pairs = angles c/2 .. c/2 + 7
+                        float4 cs4[2], sn4[2];
+#pragma unroll
+                        for (int x = 0; x < 2; ++x) {
+                            cs4[x] = *(const float4*)(cs + (c >> 1) + 4 * x);
+                            sn4[x] = *(const float4*)(cs + half + (c >> 1) + 4 * x);
+                        }
+                        const float* cf = (const float*)cs4;
+                        const float* sf = (const float*)sn4;
+#pragma unroll 1
+                        for (int hh = 0; hh < bn / d; ++hh) {
+                            const int head = head0 + hh;
+                            if (head >= qr.nq + qr.nkv) break;
+                            const bool is_q = head < qr.nq;
+                            uint32_t r16[16];
+                            tmem_ld16(acc + hh * d + c, r16);
+                            tmem_ld_wait();
+                            if (!live || (!is_q && page < 0)) continue;
+                            float bv[16], o[16];
+                            load_bias16(bv, head * d + c);
+#pragma unroll
+                            for (int x = 0; x < 8; ++x) {
+                                const float a0 = __uint_as_float(r16[2 * x]) + bv[2 * x], b0 = __uint_as_float(r16[2 * x + 1]) + bv[2 * x + 1];
+                                o[2 * x] = a0 * cf[x] - b0 * sf[x];
+                                o[2 * x + 1] = b0 * cf[x] + a0 * sf[x];
+                            }
+                            store16(head_dst(head) + c, o);
+                        }
+                    }
+                }
+                // the elements of q and k heads behind the rotated ones: bias only
+#pragma unroll 1
+                for (int c = rdim; c < d; c += 16) {
 #pragma unroll 1
                     for (int hh = 0; hh < bn / d; ++hh) {
                         const int head = head0 + hh;
-                        if (head >= qr.nq + qr.nkv) break;               // value heads and the edge: below
-                        const int col0 = head * d;
-                        const bool is_q = head < qr.nq;
-                        uint32_t ra16[16], rb16[16];
-                        tmem_ld16(acc + hh * d + c, ra16);
-                        tmem_ld16(acc + hh * d + half + c, rb16);
+                        if (head >= qr.nq + qr.nkv) break;
+                        uint32_t r16[16];
+                        tmem_ld16(acc + hh * d + c, r16);
                         tmem_ld_wait();
-                        if (!live || (!is_q && page < 0)) continue;
-                        __nv_bfloat16* dst = is_q ? qr.q_out + (size_t)ra * qr.nq * d + col0
-                                                  : qr.cache + ((((size_t)page * 2 + 0) * qr.nkv + (head - qr.nq)) * qr.P + within) * d;
-                        float ba[16], bb[16];
-                        if (qr.bias) {
+                        if (!live || (head >= qr.nq && page < 0)) continue;
+                        float bv[16], o[16];
+                        load_bias16(bv, head * d + c);
 #pragma unroll
-                            for (int x = 0; x < 4; ++x) {
-                                *(float4*)(ba + 4 * x) = *(const float4*)(qr.bias + col0 + c + 4 * x);
-                                *(float4*)(bb + 4 * x) = *(const float4*)(qr.bias + col0 + half + c + 4 * x);
-                            }
-                        } else {
-#pragma unroll
-                            for (int x = 0; x < 16; ++x) ba[x] = bb[x] = 0.f;
-                        }
-                        uint32_t pa[8], pb[8];
-#pragma unroll
-                        for (int x = 0; x < 8; ++x) {
-                            const float a0 = __uint_as_float(ra16[2 * x]) + ba[2 * x], a1 = __uint_as_float(ra16[2 * x + 1]) + ba[2 * x + 1];
-                            const float b0 = __uint_as_float(rb16[2 * x]) + bb[2 * x], b1 = __uint_as_float(rb16[2 * x + 1]) + bb[2 * x + 1];
-                            __nv_bfloat162 ta = __floats2bfloat162_rn(a0 * cf[2 * x] - b0 * sf[2 * x], a1 * cf[2 * x + 1] - b1 * sf[2 * x + 1]);
-                            __nv_bfloat162 tb = __floats2bfloat162_rn(b0 * cf[2 * x] + a0 * sf[2 * x], b1 * cf[2 * x + 1] + a1 * sf[2 * x + 1]);
-                            pa[x] = *(uint32_t*)&ta;
-                            pb[x] = *(uint32_t*)&tb;
-                        }
-                        *(uint4*)(dst + c) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
-                        *(uint4*)(dst + c + 8) = make_uint4(pa[4], pa[5], pa[6], pa[7]);
-                        *(uint4*)(dst + half + c) = make_uint4(pb[0], pb[1], pb[2], pb[3]);
-                        *(uint4*)(dst + half + c + 8) = make_uint4(pb[4], pb[5], pb[6], pb[7]);
+                        for (int x = 0; x < 16; ++x) o[x] = __uint_as_float(r16[x]) + bv[x];
+                        store16(head_dst(head) + c, o);
                     }
                 }
                 // value heads: bias, no rotation
@@ -1008,20 +1068,31 @@ MHB_EXPORT int mhb_gemm_tc(const void* X, const void* W, void* C, int c_dtype, i
 
 // The stacked q/k/v product of more than 64 tokens with bias, rotation and the append to the paged
 // KV cache done by its epilogue (see QkvRopeArgs): q_out [M, nq d] bfloat16, cache one layer's pool
-// [pages, 2, nkv, P, d] bfloat16, cos_sin [M, d] float32 (mhb_rope_table).  Head size 64 or 128.
+// [pages, 2, nkv, P, d] bfloat16, cos_sin [M, rotary_dim] float32 (mhb_rope_table).  Head size 64 or
+// 128; rotary_dim a multiple of 32 (half-split pairs) or of 16 (interleaved pairs), or 0.
+MHB_EXPORT int mhb_gemm_tc_qkv_rope_supports(int d, int rotary_dim, int interleaved) {
+    return (d == 64 || d == 128) && rotary_dim >= 0 && rotary_dim <= d && rotary_dim % (interleaved ? 16 : 32) == 0;
+}
+
 MHB_EXPORT int mhb_gemm_tc_qkv_rope(const void* X, const void* W, int M, int K, long long lda, long long ldw,
-                                    const float* bias, const float* cos_sin, const int* positions,
+                                    const float* bias, const float* cos_sin, int rotary_dim, int interleaved,
+                                    const int* positions,
                                     const int* tok_seg, const int* block_table, int table_width, void* q_out,
                                     void* cache, int nq, int nkv, int d, int P, int num_pages, int write_kv,
                                     int* status, cudaStream_t stream) {
     if (M <= 0) return 0;
-    if (d != 64 && d != 128) return fail("gemm_tc_qkv_rope: head size %d (64 or 128)", d);
+    if (!mhb_gemm_tc_qkv_rope_supports(d, rotary_dim, interleaved))
+        return fail("gemm_tc_qkv_rope: head size %d with %d rotated elements (%s pairs) is not built: head size 64 or "
+                    "128, rotated elements a multiple of %d", d, rotary_dim, interleaved ? "interleaved" : "half-split",
+                    interleaved ? 16 : 32);
+    if (rotary_dim > 0 && (cos_sin == nullptr || ((uintptr_t)cos_sin & 15)))
+        return fail("gemm_tc_qkv_rope: the cos/sin table must be given and 16-byte aligned");
     if (K <= 0 || K % 8 || lda % 8 || ldw % 8) return fail("gemm_tc: K, lda and ldw must be multiples of 8 (K %d, lda %lld, ldw %lld)", K, lda, ldw);
     if (((uintptr_t)X & 15) || ((uintptr_t)W & 15) || ((uintptr_t)q_out & 15) || ((uintptr_t)cache & 15))
         return fail("gemm_tc_qkv_rope: operands must be 16-byte aligned");
     if (nq <= 0 || nkv <= 0 || P <= 0) return fail("gemm_tc_qkv_rope: bad head counts or page size");
     QkvRopeArgs qr;
-    qr.bias = bias; qr.cos_sin = cos_sin; qr.positions = positions; qr.tok_seg = tok_seg; qr.block_table = block_table;
+    qr.bias = bias; qr.cos_sin = cos_sin; qr.rdim = rotary_dim; qr.interleaved = interleaved ? 1 : 0; qr.positions = positions; qr.tok_seg = tok_seg; qr.block_table = block_table;
     qr.q_out = (__nv_bfloat16*)q_out; qr.cache = (__nv_bfloat16*)cache; qr.table_width = table_width;
     qr.nq = nq; qr.nkv = nkv; qr.d = d; qr.P = P; qr.num_pages = num_pages; qr.write_kv = write_kv;
     const int N = (nq + 2 * nkv) * d;

@@ -18,7 +18,7 @@ from ..parts.base import Runtime
 from ..sampling.sampler import Sampler, SamplingParams
 from ..weights.loader import init_random, load_weights
 from .scheduler import Request, Scheduler, SchedulerConfig
-from .step import ModelRunner, StepEntry
+from .step import ModelRunner, StepEntry, StepError
 
 _DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "fp32": torch.float32,
            "bf16": torch.bfloat16, torch.float32: torch.float32, torch.bfloat16: torch.bfloat16}
@@ -55,7 +55,7 @@ class Engine:
     def __init__(self, model: DecoderModel, cache_config: CacheConfig | None = None, *,
                  num_pages: int | None = None, page_size: int = 16, max_requests: int = 8,
                  max_tokens_per_step: int = 2048, eos_token_id: int | None = None,
-                 use_graphs: bool = True):
+                 use_graphs: bool = True, max_step_requests: int | None = None):
         self.model = model
         if cache_config is None:
             if num_pages is None:
@@ -71,7 +71,7 @@ class Engine:
         self.cache = CacheManager(model.cache_needs, cache_config)
         self.runner = ModelRunner(model, self.cache, use_graphs=use_graphs)
         eos = eos_token_id if eos_token_id is not None else model.spec.eos_token_id
-        self.scheduler = Scheduler(self.cache, SchedulerConfig(max_tokens_per_step),
+        self.scheduler = Scheduler(self.cache, SchedulerConfig(max_tokens_per_step, max_step_requests),
                                    model.spec.vocab_size, model.spec.max_positions, eos)
         self.sampler = Sampler(model.rt.device, max_rows=cache_config.max_requests)
         self.timeline: list[dict] = []
@@ -96,9 +96,26 @@ class Engine:
         return self.scheduler.add(request_id, prompt, params)
 
     def step(self) -> list[tuple[object, int]]:
+        """One scheduler tick: plan, run the batch, sample, commit.  If a kernel reports a fault
+        (StepError), every request of that step is finished as failed and gives back its pages
+        (the cache had already taken their tokens, so they could not be fed again), the runner's
+        self-resetting scratch is put back to zero, and the error is raised; the engine and the
+        requests that were not in the step go on."""
         planned = self.scheduler.plan()
         if not planned:
             return []
+        try:
+            sampled = self._run(planned)
+        except StepError:
+            self.runner.reset_after_error()
+            self.scheduler.fail(planned)
+            raise
+        emitted = self.scheduler.commit(planned, sampled)
+        self.timeline.append({"active": len(self.scheduler.running), "waiting": len(self.scheduler.waiting),
+                              "tokens": sum(len(p.tokens) for p in planned)})
+        return emitted
+
+    def _run(self, planned) -> list[int]:
         entries = [StepEntry(p.request.request_id, p.tokens, [len(p.tokens) - 1] if p.sample else [])
                    for p in planned]
         logits = self.runner.step(entries)
@@ -121,10 +138,7 @@ class Engine:
             sampled = self.sampler.collect()
             self.runner.check_status(queued=True)    # the status word is sticky: a step without
                                                      # samples is checked with the next one
-        emitted = self.scheduler.commit(planned, sampled)
-        self.timeline.append({"active": len(self.scheduler.running), "waiting": len(self.scheduler.waiting),
-                              "tokens": sum(len(p.tokens) for p in planned)})
-        return emitted
+        return sampled
 
     def run(self) -> dict:
         while not self.scheduler.idle:

@@ -34,6 +34,7 @@ class Request:
     admitted: bool = False
     finished: bool = False
     cancelled: bool = False
+    failed: bool = False               # its step raised: what it holds was given back, it will not go on
 
     @property
     def max_new_tokens(self) -> int:
@@ -194,6 +195,22 @@ class Scheduler:
             return
         r.cancelled = True
         self._finish(r)
+
+    def fail(self, planned: list[Planned]) -> list[object]:
+        """The step that ran ``planned`` raised after the cache may already have taken its tokens:
+        the requests' positions in the cache and in the scheduler's books no longer agree, so none
+        of them can go on.  Each is finished as failed and gives back what it holds; requests that
+        were not in the step are untouched.  Returns the failed ids."""
+        failed = []
+        for p in planned:
+            r = p.request
+            if r.finished:
+                continue
+            r.failed = True
+            self._finish(r)
+            failed.append(r.request_id)
+        self.stats["failed_requests"] = self.stats.get("failed_requests", 0) + len(failed)
+        return failed
 
     @property
     def idle(self) -> bool:

@@ -22,9 +22,7 @@ from ..cache.allocator import CapacityError
 from ..cache.manager import CacheManager
 from ..kernels import api as K
 from ..kernels import build
-from ..parts.attention import ITEM_INTS, ROW_TILE, plan_attention, plan_capacity, plan_decode
-from ..parts.base import CacheView, Segment, StepContext, Workspace
-from ..parts.spec import PagedKVNeed
+from ..parts.base import CacheView, Segment, StepContext, StepPlanner, Workspace
 
 
 @dataclass
@@ -45,10 +43,11 @@ def _round_up(n: int, m: int) -> int:
 
 
 class _Layout:
-    """Offsets (in int32 words) of the packed per-step arrays for given sizes."""
+    """Offsets (in int32 words) of the packed per-step arrays for given sizes: the batch's own
+    arrays, one block table per page group, and the arrays of every plan slot."""
 
-    def __init__(self, T: int, S: int, R: int, groups: list[tuple[int, int]]):
-        self.T, self.S, self.R, self.groups = T, S, R, groups
+    def __init__(self, T: int, S: int, R: int, widths: list[int], plan_caps: list[dict[str, int]]):
+        self.T, self.S, self.R, self.widths, self.plan_caps = T, S, R, widths, plan_caps
         off = 0
 
         def take(n):
@@ -62,26 +61,21 @@ class _Layout:
         self.tok_seg = take(T)
         self.seg_slot = take(S)
         self.rows = take(R)
-        self.group_offsets = []
-        for items, width in groups:
-            self.group_offsets.append(
-                {
-                    "block_table": take(S * width),
-                    "items": take(items * ITEM_INTS),
-                    "tok_part_row": take(T),
-                    "tok_nsplit": take(T),
-                }
-            )
+        self.tables = [take(S * w) for w in widths]
+        self.plans = [{name: take(n) for name, n in caps.items()} for caps in plan_caps]
         self.total = off
 
 
 class _Staging:
-    """Two pinned host buffers used in turn, each guarded by an event of its last copy."""
+    """Two pinned host buffers used in turn, each guarded by an event of its last copy.  (Where no
+    CUDA device is visible, as in tests of the packing alone, the buffers are plain host memory
+    and there is nothing to guard.)"""
 
     def __init__(self):
         self.buffers = [None, None]
         self.events = [None, None]
         self.turn = 0
+        self.cuda = torch.cuda.is_available()
 
     def next(self, words: int) -> tuple[torch.Tensor, int]:
         i = self.turn
@@ -90,14 +84,25 @@ class _Staging:
             self.events[i].synchronize()
         buf = self.buffers[i]
         if buf is None or buf.numel() < words:
-            buf = torch.empty(max(words, 1024) * 2, dtype=torch.int32).pin_memory()
-            self.buffers[i] = buf
-        return buf, i
+            buf = torch.empty(max(words, 1024) * 2, dtype=torch.int32)
+            self.buffers[i] = buf.pin_memory() if self.cuda else buf
+        return self.buffers[i], i
 
     def mark(self, i: int):
+        if not self.cuda:
+            return
         ev = self.events[i] or torch.cuda.Event()
         ev.record()
         self.events[i] = ev
+
+
+@dataclass
+class _PlanSlot:
+    """One plan per step: the planner of the mixers of one page group whose plan keys are equal."""
+
+    gid: int
+    key: object
+    planner: StepPlanner
 
 
 class _DecodeGraph:
@@ -106,23 +111,23 @@ class _DecodeGraph:
     def __init__(self, runner: "ModelRunner", B: int, width: int):
         self.B = B
         self.ws = Workspace(runner.device)
+        batch = runner.batch
         max_keys = width * runner.cache.cfg.page_size
-        self.nsplit = [runner.batch.decode_splits(g.need, B, max_keys) for g in runner.cache.page_groups]
-        caps = []
-        for g, ns in zip(runner.cache.page_groups, self.nsplit):
-            groups = g.need.q_heads // g.need.kv_heads
-            chunks = 1 if groups <= ROW_TILE else -(-groups // ROW_TILE)
-            caps.append((B * ns * chunks, min(width, g.width)))
-        self.layout = _Layout(B, B, B, caps)
+        self.fixed = [slot.planner.decode_fixed(B, max_keys) for slot in batch.slots]
+        self.capturable = all(f is not None for f in self.fixed)
+        caps = [slot.planner.capacity(B, B, f) for slot, f in zip(batch.slots, self.fixed)]
+        self.layout = _Layout(B, B, B, [min(width, g.width) for g in runner.cache.page_groups], caps)
         self.meta = torch.zeros(self.layout.total, dtype=torch.int32, device=runner.device)
+        self.facts = None       # the plans' host facts at capture: every replay must bring the same
         self.graph = None
         self.logits = None
         self.launches = 0
 
 
 class BatchBuilder:
-    """Turns a step's entries into the device arrays the kernels read.  It knows the cache
-    manager, not the model: tests use it to run a single part."""
+    """Turns a step's entries into the device arrays the kernels read.  It knows the cache manager
+    and the planners that the cache's users bring, not the model: tests use it to run a single
+    part.  What a planner's arrays mean is the planner's and its mixer's business."""
 
     def __init__(self, cache: CacheManager, device, sm_count: int | None = None):
         self.cache = cache
@@ -132,19 +137,29 @@ class BatchBuilder:
         self.sm_count = sm_count
         self.meta = None
         self.staging = _Staging()
+        self.slots: list[_PlanSlot] = []
+        self.users: list[tuple[int | None, int | None]] = []     # user -> (cache entry, plan slot)
 
-    # ---- planning ----------------------------------------------------------------------------
-    def decode_splits(self, need: PagedKVNeed, B: int, max_keys: int) -> int:
-        """Key splits per decoded token for a batch of B with at most ``max_keys`` cached keys: as
-        many CTAs as are resident at once (two per SM), never more, so that no CTA waits for a
-        second wave, and no split shorter than MIN_KEYS_PER_SPLIT keys."""
-        from ..parts.attention import MAX_SPLITS, MIN_KEYS_PER_SPLIT, ROW_TILE
+    def add_user(self, cache_entry: int | None, part=None) -> int:
+        """Register a reader of cache entry ``cache_entry`` (a run entry's block or mixer; anything
+        with plan_key() and planner()); returns the index that cache_view() takes."""
+        slot = None
+        where = self.cache.entry_group[cache_entry] if cache_entry is not None else None
+        if where is not None and where[0] == "pages" and part is not None and part.plan_key() is not None:
+            gid, key = where[1], part.plan_key()
+            for i, sl in enumerate(self.slots):
+                if sl.gid == gid and sl.key == key:
+                    slot = i
+                    break
+            else:
+                planner = part.planner(self.cache.cfg.page_size, self.sm_count)
+                if planner is not None:
+                    self.slots.append(_PlanSlot(gid, key, planner))
+                    slot = len(self.slots) - 1
+        self.users.append((cache_entry, slot))
+        return len(self.users) - 1
 
-        groups = need.q_heads // need.kv_heads
-        chunks = 1 if groups <= ROW_TILE else -(-groups // ROW_TILE)
-        ctas = B * need.kv_heads * chunks
-        return max(1, min(MAX_SPLITS, (2 * self.sm_count) // ctas, max_keys // MIN_KEYS_PER_SPLIT))
-
+    # ---- packing -----------------------------------------------------------------------------
     def segments(self, entries: list[StepEntry]) -> tuple[list[Segment], int]:
         segments, offset = [], 0
         seen = set()
@@ -163,8 +178,21 @@ class BatchBuilder:
             offset += n
         return segments, offset
 
-    def _fill(self, buf: np.ndarray, layout: _Layout, entries, segments, fixed_nsplit=None):
-        """Write the step's arrays into ``buf`` at the layout's offsets; return per-group facts."""
+    @staticmethod
+    def _put(buf: np.ndarray, offsets: dict[str, int], caps: dict[str, int], arrays: dict[str, np.ndarray],
+             exact: bool = False) -> None:
+        for name, cap in caps.items():
+            arr = arrays[name]
+            n = arr.size
+            if n > cap or (exact and n != cap):
+                raise StepError(f"plan array {name!r} has {n} words, the layout holds {cap}")
+            region = buf[offsets[name]: offsets[name] + cap]
+            region[:n] = arr.reshape(-1)
+            region[n:] = 0
+
+    def _fill(self, buf: np.ndarray, layout: _Layout, entries, segments):
+        """Write the step's arrays into ``buf`` at the layout's offsets; return the wanted rows'
+        count and the plans' host facts."""
         T = sum(s.count for s in segments)
         tokens = buf[layout.tokens : layout.tokens + T]
         positions = buf[layout.positions : layout.positions + T]
@@ -180,29 +208,20 @@ class BatchBuilder:
         if len(rows) > layout.R:
             raise StepError("more rows wanted than the layout holds")
         buf[layout.rows : layout.rows + len(rows)] = rows
-        facts = []
+        slots = [s.slot for s in segments]
         for gi, g in enumerate(self.cache.page_groups):
-            offs = layout.group_offsets[gi]
-            cap_items, width = layout.groups[gi]
-            table = self.cache.table_rows(g.gid, [s.slot for s in segments], width)
-            buf[offs["block_table"] : offs["block_table"] + table.size] = table.reshape(-1)
-            plan = plan_attention(g.need, segments, T, self.sm_count,
-                                  fixed_nsplit=None if fixed_nsplit is None else fixed_nsplit[gi])
-            n_items = plan.items.shape[0]
-            if n_items > cap_items:
-                raise StepError(f"attention plan has {n_items} items, layout holds {cap_items}")
-            region = buf[offs["items"] : offs["items"] + cap_items * ITEM_INTS]
-            region[: n_items * ITEM_INTS] = plan.items.reshape(-1)
-            region[n_items * ITEM_INTS :] = 0
-            buf[offs["tok_part_row"] : offs["tok_part_row"] + T] = plan.tok_part_row
-            buf[offs["tok_nsplit"] : offs["tok_nsplit"] + T] = plan.tok_nsplit
-            facts.append({"n_small": plan.n_small, "n_big": plan.n_big, "part_rows": plan.part_rows,
-                          "any_split": bool(plan.part_rows), "big_split": plan.big_split})
+            table = self.cache.table_rows(g.gid, slots, layout.widths[gi])
+            buf[layout.tables[gi] : layout.tables[gi] + table.size] = table.reshape(-1)
+        facts = []
+        for pi, slot in enumerate(self.slots):
+            arrays, f = slot.planner.plan(segments, T)
+            self._put(buf, layout.plans[pi], layout.plan_caps[pi], arrays)
+            facts.append(f)
         return len(rows), facts
 
-    def _fill_decode(self, buf: np.ndarray, layout: _Layout, entries, segments, nsplit):
+    def _fill_decode(self, buf: np.ndarray, layout: _Layout, entries, segments, fixed) -> list[dict]:
         """_fill for a batch of single decoded tokens that all want their logits, without loops
-        over tokens: the arrays a captured decode graph reads."""
+        over tokens: the arrays a captured decode graph reads.  Returns the plans' facts."""
         B = len(segments)
         starts = np.fromiter((s.start for s in segments), np.int64, B)
         slots = np.fromiter((s.slot for s in segments), np.intp, B)
@@ -213,46 +232,32 @@ class BatchBuilder:
         buf[layout.seg_slot : layout.seg_slot + B] = slots
         buf[layout.rows : layout.rows + B] = ar
         for gi, g in enumerate(self.cache.page_groups):
-            offs = layout.group_offsets[gi]
-            cap_items, width = layout.groups[gi]
-            buf[offs["block_table"] : offs["block_table"] + B * width].reshape(B, width)[:] = g.table_np[slots, :width]
-            plan = plan_decode(g.need, starts, nsplit[gi])
-            n = plan.items.shape[0]
-            if n != cap_items:
-                raise StepError(f"decode plan has {n} items, the graph was captured for {cap_items}")
-            buf[offs["items"] : offs["items"] + n * ITEM_INTS] = plan.items.reshape(-1)
-            buf[offs["tok_part_row"] : offs["tok_part_row"] + B] = plan.tok_part_row
-            buf[offs["tok_nsplit"] : offs["tok_nsplit"] + B] = plan.tok_nsplit
+            width = layout.widths[gi]
+            buf[layout.tables[gi] : layout.tables[gi] + B * width].reshape(B, width)[:] = g.table_np[slots, :width]
+        facts = []
+        for pi, slot in enumerate(self.slots):
+            arrays, f = slot.planner.plan_decode(starts, fixed[pi])
+            self._put(buf, layout.plans[pi], layout.plan_caps[pi], arrays, exact=True)
+            facts.append(f)
+        return facts
 
-    def _views(self, meta: torch.Tensor, layout: _Layout, T: int, S: int, R: int, facts, launch_items=None):
+    def _views(self, meta: torch.Tensor, layout: _Layout, T: int, S: int, R: int, facts) -> dict:
         def v(off, n):
             return meta[off : off + n]
 
-        group_meta = []
-        for gi, g in enumerate(self.cache.page_groups):
-            offs = layout.group_offsets[gi]
-            cap_items, width = layout.groups[gi]
-            f = facts[gi]
-            group_meta.append(
-                {
-                    "block_table": v(offs["block_table"], S * width).view(S, width),
-                    "items": v(offs["items"], cap_items * ITEM_INTS),
-                    "n_small": cap_items if launch_items else f["n_small"],
-                    "n_big": 0 if launch_items else f["n_big"],
-                    "tok_part_row": v(offs["tok_part_row"], T),
-                    "tok_nsplit": v(offs["tok_nsplit"], T),
-                    "part_rows_cap": f["part_rows"],
-                    "any_split": f["any_split"],
-                    "big_split": f.get("big_split", False),
-                }
-            )
+        plans = []
+        for pi in range(len(self.slots)):
+            d = {name: v(layout.plans[pi][name], cap) for name, cap in layout.plan_caps[pi].items()}
+            d.update(facts[pi])
+            plans.append(d)
         return {
             "tokens": v(layout.tokens, T),
             "positions": v(layout.positions, T),
             "tok_seg": v(layout.tok_seg, T),
             "seg_slot": v(layout.seg_slot, S),
             "rows": v(layout.rows, R) if R else None,
-            "groups": group_meta,
+            "tables": [v(layout.tables[gi], S * w).view(S, w) for gi, w in enumerate(layout.widths)],
+            "plans": plans,
         }
 
     def eager(self, entries, segments):
@@ -260,12 +265,10 @@ class BatchBuilder:
         T = sum(s.count for s in segments)
         S = len(segments)
         R = sum(len(e.want) for e in entries)
-        caps = []
-        for g in self.cache.page_groups:
-            items, _ = plan_capacity(g.need, T, S)
-            width = max(1, max(-(-(s.start + s.count) // self.cache.cfg.page_size) for s in segments))
-            caps.append((items, min(width, g.width)))
-        layout = _Layout(T, S, R, caps)
+        need_pages = max(1, max(-(-(s.start + s.count) // self.cache.cfg.page_size) for s in segments))
+        widths = [min(need_pages, g.width) for g in self.cache.page_groups]
+        caps = [slot.planner.capacity(T, S) for slot in self.slots]
+        layout = _Layout(T, S, R, widths, caps)
         stage, turn = self.staging.next(layout.total)
         _, facts = self._fill(stage.numpy(), layout, entries, segments)
         if self.meta is None or self.meta.numel() < layout.total:
@@ -281,24 +284,34 @@ class BatchBuilder:
             seg_slot=views["seg_slot"], status=status,
         )
 
-    def cache_view(self, entry: int, group_meta, writable: bool = True) -> CacheView | None:
-        """The view of cache entry ``entry`` for one step."""
-        where = self.cache.entry_group[entry]
+    def cache_view(self, user: int, views: dict, writable: bool = True) -> CacheView | None:
+        """The view of its cache entry for user ``user`` (see add_user) in one step."""
+        entry, slot = self.users[user]
+        where = self.cache.entry_group[entry] if entry is not None else None
         if where is None:
             return None
         kind, g, storage = self.cache.entry_storage(entry)
         if kind == "pages":
+            meta = {"block_table": views["tables"][g.gid]}
+            if slot is not None:
+                meta.update(views["plans"][slot])
             return CacheView(g.need, g.gid, where[2], writable, storage,
-                             page_size=self.cache.cfg.page_size, meta=group_meta[g.gid])
+                             page_size=self.cache.cfg.page_size, meta=meta)
         return CacheView(g.need, g.gid, where[2], writable, storage)
 
 
 class ModelRunner:
+    MAX_GRAPHS = 16      # captured decode graphs kept (each holds a workspace of its own); least recently used goes
+
     def __init__(self, model, cache: CacheManager, use_graphs: bool = True, sm_count: int | None = None):
         self.model, self.cache = model, cache
         self.rt = model.rt
         self.device = self.rt.device
+        for block in model.blocks:
+            block.check_cache(cache.cfg.page_size)      # refuse now what a step would refuse half-way
         self.batch = BatchBuilder(cache, self.device, sm_count)
+        for i, entry in enumerate(model.spec.order):
+            self.batch.add_user(model.entry_cache[i], model.blocks[entry.layer])
         self.sm_count = self.batch.sm_count
         self.ws = Workspace(self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -310,15 +323,14 @@ class ModelRunner:
         self.observer = None
         self.side_stream = None
         self.side_events = None
-        self.stats = {"steps": 0, "tokens": 0, "graph_steps": 0, "two_stream_layers": 0, "prepared_steps": 0}
+        self.stats = {"steps": 0, "tokens": 0, "graph_steps": 0, "graph_captures": 0, "two_stream_layers": 0,
+                      "prepared_steps": 0}
         self._ahead = None      # index arrays of the next decode step, packed while the GPU ran this one
         build.build_all(model.kernel_modules())
 
-    def _cache_views(self, group_meta) -> list[CacheView | None]:
-        return [
-            self.batch.cache_view(self.model.entry_cache[i], group_meta, writable=entry.cache_of is None)
-            for i, entry in enumerate(self.model.spec.order)
-        ]
+    def _cache_views(self, views) -> list[CacheView | None]:
+        return [self.batch.cache_view(i, views, writable=entry.cache_of is None)
+                for i, entry in enumerate(self.model.spec.order)]
 
     # ---- the step -----------------------------------------------------------------------------
     @torch.inference_mode()
@@ -351,9 +363,10 @@ class ModelRunner:
             self.cache.ensure(s.request, s.start + s.count)
         decode_only = all(s.count == 1 for s in segments) and all(e.want == [0] for e in entries)
         ahead, self._ahead = self._ahead, None       # what was packed ahead serves this step or none
-        if self.use_graphs and decode_only:
+        logits = None
+        if self.use_graphs and decode_only and self.observer is None:   # a hook's calls are not replayed
             logits = self._step_graph(entries, segments, ahead)
-        else:
+        if logits is None:
             logits = self._step_eager(entries, segments, T)
         for s in segments:
             self.cache.advance(s.request, s.count)
@@ -375,18 +388,30 @@ class ModelRunner:
                 self.side_events = (torch.cuda.Event(), torch.cuda.Event())
             ctx.extras["side_stream"] = self.side_stream
             ctx.extras["side_events"] = self.side_events
-        caches = self._cache_views(views["groups"])
+        caches = self._cache_views(views)
         with K.stream_scope():
             out = self.model.forward(ctx, caches, views["rows"], observer=self.observer)
         self.stats["two_stream_layers"] += ctx.extras.get("two_stream_layers", 0)
         return out
 
-    def _step_graph(self, entries, segments, ahead=None):
-        B = len(segments)
-        width = self._table_width(segments)
-        g = self.graphs.get((B, width))
+    def _graph_for(self, B: int, width: int) -> _DecodeGraph:
+        g = self.graphs.pop((B, width), None)
         if g is None:
-            g = self.graphs[(B, width)] = _DecodeGraph(self, B, width)
+            g = _DecodeGraph(self, B, width)
+            while len(self.graphs) >= self.MAX_GRAPHS:          # the dict keeps the order of last use
+                old = self.graphs.pop(next(iter(self.graphs)))
+                if self._ahead is not None and self._ahead["graph"] is old:
+                    self._ahead = None
+        self.graphs[(B, width)] = g
+        return g
+
+    def _step_graph(self, entries, segments, ahead=None):
+        """The step through a captured graph, or None if a planner cannot hold its plan constant
+        (then the step runs eagerly)."""
+        B = len(segments)
+        g = self._graph_for(B, self._table_width(segments))
+        if not g.capturable:
+            return None
         layout = g.layout
         if (ahead is not None and ahead["graph"] is g and g.graph is not None
                 and ahead["who"] == [(s.request, s.slot, s.start) for s in segments]):
@@ -396,16 +421,15 @@ class ModelRunner:
             self.stats["prepared_steps"] += 1
         else:
             stage, turn = self.batch.staging.next(layout.total)
-            self.batch._fill_decode(stage.numpy(), layout, entries, segments, g.nsplit)
+            facts = self.batch._fill_decode(stage.numpy(), layout, entries, segments, g.fixed)
+            if g.facts is None:
+                g.facts = facts
+            elif facts != g.facts:
+                raise StepError(f"a decode plan changed after its graph was captured: {facts} vs {g.facts}")
         g.meta.copy_(stage[: layout.total], non_blocking=True)
         self.batch.staging.mark(turn)
         if g.graph is None:
-            # fixed facts for the capture: every item slot is launched, splits are constant
-            fixed = []
-            for gi, pg in enumerate(self.cache.page_groups):
-                fixed.append({"n_small": layout.groups[gi][0], "n_big": 0, "part_rows": B * g.nsplit[gi],
-                              "any_split": g.nsplit[gi] > 1})
-            views = self.batch._views(g.meta, layout, B, B, B, fixed, launch_items=True)
+            views = self.batch._views(g.meta, layout, B, B, B, g.facts)
             # one eager run sizes the workspace and warms the kernels up, then the capture
             g.logits = self._forward(g.ws, views, segments, B)
             g.ws.frozen = True
@@ -419,20 +443,22 @@ class ModelRunner:
             g.graph = graph
             # the capture itself ran nothing: the eager run above already produced this step
             self.stats["graph_steps"] += 1
+            self.stats["graph_captures"] += 1
             return g.logits
         g.graph.replay()
         K.launches += g.launches
         self.stats["graph_steps"] += 1
         return g.logits
 
-    def prepare_decode_ahead(self, requests: list) -> None:
+    def prepare_decode_ahead(self, requests: list, take_pages: bool = True) -> None:
         """Pack the index arrays of the NEXT step, assuming that it decodes one token for each of
         ``requests`` (in this order) and for nobody else.  Called between a decode step's launch and
         the wait for its result: the host would idle meanwhile, and positions, block tables and the
-        attention plan of the next step do not depend on the tokens still being computed.  If the
-        next step turns out differently (a request finished, another arrived), what was packed is
-        dropped and the step is packed as usual.  Pages the next positions need are taken now: a
-        request that ends after all gives them back with its others."""
+        plans of the next step do not depend on the tokens still being computed.  If the next step
+        turns out differently (a request finished, another arrived), what was packed is dropped and
+        the step is packed as usual.  Pages the next positions need are taken now (a request that
+        ends after all gives them back with its others); with ``take_pages`` False nothing is
+        packed when a page would have to be taken (for callers whose pool has no page to spare)."""
         self._ahead = None
         if not self.use_graphs or not requests:
             return
@@ -442,6 +468,10 @@ class ModelRunner:
             length = self.cache.length(e.request)
             if maxpos is not None and length + 1 > maxpos:
                 return
+            if not take_pages:
+                if not self.cache.has_pages(e.request, length + 1):
+                    return
+                continue
             try:
                 self.cache.ensure(e.request, length + 1)
             except CapacityError:
@@ -451,7 +481,8 @@ class ModelRunner:
         if g is None or g.graph is None:
             return              # that step will capture its graph: nothing to gain
         stage, turn = self.batch.staging.next(g.layout.total)
-        self.batch._fill_decode(stage.numpy(), g.layout, entries, segments, g.nsplit)
+        if self.batch._fill_decode(stage.numpy(), g.layout, entries, segments, g.fixed) != g.facts:
+            return
         self._ahead = {"graph": g, "stage": stage, "turn": turn,
                        "who": [(s.request, s.slot, s.start) for s in segments]}
 
@@ -464,27 +495,49 @@ class ModelRunner:
             width *= 2
         return width
 
+    # ---- the status word ------------------------------------------------------------------------
+    STATUS_BITS = {
+        1: "a token id outside the vocabulary reached the embedding",
+        2: "a position had no valid page in its block table",
+        4: "a bounded wait in the tensor-core matrix product ran out",
+        8: "a bounded wait in the TMA-fed attention kernel ran out",
+        16: "a bounded wait in the tcgen05 attention kernel ran out",
+        32: "a token's keys were split into more parts than the attention kernel merges",
+    }
+
+    @classmethod
+    def status_message(cls, bits: int) -> str:
+        what = [text for bit, text in cls.STATUS_BITS.items() if bits & bit]
+        rest = bits & ~sum(cls.STATUS_BITS)
+        if rest:
+            what.append(f"unknown status bits {rest:#x}")
+        return "; ".join(what)
+
     def queue_status(self) -> None:
         """Start the copy of the status word to the host; read it with check_status(queued=True)
         after the stream has been synchronised (saves a synchronisation of its own)."""
         self.status_host.copy_(self.status, non_blocking=True)
 
     def check_status(self, queued: bool = False) -> None:
-        """Raise if a kernel flagged a bad index (ids outside the table, pages outside the pool)."""
+        """Raise StepError if a kernel flagged a fault (ids outside the table, pages outside the pool,
+        a bounded wait that ran out).  Before raising, everything that such a kernel may have left
+        behind is put back: the status word, and the counters and flags that kernels hand to their
+        next launch as zero (see reset_after_error)."""
         bits = int(self.status_host.item()) if queued else int(self.status.item())
         if bits:
-            self.status.zero_()
-            what = []
-            if bits & 1:
-                what.append("a token id outside the vocabulary reached the embedding")
-            if bits & 2:
-                what.append("a position had no valid page in its block table")
-            if bits & 4:
-                what.append("a bounded wait in the tensor-core matrix product ran out")
-            if bits & 8:
-                what.append("a bounded wait in the TMA-fed attention kernel ran out")
-            if bits & 16:
-                what.append("a bounded wait in the tcgen05 attention kernel ran out")
-            if bits & 32:
-                what.append("a token's keys were split into more parts than the attention kernel merges")
-            raise StepError("; ".join(what) or f"kernel status {bits}")
+            self.reset_after_error()
+            raise StepError(self.status_message(bits))
+
+    def reset_after_error(self) -> None:
+        """A kernel that gave up may have left its self-resetting scratch non-zero: the counters of
+        the key-split merge in every workspace (this runner's and each captured graph's) and the
+        flags of the persistent product.  Zero them and the status word, so that the next step
+        starts clean; what was packed ahead is dropped."""
+        torch.cuda.synchronize(self.device)
+        self.status.zero_()
+        for ws in [self.ws] + [g.ws for g in self.graphs.values()]:
+            ws.zero_self_resetting()
+        scratch = getattr(self.rt, "_scratch", None)
+        if scratch is not None:
+            scratch[1].zero_()
+        self._ahead = None

@@ -111,23 +111,30 @@ def residual_add(x, delta, nsplit=1, split_stride=0):
 
 
 def rope_append(qkv, bias, positions, tok_seg, block_table, inv_freq, q_out, cache, *, nq, nkv, d,
-                page_size, write_kv=True, rotate=True, nsplit=1, split_stride=0, status=None):
+                page_size, write_kv=True, rotary_dim=None, interleaved=False, nsplit=1, split_stride=0,
+                status=None):
     """Bias + rotary encoding of q and k, q to ``q_out``, k and v into the cache pages.
 
     ``cache`` is one layer's pool [pages, 2, nkv, page_size, d]; ``block_table`` [S, width]
     holds the page ids of each segment of the batch, ``tok_seg`` [T] the segment of a token.
+    ``rotary_dim``: how many leading elements of a head are rotated (None: all of them when
+    ``inv_freq`` is given, else none); ``interleaved``: pairs (2i, 2i+1) instead of (i, i + rotary_dim/2).
     """
     lib = build.load("elementwise")
     T = q_out.shape[0]
     if cache.dtype != q_out.dtype:
         raise KernelError("rope_append: cache and activations must have one dtype")
+    if rotary_dim is None:
+        rotary_dim = d if inv_freq is not None else 0
+    if rotary_dim and (inv_freq is None or inv_freq.numel() != rotary_dim // 2):
+        raise KernelError(f"rope_append: {rotary_dim} rotated elements need {rotary_dim // 2} frequencies")
     _check(lib, lib.mhb_rope_append(
         _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_int(nsplit), c_longlong(split_stride),
         _ptr(bias), _ptr(positions), _ptr(tok_seg), _ptr(block_table),
         c_int(block_table.shape[-1]), _ptr(inv_freq), _ptr(q_out), _ptr(cache),
         c_int(dtype_code(q_out.dtype)), c_int(T), c_int(nq), c_int(nkv), c_int(d),
         c_int(page_size), c_int(cache.shape[0]), c_int(1 if write_kv else 0),
-        c_int(1 if rotate else 0), _ptr(status), _stream()), "rope_append")
+        c_int(rotary_dim), c_int(1 if interleaved else 0), _ptr(status), _stream()), "rope_append")
 
 
 def swiglu(gate_up, out, nsplit=1, split_stride=0, block=None):
@@ -218,29 +225,41 @@ def gemm_tc_swiglu(a, w, out, *, swap: bool, bn: int, status=None, scratch=None)
         c_int(1 if swap else 0), c_int(bn), *_scratch_ptrs(scratch), _ptr(status), _stream()), "gemm_tc_swiglu")
 
 
-def rope_table(positions, inv_freq, table, *, d: int, rotate: bool = True):
-    """table[t] = cos of token t's d/2 rotation angles, then their sin (float32), for the q/k/v
-    product's rotating epilogue."""
+def rope_table(positions, inv_freq, table):
+    """table[t] = cos of token t's rotation angles, then their sin (float32, [T, 2 * angles]), for the
+    q/k/v product's rotating epilogue."""
     lib = build.load("elementwise")
-    _check(lib, lib.mhb_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(table), c_int(positions.shape[0]),
-                                   c_int(d), c_int(1 if rotate else 0), _stream()), "rope_table")
+    T, rdim = table.shape
+    if inv_freq.numel() * 2 != rdim or table.dtype != torch.float32 or not table.is_contiguous():
+        raise KernelError("rope_table: the table must be float32 [tokens, 2 * frequencies]")
+    _check(lib, lib.mhb_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(table), c_int(T), c_int(rdim), _stream()),
+           "rope_table")
+
+
+def gemm_tc_qkv_rope_supports(d: int, rotary_dim: int, interleaved: bool) -> bool:
+    """Head sizes and rotations the q/k/v product's rotating epilogue is built for."""
+    return d in (64, 128) and 0 <= rotary_dim <= d and rotary_dim % (16 if interleaved else 32) == 0
 
 
 def gemm_tc_qkv_rope(x, w, bias, cos_sin, positions, tok_seg, block_table, q_out, cache, *, nq, nkv, d,
-                     page_size, write_kv=True, status=None):
+                     page_size, rotary_dim=None, interleaved=False, write_kv=True, status=None):
     """The stacked q/k/v product of more than 64 tokens whose epilogue adds the bias, rotates q and k
-    and writes q to ``q_out`` and k, v into the pages of ``cache`` (one layer's pool)."""
+    (``cos_sin`` from rope_table, None for no rotation) and writes q to ``q_out`` and k, v into the
+    pages of ``cache`` (one layer's pool)."""
     lib = build.load("gemm_tc")
     M, K = x.shape
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or q_out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("gemm_tc_qkv_rope: operands, q and the cache must be bfloat16")
     if tuple(w.shape) != ((nq + 2 * nkv) * d, K) or not cache.is_contiguous() or not q_out.is_contiguous():
         raise KernelError(f"gemm_tc_qkv_rope: w is {list(w.shape)}, expected [{(nq + 2 * nkv) * d}, {K}]; q and the pool must be contiguous")
-    if cos_sin.shape != (M, d) or cos_sin.dtype != torch.float32:
-        raise KernelError("gemm_tc_qkv_rope: the cos/sin table must be float32 [tokens, head_dim]")
+    if rotary_dim is None:
+        rotary_dim = cos_sin.shape[1] if cos_sin is not None else 0
+    if rotary_dim and (cos_sin is None or cos_sin.shape != (M, rotary_dim) or cos_sin.dtype != torch.float32):
+        raise KernelError("gemm_tc_qkv_rope: the cos/sin table must be float32 [tokens, rotated elements]")
     _check(lib, lib.mhb_gemm_tc_qkv_rope(
         _ptr(x), _ptr(w), c_int(M), c_int(K), c_longlong(x.stride(0)), c_longlong(w.stride(0)), _ptr(bias),
-        _ptr(cos_sin), _ptr(positions), _ptr(tok_seg), _ptr(block_table), c_int(block_table.shape[-1]), _ptr(q_out),
+        _ptr(cos_sin), c_int(rotary_dim), c_int(1 if interleaved else 0), _ptr(positions), _ptr(tok_seg),
+        _ptr(block_table), c_int(block_table.shape[-1]), _ptr(q_out),
         _ptr(cache), c_int(nq), c_int(nkv), c_int(d), c_int(page_size), c_int(cache.shape[0]),
         c_int(1 if write_kv else 0), _ptr(status), _stream()), "gemm_tc_qkv_rope")
 

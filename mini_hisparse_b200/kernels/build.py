@@ -2,7 +2,7 @@
 
 Each ``.cu`` file becomes one shared library, built the first time something asks for it:
 a float32 model never compiles the tensor-core kernels.  Libraries are named after a hash
-of their source, the shared headers and the flags, so a stale build is never loaded.  They
+of their source, every header of ``csrc/`` and the flags, so a stale build is never loaded.  They
 are built in-tree (``csrc/_build``) when that folder can be written, else under the
 system's temporary folder; no home directory and no network is needed.
 """
@@ -82,7 +82,7 @@ def build_dir() -> Path:
 def _digest(module: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
-    for path in sorted(CSRC.glob("*.cuh")) + [CSRC / f"{module}.cu"]:
+    for path in sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + [CSRC / f"{module}.cu"]:
         h.update(path.name.encode())
         h.update(path.read_bytes())
     return h.hexdigest()[:16]

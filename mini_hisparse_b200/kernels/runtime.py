@@ -81,19 +81,25 @@ class BFloat16Runtime(Runtime):
         appends, so the float32 q/k/v matrix is never written (a third of that product's time in a
         2,048-token prefill went into writing and re-reading it)."""
         M, Kd = x.shape
-        if (M <= 64 or d not in (64, 128) or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16
+        rdim = int(getattr(position, "rotary_dim", 0) or 0)
+        interleaved = bool(getattr(position, "interleaved", False))
+        if (M <= 64 or not K.gemm_tc_qkv_rope_supports(d, rdim, interleaved) or x.dtype != torch.bfloat16
+                or weight.dtype != torch.bfloat16
                 or cache_storage.dtype != torch.bfloat16 or Kd % 8 or x.stride(0) % 8 or weight.stride(0) % 8
                 or x.data_ptr() % 16 or weight.data_ptr() % 16 or not cache_storage.is_contiguous()):
             return False
-        tables = ctx.extras.setdefault("rope_tables", {})
-        key = (position.spec, d)       # frozen dataclass: layers with the same encoding share the table
-        table = tables.get(key)
-        if table is None:          # once per step for all layers with this encoding
-            table = ctx.ws.get(f"rope_table_{len(tables)}", (M, d), torch.float32)
-            K.rope_table(ctx.positions, position.inv_freq, table, d=d, rotate=position.rotates)
-            tables[key] = table
+        table = None
+        if rdim:
+            tables = ctx.extras.setdefault("rope_tables", {})
+            key = position.spec            # frozen dataclass: layers with the same encoding share the table
+            table = tables.get(key)
+            if table is None:              # once per step for all layers with this encoding
+                table = ctx.ws.get(f"rope_table_{len(tables)}", (M, rdim), torch.float32)
+                K.rope_table(ctx.positions, position.inv_freq, table)
+                tables[key] = table
         K.gemm_tc_qkv_rope(x, weight, bias, table, ctx.positions, ctx.tok_seg, block_table, q_out, cache_storage,
-                           nq=nq, nkv=nkv, d=d, page_size=page_size, write_kv=write_kv, status=self.status)
+                           nq=nq, nkv=nkv, d=d, page_size=page_size, rotary_dim=rdim, interleaved=interleaved,
+                           write_kv=write_kv, status=self.status)
         return True
 
     def linear(self, x, weight, ws: Workspace, name: str, out_dtype=None, bias=None,

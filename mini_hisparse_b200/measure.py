@@ -99,8 +99,7 @@ def decode_bytes(model, cache, live_tokens: int) -> int:
         weights -= emb.numel() * emb.element_size()
     kv = 0
     for g in cache.page_groups:
-        n = g.need
-        kv += len(g.entries) * 2 * n.kv_heads * n.head_dim * cache.cfg.dtype.itemsize * live_tokens
+        kv += g.page_bytes() // cache.cfg.page_size * live_tokens
     return weights + kv
 
 
@@ -121,14 +120,12 @@ def build_engine(config: dict, *, batch: int, context: int, dtype="bfloat16", de
     from .engine.engine import Engine, load_model
 
     config = dict(config)
-    full_layers = config["num_hidden_layers"]
     if layers is not None:
         config["num_hidden_layers"] = layers
     model = load_model(config, device=device, dtype=dtype, random_seed=weight_seed)
     pages = batch * -(-context // page_size) + extra_pages
     engine = Engine(model, num_pages=pages, page_size=page_size, max_requests=batch,
                     max_tokens_per_step=max_tokens_per_step)
-    engine.full_layers = full_layers
     return engine
 
 
@@ -184,81 +181,13 @@ def time_decode(engine, names, steps: int, warmup: int, vocab: int, sampled_warm
             "launches": K.launches - launches0, "clocks": clocks.result}
 
 
-def time_decode_e2e(engine, prompts: dict, steps: int, warmup: int) -> dict:
-    """The same through ``Engine.step()``: host token ids in, sampled host tokens out, every step."""
-    for name, (cached, last) in prompts.items():
-        pass
-    t0 = None
-    done = 0
-    B = len(engine.scheduler.running)
-    for i in range(warmup + steps):
-        if i == warmup:
-            torch.cuda.synchronize()
-            t0 = time.perf_counter()
-        emitted = engine.step()
-        if i >= warmup:
-            done += len(emitted)
-    torch.cuda.synchronize()
-    sec = time.perf_counter() - t0
-    return {"tokens_per_s": done / sec, "ms_per_step": sec / steps * 1e3, "batch": B}
-
-
-LEAVE_OUT = {
-    # name on the command line -> (function of kernels.api, filter on its arguments or None)
-    "add_rmsnorm": ("add_rmsnorm", None),
-    "rope_append": ("rope_append", None),
-    "attention": ("attention_tma", None),
-    "gate_up": ("gemm_tc_swiglu", None),
-    "qkv": ("gemm_tc", lambda cfg, a, w: w.shape[0] == (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"])
-            * (cfg["hidden_size"] // cfg["num_attention_heads"]) and w.shape[1] == cfg["hidden_size"]),
-    "o_proj": ("gemm_tc", lambda cfg, a, w: tuple(w.shape) == (cfg["hidden_size"], cfg["hidden_size"])),
-    "down": ("gemm_tc", lambda cfg, a, w: w.shape[1] == cfg["intermediate_size"]),
-    "lm_head": ("gemm_tc", lambda cfg, a, w: w.shape[0] == cfg["vocab_size"]),
-}
-
-
-class leave_out:
-    """Profiling aid: inside the block the named kernel launches are skipped, so that a decode
-    graph captured there lacks them.  The step's results are garbage; the difference of the step's
-    time with and without is what those launches cost INSIDE the graph, where launches overlap
-    (a profiler serialises them and cannot show that)."""
-
-    def __init__(self, config: dict, names):
-        self.config, self.names, self.saved = config, list(names), {}
-
-    def __enter__(self):
-        for n in self.names:
-            if n not in LEAVE_OUT:
-                raise ValueError(f"unknown kernel {n!r}: choose from {sorted(LEAVE_OUT)}")
-            fn_name, pred = LEAVE_OUT[n]
-            orig = getattr(K, fn_name)
-            self.saved.setdefault(fn_name, orig)
-            if pred is None:
-                setattr(K, fn_name, lambda *a, **k: None)
-            else:
-                def skipping(a, w, out, *rest, _orig=orig, _pred=pred, **k):
-                    return None if _pred(self.config, a, w) else _orig(a, w, out, *rest, **k)
-                setattr(K, fn_name, skipping)
-        return self
-
-    def __exit__(self, *exc):
-        for fn_name, orig in self.saved.items():
-            setattr(K, fn_name, orig)
-
-
 def decode_benchmark(config: dict, *, batch=8, prompt_tokens=1024, steps=20, warmup=3,
                      dtype="bfloat16", device="cuda:0", page_size=16, weight_seed=0,
-                     layers: int | None = None, leave_out_kernels=()) -> dict:
+                     layers: int | None = None) -> dict:
     """What ``bench`` of the command line prints: decode tokens a second at one batch size."""
     engine = build_engine(config, batch=batch, context=prompt_tokens + steps + warmup + 1, dtype=dtype,
                           device=device, page_size=page_size, weight_seed=weight_seed, layers=layers)
     names = synthetic_context(engine, batch, prompt_tokens)
-    if leave_out_kernels:
-        with leave_out(config, leave_out_kernels):
-            r = time_decode(engine, names, steps, warmup, engine.model.spec.vocab_size)
-        return {"metric": "decode step time with kernels left out (results are garbage)", "batch": batch,
-                "context": prompt_tokens, "dtype": dtype, "left_out": list(leave_out_kernels),
-                "ms_per_step": r["ms_per_step"]}
     r = time_decode(engine, names, steps, warmup, engine.model.spec.vocab_size)
     live = batch * (prompt_tokens + warmup + steps // 2)
     nbytes = decode_bytes(engine.model, engine.cache, live)

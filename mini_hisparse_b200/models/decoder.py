@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import torch
 
+from ..kernels import api as K
 from ..parts.base import CacheView, Product, Runtime, StepContext
 from ..parts.registry import BLOCKS, EMBEDDINGS, HEADS, NORMS
 from ..parts.spec import ModelSpec, ParamSpec
@@ -28,10 +29,10 @@ class DecoderModel:
         for i, e in enumerate(spec.order):
             if e.cache_of is None:
                 self.entry_cache.append(len(self.cache_needs))
-                self.cache_needs.append(self.blocks[e.layer].mixer.cache_need())
+                self.cache_needs.append(self.blocks[e.layer].cache_need())
             else:
                 owner = self.entry_cache[e.cache_of]
-                mine, theirs = self.blocks[e.layer].mixer.cache_need(), self.cache_needs[owner]
+                mine, theirs = self.blocks[e.layer].cache_need(), self.cache_needs[owner]
                 if mine != theirs:
                     raise ValueError(
                         f"run entry {i} reads the cache of entry {e.cache_of}, but their needs differ: "
@@ -88,7 +89,13 @@ class DecoderModel:
     # ---- forward --------------------------------------------------------------------------------
     def forward(self, ctx: StepContext, caches: list[CacheView | None], rows: torch.Tensor | None,
                 observer=None) -> torch.Tensor | None:
-        """Run the batch; return logits [R, V] float32 at ``rows`` (None: no logits wanted)."""
+        """Run the batch; return logits [R, V] float32 at ``rows`` (None: no logits wanted).
+
+        ``observer(i, residual, pending)`` is called after every run entry i with the float32
+        residual stream [T, H] and the entry's output that is not yet added to it (a Product), and
+        once more as ``observer("final", residual, None)`` with everything added: the reference's
+        layer hook (mini_hisparse/model.py:171-172, 202-203) for this engine's fused residual adds.
+        The tensors are the step's own buffers: copy what is to be kept."""
         if not self.loaded:
             raise RuntimeError("the model has no weights yet")
         x = self.embedding.forward(ctx)
@@ -98,6 +105,12 @@ class DecoderModel:
             pending = self.blocks[entry.layer].forward(x, pending, ctx, view)
             if observer is not None:
                 observer(i, x, pending)
+        if observer is not None and pending is not None:
+            # the hook's last call sees the finished residual stream (the head needs only its wanted
+            # rows and never adds the last output into every row)
+            K.residual_add(x, pending.tensor, nsplit=pending.nsplit, split_stride=pending.split_stride)
+            observer("final", x, None)
+            pending = None
         if rows is None or rows.numel() == 0:
             return None
         h = self.final_norm.forward(x, ctx, delta=pending, rows=rows, name="h_rows")

@@ -27,8 +27,7 @@ def qwen2_spec(cfg: Qwen2Config) -> ModelSpec:
     )
     ff = PartSpec.make("swiglu", hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size)
     layers = tuple(
-        LayerSpec(prefix=f"model.layers.{i}", block="pre_norm", mixer=mixer, mixer_norm=norm,
-                  feed_forward=ff, ff_norm=norm)
+        LayerSpec.pre_norm(f"model.layers.{i}", mixer=mixer, mixer_norm=norm, feed_forward=ff, ff_norm=norm)
         for i in range(cfg.num_hidden_layers)
     )
     return ModelSpec(

@@ -1,6 +1,7 @@
 """Parts that layers are put together from.  Importing the package registers the built-in kinds."""
 from . import attention, block, embedding, feed_forward, norm, position  # noqa: F401
-from .base import CacheView, FeedForward, Mixer, Norm, Part, Product, Runtime, Segment, StepContext, Workspace
+from .base import (Block, CacheView, FeedForward, Mixer, Norm, Part, Product, Runtime, Segment, StepContext,
+                   StepPlanner, Workspace)
 from .registry import (
     BLOCKS,
     EMBEDDINGS,
@@ -15,4 +16,5 @@ from .registry import (
     register_norm,
     register_position,
 )
-from .spec import CacheNeed, LayerSpec, ModelSpec, PagedKVNeed, ParamSpec, PartSpec, RunEntry, StateNeed
+from .spec import (CacheNeed, LayerSpec, ModelSpec, PagedKVNeed, PagedNeed, ParamSpec, PartSpec, RunEntry,
+                   StateNeed)

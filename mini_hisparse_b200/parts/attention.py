@@ -7,7 +7,7 @@ import numpy as np
 import torch
 
 from ..kernels import api as K
-from .base import CacheView, Mixer, Product, StepContext
+from .base import CacheView, Mixer, Product, StepContext, StepPlanner
 from .registry import POSITIONS, register_mixer
 from .spec import PagedKVNeed, ParamSpec, PartSpec
 
@@ -21,6 +21,17 @@ MAX_BIG_SPLITS = 8       # key splits of a long portion's tile (tcgen05 kernel o
 BIG_SPLIT_ITEMS = 1024   # long-portion tiles are only split while their items stay below this
 BIG_SPLIT_ROWS = 4096    # ... and their partial rows (tokens x splits) below this
 MIN_KEYS_PER_BIG_SPLIT = 512
+
+
+@dataclass(frozen=True)
+class AttentionShape:
+    """What the plan of a step's attention depends on: head counts, the window, and the query rows
+    per tile that the kernel for long portions takes (a kernel's choice, made by the mixer)."""
+
+    q_heads: int
+    kv_heads: int
+    window: int | None = None
+    tile_rows: int = ROW_TILE
 
 
 @dataclass
@@ -45,7 +56,7 @@ def _tiling(groups: int, rows: int):
     return [(h, min(rows, groups - h)) for h in range(0, groups, rows)], 1
 
 
-def plan_attention(need: PagedKVNeed, segments, T: int, sm_count: int = 148,
+def plan_attention(need: AttentionShape, segments, T: int, sm_count: int = 148,
                    fixed_nsplit: int | None = None) -> AttentionPlan:
     """Cut the step's attention into items.
 
@@ -156,7 +167,7 @@ def plan_attention(need: PagedKVNeed, segments, T: int, sm_count: int = 148,
     return AttentionPlan(arr, n_small, len(big_items), tok_part_row, tok_nsplit, part_rows, big_split)
 
 
-def plan_decode(need: PagedKVNeed, starts: np.ndarray, nsplit: int) -> AttentionPlan:
+def plan_decode(need: AttentionShape, starts: np.ndarray, nsplit: int) -> AttentionPlan:
     """The plan of a batch of single decoded tokens (token i belongs to segment i and sits at
     position starts[i]) with exactly ``nsplit`` key splits each: what plan_attention gives for such
     a batch with fixed_nsplit, computed with arrays instead of loops."""
@@ -191,7 +202,7 @@ def plan_decode(need: PagedKVNeed, starts: np.ndarray, nsplit: int) -> Attention
                          (seg * nsplit).astype(np.int32), np.full(B, nsplit, np.int32), B * nsplit)
 
 
-def plan_capacity(need: PagedKVNeed, max_tokens: int, max_segments: int,
+def plan_capacity(need: AttentionShape, max_tokens: int, max_segments: int,
                   fixed_nsplit: int | None = None) -> tuple[int, int]:
     """Upper bounds (items, partial rows) for a step of at most max_tokens / max_segments."""
     groups = need.q_heads // need.kv_heads
@@ -203,6 +214,43 @@ def plan_capacity(need: PagedKVNeed, max_tokens: int, max_segments: int,
     short_tokens = min(max_tokens, max_segments * SPLIT_MAX_TOKENS)
     small = (short_tokens // small_tpt + max_segments) * len(small_chunks) * splits
     return big + small, short_tokens * splits + BIG_SPLIT_ROWS
+
+
+class AttentionPlanner(StepPlanner):
+    """The plan of grouped-query attention for the step function: work items, and for every token
+    the first of its partial rows and the number of its key splits."""
+
+    def __init__(self, shape: AttentionShape, sm_count: int):
+        self.shape, self.sm_count = shape, sm_count
+        groups = shape.q_heads // shape.kv_heads
+        self.chunks = 1 if groups <= ROW_TILE else -(-groups // ROW_TILE)
+
+    def capacity(self, max_tokens, max_segments, fixed=None):
+        if fixed is not None:            # a captured graph of single tokens: exactly these many
+            return {"items": max_segments * fixed * self.chunks * ITEM_INTS, "tok_part_row": max_tokens,
+                    "tok_nsplit": max_tokens}
+        items, _ = plan_capacity(self.shape, max_tokens, max_segments)
+        return {"items": items * ITEM_INTS, "tok_part_row": max_tokens, "tok_nsplit": max_tokens}
+
+    @staticmethod
+    def _out(plan: AttentionPlan):
+        arrays = {"items": plan.items.reshape(-1), "tok_part_row": plan.tok_part_row, "tok_nsplit": plan.tok_nsplit}
+        facts = {"n_small": plan.n_small, "n_big": plan.n_big, "part_rows_cap": plan.part_rows,
+                 "any_split": bool(plan.part_rows), "big_split": plan.big_split}
+        return arrays, facts
+
+    def plan(self, segments, T, fixed=None):
+        return self._out(plan_attention(self.shape, segments, T, self.sm_count, fixed_nsplit=fixed))
+
+    def decode_fixed(self, segments_count, max_positions):
+        """Key splits per decoded token for a batch of B with at most ``max_positions`` cached keys: as
+        many CTAs as are resident at once (two per SM), never more, so that no CTA waits for a
+        second wave, and no split shorter than MIN_KEYS_PER_SPLIT keys."""
+        ctas = segments_count * self.shape.kv_heads * self.chunks
+        return max(1, min(MAX_SPLITS, (2 * self.sm_count) // ctas, max_positions // MIN_KEYS_PER_SPLIT))
+
+    def plan_decode(self, starts, fixed):
+        return self._out(plan_decode(self.shape, starts, fixed))
 
 
 @register_mixer("gq_attention")
@@ -236,26 +284,38 @@ class GQAttention(Mixer):
         """bfloat16 and a head size the mma kernel is built for; else the CUDA-core kernel."""
         return (self.rt is not None and self.rt.dtype == torch.bfloat16 and self.d in K.MMA_HEAD_DIMS)
 
-    @property
-    def big_tile_rows(self) -> int:
-        """Query rows per tile for long portions: 128 for the tcgen05 kernel, 64 for the mma.sync
-        kernels, 16 for the CUDA-core kernel."""
+    def kernel_family(self, page_size: int) -> str:
+        """Which attention kernels serve pages of ``page_size`` keys: "tc" (TMA-fed 16-row tiles for
+        short segments, tcgen05 128-row tiles for long portions: bfloat16, head size 64 or 128,
+        pages that divide 64), "mma" (mma.sync with 16- and 64-row tiles: bfloat16, head size 32,
+        64, 96 or 128, any page size) or "simt" (CUDA cores: everything else)."""
         if not self.tensor_core_attention:
-            return ROW_TILE
-        return 128 if self.d in (64, 128) else 64
+            return "simt"
+        return "tc" if K.attention_tma_supports(self.d, page_size) else "mma"
+
+    def big_tile_rows(self, page_size: int) -> int:
+        """Query rows per tile for long portions."""
+        return {"tc": 128, "mma": 64, "simt": ROW_TILE}[self.kernel_family(page_size)]
 
     def kernel_modules(self):
         """attention_simt holds the CUDA-core kernel and the merge of key splits; the tensor-core
-        kernels come in for the head sizes they are built for."""
+        kernels come in for the head sizes they are built for (which of them runs depends on the
+        page size, which the cache brings)."""
         if not self.tensor_core_attention:
             return ("attention_simt",)
-        if self.big_tile_rows == 128:
+        if self.d in (64, 128):
             return ("attention_simt", "attention_mma", "attention_tma", "attention_tc")
         return ("attention_simt", "attention_mma")
 
     def cache_need(self):
-        return PagedKVNeed(kv_heads=self.nkv, head_dim=self.d, q_heads=self.nq, window=self.window,
-                           tile_rows=self.big_tile_rows)
+        return PagedKVNeed(kv_heads=self.nkv, head_dim=self.d, window=self.window)
+
+    def plan_key(self):
+        return ("gq_attention", self.nq, self.nkv, self.d, self.window)
+
+    def planner(self, page_size: int, sm_count: int):
+        return AttentionPlanner(AttentionShape(self.nq, self.nkv, self.window, self.big_tile_rows(page_size)),
+                                sm_count)
 
     def parameters(self):
         q, kv = self.nq * self.d, self.nkv * self.d
@@ -293,7 +353,9 @@ class GQAttention(Mixer):
             K.rope_append(
                 qkv.tensor, self.qkv_bias_vec, ctx.positions, ctx.tok_seg, meta["block_table"],
                 self.position.inv_freq, q, cache.storage, nq=self.nq, nkv=self.nkv, d=self.d,
-                page_size=cache.page_size, write_kv=cache.writable, rotate=self.position.rotates,
+                page_size=cache.page_size, write_kv=cache.writable,
+                rotary_dim=int(getattr(self.position, "rotary_dim", 0) or 0),
+                interleaved=bool(getattr(self.position, "interleaved", False)),
                 nsplit=qkv.nsplit, split_stride=qkv.split_stride, status=ctx.status,
             )
         attn = ws.get("attn", (T, self.nq * self.d), rt.dtype)
@@ -305,8 +367,9 @@ class GQAttention(Mixer):
         args = (q, cache.storage, attn, part_acc, part_ml)
         tail = (ctx.positions, meta["block_table"], meta["tok_part_row"])
         n_small, n_big = meta["n_small"], meta["n_big"]
-        if self.tensor_core_attention:
-            tma = K.attention_tma_supports(self.d, cache.page_size)
+        family = self.kernel_family(cache.page_size)
+        if family != "simt":
+            tma = family == "tc"
             kernel = K.attention_tma if tma else K.attention_mma
             extra = {"status": ctx.status} if tma else {}
             def short_segments():
@@ -320,11 +383,7 @@ class GQAttention(Mixer):
 
             def long_portions():
                 big_items = meta["items"][n_small * ITEM_INTS:]
-                if self.big_tile_rows == 128:
-                    if not tma:
-                        raise K.KernelError(
-                            f"attention: pages of {cache.page_size} keys do not divide 64, which the "
-                            f"tensor-core kernels for head_dim {self.d} need")
+                if tma:
                     K.attention_tc(q, cache.storage, attn, big_items, n_big, ctx.positions, meta["block_table"],
                                    part_acc=part_acc, part_ml=part_ml, tok_part_row=meta["tok_part_row"],
                                    status=ctx.status, **common)
@@ -356,7 +415,7 @@ class GQAttention(Mixer):
                     long_portions()
         elif n_small + n_big:
             K.attention_simt(*args, meta["items"], n_small + n_big, n_small + n_big, *tail, **common)
-        if meta["any_split"] and not self.tensor_core_attention:
+        if meta["any_split"] and family == "simt":
             K.attention_combine(part_acc, part_ml, meta["tok_part_row"], meta["tok_nsplit"], attn,
                                 nq=self.nq, d=self.d)
         return rt.linear(attn, self.o_weight, ws, "mix_out")

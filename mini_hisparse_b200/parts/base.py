@@ -11,6 +11,10 @@ Interfaces, in short:
 * ``Mixer.cache_need()`` -> CacheNeed | None;
   ``Mixer.forward(h, ctx, cache)`` -> Product [T, H]; ``cache`` is a view of the entry's cache
   (``cache.writable`` is False when the entry only reads another entry's cache).
+* ``Mixer.planner(page_size, sm_count)`` -> StepPlanner | None: the host-side plan of the mixer's
+  work for one step (index arrays its kernels read).  The step function packs what the planner
+  returns beside the block tables and hands the device views back in ``cache.meta``; it does not
+  know what the arrays mean.
 * ``FeedForward.forward(h, ctx)`` -> Product [T, H].
 * ``Block.forward(x, pending, ctx, cache)`` -> pending: the block adds ``pending`` (the previous
   block's last output) into x where it normalises, and returns its own last output unadded.
@@ -20,6 +24,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any
 
+import numpy as np
 import torch
 
 from ..kernels import api as K
@@ -57,6 +62,7 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._buffers: dict[str, torch.Tensor] = {}
+        self._zeroed: set[str] = set()
         self.frozen = False
 
     def get(self, name: str, shape, dtype) -> torch.Tensor:
@@ -74,7 +80,8 @@ class Workspace:
         return buf[:nbytes].view(dtype).view(*shape)
 
     def get_zeroed(self, name: str, shape, dtype) -> torch.Tensor:
-        """A buffer that is zero when first handed out; its users leave it zero."""
+        """A buffer that is zero when first handed out; its users leave it zero (counters that
+        reset themselves).  zero_self_resetting() puts all of them back after a fault."""
         n = 1
         for s in shape:
             n *= int(s)
@@ -83,7 +90,12 @@ class Workspace:
             if self.frozen:
                 raise RuntimeError(f"workspace buffer {name!r} would grow after it was frozen")
             self._buffers[name] = torch.zeros(max(n * dtype.itemsize, 256), dtype=torch.uint8, device=self.device)
+        self._zeroed.add(name)
         return self.get(name, shape, dtype)
+
+    def zero_self_resetting(self) -> None:
+        for name in self._zeroed:
+            self._buffers[name].zero_()
 
     def nbytes(self) -> int:
         return sum(b.numel() for b in self._buffers.values())
@@ -126,7 +138,8 @@ class Runtime:
     def qkv_rope_append(self, x, weight, bias, ctx, position, block_table, q_out, cache_storage, *,
                         nq: int, nkv: int, d: int, page_size: int, write_kv: bool) -> bool:
         """The stacked q/k/v product with bias, rotation and the append to the cache in ONE kernel,
-        if this runtime has one for these sizes: then q_out and the cache are written and True is
+        if this runtime has one for these sizes and this rotation (``position``: an object with
+        rotary_dim, inv_freq and interleaved): then q_out and the cache are written and True is
         returned.  False: the caller runs the product and the rotary kernel one after the other."""
         return False
 
@@ -205,9 +218,54 @@ class Part:
         return total
 
 
+class StepPlanner:
+    """The host-side plan of a paged mixer's work for one step.
+
+    A planner turns the step's segments into int32 index arrays (work items and the like) that
+    the mixer's kernels read, and host facts (counts that size the launches).  The step function
+    packs the arrays into the step's single host-to-device copy beside the block tables and gives
+    the mixer their device views as ``cache.meta[name]``; facts arrive as ``cache.meta[name]`` too.
+    Mixers of one page group whose ``plan_key()`` compare equal share one planner and one plan.
+
+    ``fixed`` is what ``decode_fixed`` returned when a CUDA graph of single-token segments was
+    captured: with it, the arrays' sizes and the facts must depend on the number of segments
+    only, since a replayed graph launches what was captured.
+    """
+
+    def capacity(self, max_tokens: int, max_segments: int, fixed=None) -> dict[str, int]:
+        """Upper bounds of the arrays' lengths (int32 words) for a step of that size."""
+        raise NotImplementedError
+
+    def plan(self, segments: list["Segment"], T: int, fixed=None) -> tuple[dict[str, np.ndarray], dict]:
+        """(arrays, facts) of one step; every array no longer than its capacity."""
+        raise NotImplementedError
+
+    def decode_fixed(self, segments_count: int, max_positions: int):
+        """What to hold constant in a captured graph of ``segments_count`` single-token segments
+        with at most ``max_positions`` cached positions each (None: nothing)."""
+        return None
+
+    def plan_decode(self, starts: np.ndarray, fixed) -> tuple[dict[str, np.ndarray], dict]:
+        """plan() for single-token segments at positions ``starts`` (segment i = token i = slot
+        row i), as a fast path without per-token loops.  Default: the general plan."""
+        segments = [Segment(i, i, int(p), 1, i) for i, p in enumerate(starts)]
+        return self.plan(segments, len(segments), fixed)
+
+
 class Mixer(Part):
     def cache_need(self) -> CacheNeed | None:
         return None
+
+    def plan_key(self):
+        """Mixers of one page group with equal keys share a planner (None: no plan needed)."""
+        return None
+
+    def planner(self, page_size: int, sm_count: int) -> StepPlanner | None:
+        return None
+
+    def check_cache(self, page_size: int) -> None:
+        """Raise ValueError if this mixer cannot work over pages of ``page_size`` positions: called
+        when a model is paired with a cache, so that a step never finds out half-way."""
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: CacheView | None) -> Product:
         raise NotImplementedError
@@ -221,6 +279,43 @@ class FeedForward(Part):
         raise NotImplementedError
 
     graph_safe = True
+
+
+class Block:
+    """Base of block arrangements: how a layer's parts are wired to the residual stream.
+
+    A subclass builds its parts from ``spec.part(role)`` with the registries it wants, lists them
+    in ``parts()`` (role -> part, the roles of its LayerSpec), and names the ONE part that owns
+    per-request memory as ``self.mixer`` (or overrides the three methods below).
+    ``forward(x, pending, ctx, cache) -> pending``: x is the float32 residual [T, H]; ``pending``
+    is the previous block's last output, not yet added to x (None for the first block).
+    """
+
+    mixer: "Mixer | None" = None
+
+    def parts(self) -> dict[str, Part]:
+        raise NotImplementedError
+
+    def cache_need(self) -> CacheNeed | None:
+        return self.mixer.cache_need() if self.mixer is not None else None
+
+    def plan_key(self):
+        return self.mixer.plan_key() if self.mixer is not None else None
+
+    def planner(self, page_size: int, sm_count: int) -> StepPlanner | None:
+        return self.mixer.planner(page_size, sm_count) if self.mixer is not None else None
+
+    def check_cache(self, page_size: int) -> None:
+        if self.mixer is not None:
+            self.mixer.check_cache(page_size)
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", True) for p in self.parts().values())
+
+    def forward(self, x: torch.Tensor, pending: Product | None, ctx: StepContext,
+                cache: CacheView | None) -> Product:
+        raise NotImplementedError
 
 
 class Norm(Part):

@@ -57,26 +57,46 @@ class ParamSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One block: its arrangement and the four parts it is made of.
+    """One block: its arrangement and the parts it is made of, by role.
 
-    ``names`` maps each part to its sub-prefix in the checkpoint, e.g. mixer -> "self_attn".
+    ``parts`` maps a role of the arrangement ("mixer", "mixer_norm", "feed_forward", "ff_norm" for
+    the pre-norm block; another arrangement names its own roles and may have more or fewer) to the
+    part that fills it; ``names`` maps each role to its sub-prefix in the checkpoint, e.g.
+    mixer -> "self_attn".  A role without a name uses the role itself as sub-prefix.
     """
 
     prefix: str
     block: str
-    mixer: PartSpec
-    mixer_norm: PartSpec
-    feed_forward: PartSpec
-    ff_norm: PartSpec
-    names: tuple[tuple[str, str], ...] = (
-        ("mixer", "self_attn"),
-        ("mixer_norm", "input_layernorm"),
-        ("feed_forward", "mlp"),
-        ("ff_norm", "post_attention_layernorm"),
-    )
+    parts: tuple[tuple[str, PartSpec], ...]
+    names: tuple[tuple[str, str], ...] = ()
 
-    def name_of(self, part: str) -> str:
-        return dict(self.names)[part]
+    @staticmethod
+    def make(prefix: str, block: str, parts: Mapping[str, PartSpec],
+             names: Mapping[str, str] | None = None) -> "LayerSpec":
+        return LayerSpec(prefix, block, tuple(parts.items()), tuple((names or {}).items()))
+
+    @staticmethod
+    def pre_norm(prefix: str, *, mixer: PartSpec, mixer_norm: PartSpec, feed_forward: PartSpec,
+                 ff_norm: PartSpec, names: Mapping[str, str] | None = None) -> "LayerSpec":
+        """The pre-norm block with Hugging Face's sub-prefixes unless ``names`` gives others."""
+        default = {"mixer": "self_attn", "mixer_norm": "input_layernorm", "feed_forward": "mlp",
+                   "ff_norm": "post_attention_layernorm"}
+        return LayerSpec.make(prefix, "pre_norm",
+                              {"mixer_norm": mixer_norm, "mixer": mixer, "ff_norm": ff_norm,
+                               "feed_forward": feed_forward}, {**default, **(names or {})})
+
+    def part(self, role: str) -> PartSpec:
+        for r, spec in self.parts:
+            if r == role:
+                return spec
+        known = ", ".join(r for r, _ in self.parts)
+        raise KeyError(f"layer {self.prefix!r} has no part in the role {role!r}; it has: {known}")
+
+    def roles(self) -> tuple[str, ...]:
+        return tuple(r for r, _ in self.parts)
+
+    def name_of(self, role: str) -> str:
+        return dict(self.names).get(role, role)
 
 
 @dataclass(frozen=True)
@@ -126,20 +146,34 @@ class CacheNeed:
 
 
 @dataclass(frozen=True)
-class PagedKVNeed(CacheNeed):
-    """Keys and values of every cached position, in pages.
+class PagedNeed(CacheNeed):
+    """Per-position memory in pages.  A subclass says what one page looks like.
 
-    ``window``: None keeps all keys; a number keeps the last ``window`` keys, and pages that the
-    window has passed are given back.  Layers whose needs compare equal share one group: one
-    pool, one block table per request.
+    ``window``: None keeps every position; a number keeps the last ``window`` positions, and pages
+    that the window has passed are given back.  Entries whose needs compare equal share one
+    group: one pool, one allocator, one block table per request.  So a need holds what decides
+    the memory's geometry and lifetime and nothing else: how a mixer's kernels tile their work is
+    the mixer's business (its planner), not a reason for a pool of its own.
     """
 
-    kv_heads: int
-    head_dim: int
-    q_heads: int
-    window: int | None = None
-    tile_rows: int = 16      # query rows per attention tile for long portions (a kernel's choice)
     kind: str = field(default="pages", init=False)
+    window = None          # a subclass makes this a field if its mixer can have a window
+
+    def page_shape(self, page_size: int) -> tuple[int, ...]:
+        """Shape of one page of one cache entry for pages of ``page_size`` positions."""
+        raise NotImplementedError
+
+
+@dataclass(frozen=True)
+class PagedKVNeed(PagedNeed):
+    """Keys and values of every cached position: a page is [2 (K, V), kv_heads, page_size, head_dim]."""
+
+    kv_heads: int = 1
+    head_dim: int = 16
+    window: int | None = None
+
+    def page_shape(self, page_size: int) -> tuple[int, ...]:
+        return (2, self.kv_heads, page_size, self.head_dim)
 
 
 @dataclass(frozen=True)

@@ -10,6 +10,13 @@ oracle rests on the reference's code and not only on its formulas.
 
 Everything runs in the dtype it is given (float32 or float64 on the CPU; the
 GPU tests also run it in float32 on the device at large sizes).
+
+``act``: the functions that end a part take an optional dtype to which that part's
+output is rounded (and widened again), so that a float32 run can stand in for a
+model whose activations between the parts are bfloat16 while every sum stays
+float32: normalised rows, rotated q and k, v, the attention output and the gated
+feed-forward activation.  The reference rounds at the same places when its model
+dtype is bfloat16 (model.py:51, 138-153, 179, 71); with ``act=None`` nothing is rounded.
 """
 from __future__ import annotations
 
@@ -83,16 +90,20 @@ def load_folder(folder, dtype=torch.float32, device="cpu"):
 # parts
 # ---------------------------------------------------------------------------
 
+def _rounded(t: torch.Tensor, act) -> torch.Tensor:
+    return t if act is None else t.to(act).to(t.dtype)
+
+
 def embedding(tokens: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     """model.py:166 — plain row lookup, no scaling."""
     return table[tokens]
 
 
-def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, act=None) -> torch.Tensor:
     """model.py:49-51 — x * rsqrt(mean(x^2) + eps), then times the weight."""
     xf = x.float() if x.dtype in (torch.float16, torch.bfloat16) else x
     n = xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)
-    return n.to(x.dtype) * weight
+    return _rounded(n.to(x.dtype) * weight, act)
 
 
 def linear(x, weight, bias=None):
@@ -137,13 +148,13 @@ def causal_attention(q, k, v, window: int | None = None) -> torch.Tensor:
     return out.to(q.dtype)
 
 
-def swiglu(x, gate_w, up_w, down_w):
+def swiglu(x, gate_w, up_w, down_w, act=None):
     """model.py:70-71 — down(silu(gate(x)) * up(x))."""
     g = linear(x, gate_w)
-    return linear(g * torch.sigmoid(g) * linear(x, up_w), down_w)
+    return linear(_rounded(g * torch.sigmoid(g) * linear(x, up_w), act), down_w)
 
 
-def attention_block(cfg, w, prefix, x, positions):
+def attention_block(cfg, w, prefix, x, positions, act=None):
     """model.py:135-153 (project + rotate) and 173-179 (attend) and o_proj of 157."""
     T = x.shape[0]
     q = linear(x, w[prefix + "q_proj.weight"], w[prefix + "q_proj.bias"])
@@ -153,24 +164,24 @@ def attention_block(cfg, w, prefix, x, positions):
     k = k.view(T, cfg.num_key_value_heads, cfg.head_dim)
     v = v.view(T, cfg.num_key_value_heads, cfg.head_dim)
     cosine, sine = rope_tables(positions, cfg.head_dim, cfg.rope_theta, x.dtype)
-    q, k = rotate(q, cosine, sine), rotate(k, cosine, sine)
-    a = causal_attention(q, k, v)
+    q, k, v = _rounded(rotate(q, cosine, sine), act), _rounded(rotate(k, cosine, sine), act), _rounded(v, act)
+    a = _rounded(causal_attention(q, k, v), act)
     return linear(a.reshape(T, -1), w[prefix + "o_proj.weight"])
 
 
-def decoder_layer(cfg, w, index, x, positions):
+def decoder_layer(cfg, w, index, x, positions, act=None):
     """model.py:155-158 — pre-norm residual block."""
     p = f"model.layers.{index}."
-    h = rms_norm(x, w[p + "input_layernorm.weight"], cfg.rms_norm_eps)
-    x = x + attention_block(cfg, w, p + "self_attn.", h, positions)
-    h = rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps)
+    h = rms_norm(x, w[p + "input_layernorm.weight"], cfg.rms_norm_eps, act)
+    x = x + attention_block(cfg, w, p + "self_attn.", h, positions, act)
+    h = rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps, act)
     return x + swiglu(
-        h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"]
+        h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"], act
     )
 
 
 @torch.inference_mode()
-def forward_logits(cfg, w, tokens) -> torch.Tensor:
+def forward_logits(cfg, w, tokens, act=None) -> torch.Tensor:
     """Logits at EVERY position of one whole sequence, float32 [T, V]
     (model.py:160-181 returns the last row only; the rows are independent of that choice)."""
     table = w["model.embed_tokens.weight"]
@@ -178,8 +189,8 @@ def forward_logits(cfg, w, tokens) -> torch.Tensor:
     positions = torch.arange(len(tokens), device=table.device)
     x = embedding(tokens, table)
     for i in range(cfg.num_hidden_layers):
-        x = decoder_layer(cfg, w, i, x, positions)
-    x = rms_norm(x, w["model.norm.weight"], cfg.rms_norm_eps)
+        x = decoder_layer(cfg, w, i, x, positions, act)
+    x = rms_norm(x, w["model.norm.weight"], cfg.rms_norm_eps, act)
     return linear(x, w["lm_head.weight"]).float()
 
 

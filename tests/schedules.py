@@ -14,15 +14,31 @@ def whole(requests: dict[str, list[int]]):
             for rid, toks in requests.items()]
 
 
-def tail_one_by_one(requests, tail=32):
-    """Most of it in one step, the last ``tail`` tokens one by one."""
+def tail_one_by_one(requests, tail=32, together=3):
+    """Most of it in one step, the last ``tail`` tokens one by one.  ``together`` requests at a
+    time: each gets most of its prompt in a step of its own, then their last tokens are decoded
+    side by side, one token of each per step (the batch shrinks as the shorter tails end)."""
     steps = []
-    for rid, toks in requests.items():
-        head = max(0, len(toks) - tail)
-        if head:
-            steps.append(([{"id": rid, "tokens": toks[:head], "want": list(range(head))}], []))
-        for i in range(head, len(toks)):
-            steps.append(([{"id": rid, "tokens": [toks[i]], "want": [0]}], [rid] if i == len(toks) - 1 else []))
+    names = list(requests)
+    for g in range(0, len(names), together):
+        group = names[g:g + together]
+        done = {}
+        for rid in group:
+            toks = requests[rid]
+            head = max(0, len(toks) - tail)
+            done[rid] = head
+            if head:
+                steps.append(([{"id": rid, "tokens": toks[:head], "want": list(range(head))}], []))
+        while done:
+            entries, end = [], []
+            for rid in list(done):
+                toks, i = requests[rid], done[rid]
+                entries.append({"id": rid, "tokens": [toks[i]], "want": [0]})
+                done[rid] = i + 1
+                if i + 1 == len(toks):
+                    end.append(rid)
+                    del done[rid]
+            steps.append((entries, end))
     return steps
 
 

@@ -7,7 +7,7 @@ import pytest
 from mini_hisparse_b200.parts.attention import (ITEM_INTS, MAX_SPLITS, ROW_TILE, plan_attention, plan_capacity,
                                                 plan_decode)
 from mini_hisparse_b200.parts.base import Segment
-from mini_hisparse_b200.parts.spec import PagedKVNeed
+from mini_hisparse_b200.parts.attention import AttentionShape
 
 
 def segments_of(specs):
@@ -72,9 +72,9 @@ CASES = [
 
 @pytest.mark.parametrize("specs", CASES)
 @pytest.mark.parametrize("need", [
-    PagedKVNeed(4, 128, 28, None, tile_rows=128), PagedKVNeed(8, 128, 40, None, tile_rows=128),
-    PagedKVNeed(1, 32, 3, None, tile_rows=64), PagedKVNeed(2, 16, 4, None, tile_rows=16),
-    PagedKVNeed(2, 128, 512, None, tile_rows=128), PagedKVNeed(4, 64, 4, 100, tile_rows=128),
+    AttentionShape(28, 4, None, 128), AttentionShape(40, 8, None, 128),
+    AttentionShape(3, 1, None, 64), AttentionShape(4, 2, None, 16),
+    AttentionShape(512, 2, None, 128), AttentionShape(4, 4, 100, 128),
 ])
 def test_every_key_is_covered_once(need, specs):
     segments, T = segments_of(specs)
@@ -85,7 +85,7 @@ def test_every_key_is_covered_once(need, specs):
 
 
 def test_long_tiles_are_split_only_when_they_are_fewer_than_sms():
-    need = PagedKVNeed(4, 128, 28, None, tile_rows=128)
+    need = AttentionShape(28, 4, None, 128)
     few = plan_attention(need, segments_of([(16000, 100)])[0], 100, 148)
     assert few.big_split and (few.items[few.n_small:, 7] >= 0).all()
     many = plan_attention(need, segments_of([(0, 2048)])[0], 2048, 148)
@@ -95,7 +95,7 @@ def test_long_tiles_are_split_only_when_they_are_fewer_than_sms():
 
 
 def test_a_long_history_beside_short_ones_gets_more_parts():
-    need = PagedKVNeed(8, 128, 40, None, tile_rows=128)
+    need = AttentionShape(40, 8, None, 128)
     specs = [(4000, 1)] + [(200, 1)] * 29
     plan = plan_attention(need, segments_of(specs)[0], 30, 148)
     assert plan.tok_nsplit[0] >= 2 and (plan.tok_nsplit[1:] <= 1).all()
@@ -104,7 +104,7 @@ def test_a_long_history_beside_short_ones_gets_more_parts():
 
 @pytest.mark.parametrize("nsplit", [1, 3, 16])
 def test_decode_plan_for_a_captured_graph(nsplit):
-    need = PagedKVNeed(4, 128, 28, None, tile_rows=128)
+    need = AttentionShape(28, 4, None, 128)
     starts = np.array([4000, 17, 0, 999], np.int64)
     plan = plan_decode(need, starts, nsplit)
     assert plan.items.shape == (4 * nsplit, ITEM_INTS)

@@ -10,7 +10,7 @@ from mini_hisparse_b200.parts.spec import PagedKVNeed, StateNeed
 
 
 def manager(num_pages=12, page_size=4, max_requests=4, needs=None, width=None):
-    needs = needs or [PagedKVNeed(kv_heads=2, head_dim=16, q_heads=4)] * 3
+    needs = needs or [PagedKVNeed(kv_heads=2, head_dim=16)] * 3
     cfg = CacheConfig(num_pages=num_pages, page_size=page_size, max_requests=max_requests,
                       max_pages_per_request=width, dtype=torch.float32, device="cpu",
                       allocate_storage=False)
@@ -51,8 +51,8 @@ def test_reservations_hold_pages_for_their_owner():
 
 
 def test_groups_by_need_and_state_slots():
-    full = PagedKVNeed(kv_heads=2, head_dim=16, q_heads=4)
-    win = PagedKVNeed(kv_heads=2, head_dim=16, q_heads=4, window=8)
+    full = PagedKVNeed(kv_heads=2, head_dim=16)
+    win = PagedKVNeed(kv_heads=2, head_dim=16, window=8)
     state = StateNeed(shape=(5,), dtype="float32")
     m = manager(needs=[full, win, full, state, None, win])
     assert len(m.page_groups) == 2 and len(m.state_groups) == 1
@@ -62,7 +62,7 @@ def test_groups_by_need_and_state_slots():
 
 
 def test_window_pages_come_back_and_are_used_again():
-    win = PagedKVNeed(kv_heads=1, head_dim=16, q_heads=1, window=8)
+    win = PagedKVNeed(kv_heads=1, head_dim=16, window=8)
     m = manager(num_pages=5, page_size=4, needs=[win], width=16)
     m.open("a")
     held = []
@@ -96,8 +96,8 @@ def test_open_failure_changes_nothing():
 
 
 def test_ensure_is_all_or_nothing_across_groups():
-    full = PagedKVNeed(kv_heads=2, head_dim=16, q_heads=4)
-    other = PagedKVNeed(kv_heads=1, head_dim=32, q_heads=4)
+    full = PagedKVNeed(kv_heads=2, head_dim=16)
+    other = PagedKVNeed(kv_heads=1, head_dim=32)
     m = manager(num_pages=4, page_size=4, needs=[full, other])
     m.open("a")
     m.open("b")
@@ -113,8 +113,8 @@ def test_ensure_is_all_or_nothing_across_groups():
 @pytest.mark.parametrize("seed", range(6))
 def test_random_orders_lose_nothing(seed):
     rng = random.Random(seed)
-    full = PagedKVNeed(kv_heads=2, head_dim=16, q_heads=4)
-    win = PagedKVNeed(kv_heads=2, head_dim=16, q_heads=4, window=6)
+    full = PagedKVNeed(kv_heads=2, head_dim=16)
+    win = PagedKVNeed(kv_heads=2, head_dim=16, window=6)
     m = manager(num_pages=10, page_size=4, max_requests=3, needs=[full, win, full, StateNeed((3,))], width=64)
     live, names = {}, iter(range(10_000))
     for _ in range(600):

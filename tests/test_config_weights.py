@@ -47,7 +47,7 @@ def test_registry_names_the_model():
     assert "Qwen2ForCausalLM" in known_architectures()
     cfg, spec = resolve(TINY_B)
     assert spec.architecture == "Qwen2ForCausalLM" and len(spec.layers) == 3 and len(spec.order) == 3
-    assert spec.layers[0].mixer["q_heads"] == 3 and spec.layers[0].mixer["kv_heads"] == 1
+    assert spec.layers[0].part("mixer")["q_heads"] == 3 and spec.layers[0].part("mixer")["kv_heads"] == 1
     with pytest.raises(KeyError, match="Qwen2ForCausalLM"):
         architecture_of({"architectures": ["MysteryForCausalLM"]})
 
@@ -100,3 +100,36 @@ def test_tied_head_needs_no_lm_head_tensor():
     assert exp_a["lm_head.weight"].optional and not exp_b["lm_head.weight"].optional
     have = {n: ps.shape for n, ps in exp_a.items() if n != "lm_head.weight"}
     check_names(exp_a, have)
+
+
+def test_sharded_model_folder(tmp_path):
+    """A folder of two shards and model.safetensors.index.json (how large checkpoints come) is read
+    like a single file: names and shapes are checked over all shards, and a tensor the index
+    promises but no shard holds is reported as missing."""
+    write_random_model(TINY_B, 5, tmp_path / "one", dtype=torch.bfloat16)
+    tensors = P.read_safetensors(tmp_path / "one" / "model.safetensors")
+    names = sorted(tensors)
+    halves = [names[: len(names) // 2], names[len(names) // 2:]]
+    folder = tmp_path / "sharded"
+    folder.mkdir()
+    weight_map = {}
+    for i, part in enumerate(halves):
+        fname = f"model-{i + 1:05d}-of-00002.safetensors"
+        write_safetensors(folder / fname, {n: tensors[n] for n in part})
+        weight_map.update({n: fname for n in part})
+    (folder / "config.json").write_text((tmp_path / "one" / "config.json").read_text())
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": weight_map}))
+    ck = Checkpoint(folder)
+    assert len(ck.files) == 2 and set(ck.names()) == set(names)
+    for n in (names[0], names[-1]):
+        assert torch.equal(ck.read(n), tensors[n])
+    expected = expected_tensors_of_spec(resolve(TINY_B)[1])
+    check_names(expected, {n: ck.info(n).shape for n in ck.names()})
+    ck.close()
+    # drop a tensor from the second shard: one error names it
+    victim = halves[1][0]
+    write_safetensors(folder / "model-00002-of-00002.safetensors", {n: tensors[n] for n in halves[1][1:]})
+    ck = Checkpoint(folder)
+    with pytest.raises(WeightError, match=victim.replace(".", r"\.")):
+        check_names(expected, {n: ck.info(n).shape for n in ck.names()})
+    ck.close()

@@ -76,6 +76,100 @@ def test_temperature_sampling_equals_plain_chain(folders):
     assert len({tuple(v) for v in out.values()}) == 4
 
 
+def test_temperature_sampling_in_bfloat16(folders):
+    """The same chain with bfloat16 logits: a token is the plain draw for the engine's own history,
+    or the uniform number lies so close to an edge of that token's share of the CDF that the
+    rounding of the logits decides; most draws are far from an edge and agree exactly."""
+    from mini_hisparse_b200 import Engine
+
+    cfg, page = TINY["B"]
+    pc, w = P.load_folder(folders["B"])
+    engine = Engine(load(folders["B"], "bfloat16"), num_pages=32, page_size=page, max_requests=4,
+                    max_tokens_per_step=48)
+    prompts = {str(n): random_tokens(cfg["vocab_size"], n, seed=n) for n in (1, 31, 100, 257)}
+    for i, (rid, prompt) in enumerate(prompts.items()):
+        engine.add_request(rid, prompt, max_new_tokens=24, temperature=0.8, seed=1234 + i)
+    out = engine.run()
+    exact = total = 0
+    for i, (rid, prompt) in enumerate(prompts.items()):
+        history = list(prompt)
+        assert len(out[rid]) == 24
+        for step, token in enumerate(out[rid]):
+            logits = P.forward_logits(pc, w, history)[-1]
+            want, _ = P.sample_temperature(logits, 0.8, 1234 + i, step)
+            cdf = (logits.double() / 0.8).softmax(-1).cumsum(-1)
+            u = P.uniform_from_counter(1234 + i, step) * float(cdf[-1])
+            low, high = (float(cdf[token - 1]) if token else 0.0), float(cdf[token])
+            assert max(low - u, u - high, 0.0) < 0.03, (rid, step, token, want)
+            exact += token == want
+            total += 1
+            history.append(token)
+    assert exact >= 0.85 * total, (exact, total)
+
+
+def test_most_requests_in_one_step_on_the_engine(folders):
+    """max_step_requests = 2 with four requests: steps hold two requests at most, everybody finishes,
+    and the tokens are those of the plain implementation."""
+    from mini_hisparse_b200 import Engine
+
+    cfg, page = TINY["A"]
+    pc, w = P.load_folder(folders["A"])
+    engine = Engine(load(folders["A"], "float32"), num_pages=32, page_size=page, max_requests=4,
+                    max_tokens_per_step=40, max_step_requests=2)
+    prompts = {str(n): random_tokens(cfg["vocab_size"], n, seed=n) for n in (5, 21, 34, 9)}
+    for rid, prompt in prompts.items():
+        engine.add_request(rid, prompt, max_new_tokens=6)
+    while not engine.scheduler.idle:
+        before = engine.runner.stats["steps"]
+        engine.step()
+        assert engine.runner.stats["steps"] == before + 1
+    assert all(t["tokens"] >= 1 for t in engine.timeline)
+    for rid, prompt in prompts.items():
+        assert engine.requests[rid].generated == P.generate(pc, w, prompt, 6)
+    engine.cache.assert_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_observer_sees_every_layer(folders, dtype):
+    """The observer hook of the step function: after every run entry it gets the residual stream and
+    the entry's still-unadded output; their sum is the plain implementation's hidden state after
+    that layer (the reference's hook: mini_hisparse/model.py:171-172, 202-203).  The prompt goes in
+    two portions, so the second call of a layer sees rows of later positions."""
+    from mini_hisparse_b200 import CacheConfig, CacheManager
+    from mini_hisparse_b200.engine import ModelRunner, StepEntry
+
+    cfg, page = TINY["B"]
+    pc, w = P.load_folder(folders["B"])
+    model = load(folders["B"], dtype)
+    cache = CacheManager(model.cache_needs, CacheConfig(num_pages=8, page_size=page, max_requests=2,
+                                                        dtype=model.rt.dtype))
+    runner = ModelRunner(model, cache)
+    toks = random_tokens(cfg["vocab_size"], 50, seed=3)
+    positions = torch.arange(50)
+    x = w["model.embed_tokens.weight"].float()[torch.tensor(toks)]
+    hidden = []
+    for layer in range(cfg["num_hidden_layers"]):
+        x = P.decoder_layer(pc, w, layer, x, positions)
+        hidden.append(x)
+    seen = []
+    runner.observer = lambda i, residual, pending: seen.append(
+        (i, (residual + pending.reduced()).float().cpu() if pending is not None else residual.float().cpu()))
+    cache.open("a")
+    runner.step([StepEntry("a", toks[:37], [])])
+    runner.step([StepEntry("a", toks[37:], [12])])
+    runner.check_status()
+    layers = cfg["num_hidden_layers"]
+    assert [i for i, _ in seen] == (list(range(layers)) + ["final"]) * 2
+    for call, rows in ((0, slice(0, 37)), (1, slice(37, 50))):
+        for layer in range(layers):
+            got = seen[call * (layers + 1) + layer][1]
+            ref = hidden[layer][rows]
+            tol = dict(atol=3e-5, rtol=3e-5) if dtype == "float32" else dict(atol=0.02 * float(ref.abs().max()), rtol=0.0)
+            torch.testing.assert_close(got, ref, **tol)
+        # after the last entry the hook gets the whole residual stream, the last output added
+        torch.testing.assert_close(seen[call * (layers + 1) + layers][1], hidden[-1][rows], **tol)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_and_first_tokens(folders, dtype):
     """A one-token prompt (positions 0, 1, 2, ... are all decoded) run far past several pages."""

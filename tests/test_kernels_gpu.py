@@ -216,17 +216,21 @@ def test_gemm_tensor_core_refuses_unaligned_k():
 
 @pytest.mark.parametrize("nq,nkv,d,P_,T,Kd", [(28, 4, 128, 16, 300, 3584), (3, 1, 64, 32, 70, 192), (5, 5, 128, 8, 129, 256),
                                                (2, 1, 64, 16, 2100, 64)])
-@pytest.mark.parametrize("rotate", [True, False])
-def test_gemm_qkv_epilogue_rotates_and_appends(nq, nkv, d, P_, T, Kd, rotate):
+@pytest.mark.parametrize("rdim_of,interleaved", [(lambda d: d, False), (lambda d: 0, False), (lambda d: d, True),
+                                                 (lambda d: d // 2, False), (lambda d: d // 4 * 3, True)],
+                         ids=["half_split", "none", "interleaved", "partial_half_split", "partial_interleaved"])
+def test_gemm_qkv_epilogue_rotates_and_appends(nq, nkv, d, P_, T, Kd, rdim_of, interleaved):
     """The q/k/v product whose epilogue adds the bias, rotates and appends to the paged cache,
     against the product followed by the rotary kernel (which has its own test against the plain
-    formulas): two segments, one of which starts inside a page."""
+    formulas): two segments, one of which starts inside a page; every rotation style."""
+    rdim = rdim_of(d)
+    assert K().gemm_tc_qkv_rope_supports(d, rdim, interleaved)
     N = (nq + 2 * nkv) * d
     x = rnd(T, Kd, dtype=torch.bfloat16, seed=1)
     w = rnd(N, Kd, dtype=torch.bfloat16, seed=2, scale=1.0 / math.sqrt(Kd))
     bias = rnd(N, seed=3) * 0.1
     theta = 10000.0
-    inv = (theta ** (-torch.arange(0, d, 2).float() / d)).to(DEV)
+    inv = (theta ** (-torch.arange(0, rdim, 2).float() / rdim)).to(DEV) if rdim else None
     n0 = T // 3
     positions = torch.tensor(list(range(37, 37 + n0)) + list(range(0, T - n0)), dtype=torch.int32, device=DEV)
     tok_seg = torch.tensor([0] * n0 + [1] * (T - n0), dtype=torch.int32, device=DEV)
@@ -244,13 +248,15 @@ def test_gemm_qkv_epilogue_rotates_and_appends(nq, nkv, d, P_, T, Kd, rotate):
     q_ref = torch.empty(T, nq * d, dtype=torch.bfloat16, device=DEV)
     cache_ref = torch.zeros(num_pages, 2, nkv, P_, d, dtype=torch.bfloat16, device=DEV)
     K().rope_append(qkv, bias, positions, tok_seg, table, inv, q_ref, cache_ref, nq=nq, nkv=nkv, d=d, page_size=P_,
-                    rotate=rotate, status=status)
-    cs = torch.empty(T, d, device=DEV)
-    K().rope_table(positions, inv, cs, d=d, rotate=rotate)
+                    rotary_dim=rdim, interleaved=interleaved, status=status)
+    cs = None
+    if rdim:
+        cs = torch.empty(T, rdim, device=DEV)
+        K().rope_table(positions, inv, cs)
     q = torch.full((T, nq * d), float("nan"), dtype=torch.bfloat16, device=DEV)
     cache = torch.zeros(num_pages, 2, nkv, P_, d, dtype=torch.bfloat16, device=DEV)
     K().gemm_tc_qkv_rope(x, w, bias, cs, positions, tok_seg, table, q, cache, nq=nq, nkv=nkv, d=d, page_size=P_,
-                         status=status)
+                         rotary_dim=rdim, interleaved=interleaved, status=status)
     assert int(status) == 0
     scale = float(qkv.abs().max())
     torch.testing.assert_close(q.float(), q_ref.float(), atol=1e-2 * scale, rtol=1.6e-2)
@@ -260,14 +266,39 @@ def test_gemm_qkv_epilogue_rotates_and_appends(nq, nkv, d, P_, T, Kd, rotate):
     # without write access nothing is appended
     cache2 = torch.zeros_like(cache)
     K().gemm_tc_qkv_rope(x, w, bias, cs, positions, tok_seg, table, q, cache2, nq=nq, nkv=nkv, d=d, page_size=P_,
-                         write_kv=False, status=status)
+                         rotary_dim=rdim, interleaved=interleaved, write_kv=False, status=status)
     assert int(cache2.abs().sum()) == 0
 
 
 # ---- rotary + append -----------------------------------------------------------------------------
+def plain_rotation(t, positions, theta, rdim, interleaved):
+    """The first rdim elements of every head of t [T, heads, d] turned by angle_i = pos * theta^(-2i/rdim):
+    pairs (i, i + rdim/2), or (2i, 2i + 1) if interleaved; the rest of the head passes.  With rdim = d
+    and half-split pairs this is the reference's rotation (mini_hisparse/model.py:141-151)."""
+    if rdim == 0:
+        return t
+    inv = theta ** (-torch.arange(0, rdim, 2, device=t.device).float() / rdim)
+    ang = positions.float()[:, None] * inv[None, :]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    out = t.clone()
+    if interleaved:
+        a, b = t[..., 0:rdim:2], t[..., 1:rdim:2]
+        out[..., 0:rdim:2], out[..., 1:rdim:2] = a * cos - b * sin, b * cos + a * sin
+    else:
+        a, b = t[..., : rdim // 2], t[..., rdim // 2: rdim]
+        out[..., : rdim // 2], out[..., rdim // 2: rdim] = a * cos - b * sin, b * cos + a * sin
+    return out
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nq,nkv,d,P_", [(4, 2, 16, 16), (3, 1, 32, 32), (10, 2, 48, 16), (7, 7, 128, 8)])
-def test_rope_append(dtype, nq, nkv, d, P_):
+@pytest.mark.parametrize("nq,nkv,d,P_,rdim,interleaved", [
+    (4, 2, 16, 16, 16, False), (3, 1, 32, 32, 32, False), (10, 2, 48, 16, 48, False), (7, 7, 128, 8, 128, False),
+    (3, 1, 32, 24, 32, True), (10, 2, 48, 7, 24, False), (2, 2, 64, 16, 40, True), (5, 1, 80, 16, 6, True),
+    (2, 1, 18, 16, 10, False), (4, 4, 64, 16, 0, False)])
+def test_rope_append(dtype, nq, nkv, d, P_, rdim, interleaved):
+    """Every rotation style against the plain rotation: the reference's (half-split pairs over the
+    whole head), interleaved pairs, a rotated part of the head (widths that the vector kernel takes and
+    widths that only the scalar kernel takes), and none."""
     theta = 50000.0
     T, pages = 21, 9
     width = (nq + 2 * nkv) * d
@@ -284,15 +315,20 @@ def test_rope_append(dtype, nq, nkv, d, P_):
     table = table.to(DEV)
     cache = torch.zeros(64, 2, nkv, P_, d, dtype=dtype, device=DEV)
     q_out = torch.empty(T, nq * d, dtype=dtype, device=DEV)
-    inv = (theta ** (-torch.arange(0, d, 2).float() / d)).to(DEV)
-    K().rope_append(qkv, bias, positions, tok_seg, table, inv, q_out, cache, nq=nq, nkv=nkv, d=d, page_size=P_)
+    inv = (theta ** (-torch.arange(0, rdim, 2).float() / rdim)).to(DEV) if rdim else None
+    K().rope_append(qkv, bias, positions, tok_seg, table, inv, q_out, cache, nq=nq, nkv=nkv, d=d, page_size=P_,
+                    rotary_dim=rdim, interleaved=interleaved)
     full = qkv + bias
     q = full[:, : nq * d].view(T, nq, d)
     k = full[:, nq * d : (nq + nkv) * d].view(T, nkv, d)
     v = full[:, (nq + nkv) * d :].view(T, nkv, d)
-    cos, sin = P.rope_tables(positions, d, theta, torch.float32)
-    torch.testing.assert_close(q_out.float().view(T, nq, d), P.rotate(q, cos, sin), **tol(dtype, 4))
-    kr = P.rotate(k, cos, sin)
+    if rdim == d and not interleaved:          # the reference's own form, as the plain model computes it
+        cos, sin = P.rope_tables(positions, d, theta, torch.float32)
+        torch.testing.assert_close(plain_rotation(q, positions, theta, rdim, False), P.rotate(q, cos, sin),
+                                   atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(q_out.float().view(T, nq, d), plain_rotation(q, positions, theta, rdim, interleaved),
+                               **tol(dtype, 4))
+    kr = plain_rotation(k, positions, theta, rdim, interleaved)
     for t in range(T):
         pos, seg = int(positions[t]), int(tok_seg[t])
         page = int(table[seg, pos // P_])
@@ -371,14 +407,13 @@ def paged_case(nq, nkv, d, P_, seg_specs, dtype, seed=0):
 
 def run_attention(nq, nkv, d, P_, seg_specs, dtype, window=None, fixed_nsplit=None, seed=0, edit=None,
                   kernel="simt"):
-    from mini_hisparse_b200.parts.attention import ITEM_INTS, plan_attention
-    from mini_hisparse_b200.parts.spec import PagedKVNeed
+    from mini_hisparse_b200.parts.attention import ITEM_INTS, AttentionShape, plan_attention
 
     cache, table, segments, qs, ks, vs, positions = paged_case(nq, nkv, d, P_, seg_specs, dtype, seed)
     if edit:
         edit(qs, ks, vs, cache, table)
     T = sum(n for _, n in seg_specs)
-    need = PagedKVNeed(nkv, d, nq, window, tile_rows={"mma": 64, "tc": 128}.get(kernel, 16))
+    need = AttentionShape(nq, nkv, window, {"mma": 64, "tc": 128}.get(kernel, 16))
     plan = plan_attention(need, segments, T, 148, fixed_nsplit=fixed_nsplit)
     q = torch.cat([qq[h:] for qq, (h, n) in zip(qs, seg_specs)]).reshape(T, nq * d).to(DEV)
     out = torch.full((T, nq * d), float("nan"), dtype=dtype, device=DEV)

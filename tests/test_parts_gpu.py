@@ -79,6 +79,7 @@ def test_attention_mixer_over_its_cache(dtype, nq, nkv, d, theta):
                          window=None, position=PartSpec.make("rotary", head_dim=d, theta=theta))
     rt, cache, batch, ws, status = harness([MIXERS.get("gq_attention")(spec).cache_need()], dtype)
     mixer = MIXERS.build(spec, rt=rt)
+    user = batch.add_user(0, mixer)      # the mixer's planner joins the step's packing
     w = fill(mixer, 2, dtype)
 
     @dataclass_like
@@ -96,7 +97,7 @@ def test_attention_mixer_over_its_cache(dtype, nq, nkv, d, theta):
         entries = [StepEntry(r, [0] * cuts[r][step], []) for r in ("a", "b")]
         ctx, views, segments = context(rt, cache, batch, ws, status, entries)
         h = torch.cat([hs[r][done[r]: done[r] + cuts[r][step]] for r in ("a", "b")]).to(DEV, dtype)
-        out = mixer.forward(h, ctx, batch.cache_view(0, views["groups"])).reduced().cpu()
+        out = mixer.forward(h, ctx, batch.cache_view(user, views)).reduced().cpu()
         row = 0
         for r in ("a", "b"):
             n = cuts[r][step]
@@ -154,8 +155,9 @@ def test_block_alone(dtype, folders):
     cfg, spec = resolve(TINY_B)
     layer = spec.layers[1]
     block0 = BLOCKS.get(layer.block)(layer, None)
-    rt, cache, batch, ws, status = harness([block0.mixer.cache_need()], dtype, page_size=32)
+    rt, cache, batch, ws, status = harness([block0.cache_need()], dtype, page_size=32)
     block = BLOCKS.get(layer.block)(layer, rt)
+    user = batch.add_user(0, block)
     pw, sd = P.load_folder(folders["B"])
     for role, part in block.parts().items():
         prefix = f"{layer.prefix}.{layer.name_of(role)}."
@@ -167,7 +169,7 @@ def test_block_alone(dtype, folders):
     x0 = torch.randn(T, 96)
     pend = (torch.randn(T, 96) * 0.3).to(torch.bfloat16).float()
     x = x0.clone().to(DEV)
-    out = block.forward(x, Product(pend.to(DEV, dtype)), ctx, batch.cache_view(0, views["groups"]))
+    out = block.forward(x, Product(pend.to(DEV, dtype)), ctx, batch.cache_view(user, views))
     total = x.cpu() + out.reduced().cpu()
     ref = P.decoder_layer(pw, sd, 1, x0 + pend, torch.arange(T))
     torch.testing.assert_close(total, ref, **tol(dtype, ref))

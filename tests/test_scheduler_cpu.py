@@ -9,7 +9,7 @@ from mini_hisparse_b200.sampling import SamplingParams
 
 
 def make(num_pages=16, page_size=4, max_requests=4, budget=8, vocab=50, max_positions=None, eos=None):
-    cache = CacheManager([PagedKVNeed(2, 16, 4)] * 2,
+    cache = CacheManager([PagedKVNeed(2, 16)] * 2,
                          CacheConfig(num_pages=num_pages, page_size=page_size, max_requests=max_requests,
                                      dtype=torch.float32, device="cpu", allocate_storage=False))
     return Scheduler(cache, SchedulerConfig(max_tokens_per_step=budget), vocab, max_positions, eos), cache
@@ -137,3 +137,58 @@ def test_more_decoders_than_budget_take_turns():
         seen += [p.request.request_id for p in planned]
         fake_step(s, c, planned)
     assert {seen.count(x) for x in "012"} == {4}
+
+
+def test_most_requests_in_one_step():
+    """max_step_requests caps how many requests share a step: the decoders take turns (the deque
+    rotates, nobody starves) and a prompt waits for a free place."""
+    cache = CacheManager([PagedKVNeed(2, 16)] * 2,
+                         CacheConfig(num_pages=32, page_size=4, max_requests=6, dtype=torch.float32, device="cpu",
+                                     allocate_storage=False))
+    s = Scheduler(cache, SchedulerConfig(max_tokens_per_step=64, max_step_requests=2), 50)
+    for name in "abc":
+        s.add(name, [1, 2, 3], SamplingParams(6))
+    turns = {n: 0 for n in "abcd"}
+    late_added = False
+    for step in range(40):
+        if s.idle:
+            break
+        planned = s.plan()
+        assert 1 <= len(planned) <= 2, [p.request.request_id for p in planned]
+        for p in planned:
+            turns[p.request.request_id] += 1
+        fake_step(s, cache, planned)
+        if step == 3 and not late_added:
+            s.add("d", [4, 5, 6, 7], SamplingParams(2))     # a prompt that arrives while three decode
+            late_added = True
+    assert s.idle
+    assert all(len(s.requests[n].generated) == 6 for n in "abc") and len(s.requests["d"].generated) == 2
+    assert turns["a"] == turns["b"] == turns["c"] == 6      # one prompt step and five decode steps each
+    cache.assert_invariants()
+    assert cache.snapshot()["page_groups"][0]["pages_free"] == 32
+
+
+def test_a_failed_step_finishes_its_requests_and_frees_their_pages():
+    """A step raised after the cache had taken its tokens: its requests cannot be fed again (their
+    cache positions ran ahead of the scheduler's books), so they end as failed and give everything
+    back; a request that was not in the step goes on."""
+    s, c = make(num_pages=16, budget=6)
+    s.add("a", [1, 2, 3, 4], SamplingParams(4))
+    s.add("b", [5, 6], SamplingParams(4))
+    s.add("late", list(range(1, 9)), SamplingParams(2))
+    planned = s.plan()                       # a whole, b whole, nothing of late (budget 6)
+    assert [p.request.request_id for p in planned] == ["a", "b"]
+    for p in planned:                        # the runner got as far as growing the cache, then raised
+        rid = p.request.request_id
+        c.ensure(rid, len(p.tokens))
+        c.advance(rid, len(p.tokens))
+    failed = s.fail(planned)
+    assert failed == ["a", "b"]
+    assert all(s.requests[n].failed and s.requests[n].finished and not s.requests[n].generated for n in "ab")
+    assert "a" not in c.requests and "b" not in c.requests
+    c.assert_invariants()
+    assert c.snapshot()["page_groups"][0]["pages_free"] == 16
+    while not s.idle:                        # the third request is served as if nothing had happened
+        fake_step(s, c, s.plan())
+    assert s.requests["late"].generated == [7, 7] and not s.requests["late"].failed
+    assert s.stats["failed_requests"] == 2

@@ -1,9 +1,12 @@
 """Generality of the parts: a toy model defined HERE, with a mixer that keeps a state of its own,
 a feed-forward that routes each token to one of two experts, a position encoding of its own
 (rotary with stretched wavelengths), a layer that runs twice, a layer that reads another layer's
-cache and a layer without position encoding, is registered, built from a model folder and stepped
-in portions, without a change to the framework's files.  It is compared with a whole-sequence
-computation written here.  None of these toys is anyone's model."""
+cache, a layer without position encoding, a layer whose attention has twice the query heads over
+the same keys (it shares the other layers' pages and block table) with interleaved rotation of
+half of each head, and a block arrangement of its own with one norm more than the built-in one,
+is registered, built from a model folder and stepped in portions, without a change to the
+framework's files.  It is compared with a whole-sequence computation written here.  None of
+these toys is anyone's model."""
 import json
 from dataclasses import dataclass
 
@@ -21,21 +24,48 @@ TOY = dict(architectures=["ToyForCausalLM"], vocab_size=130, hidden_size=48, int
 
 def register_toy():
     from mini_hisparse_b200 import register_architecture
-    from mini_hisparse_b200.parts import (FeedForward, LayerSpec, Mixer, ModelSpec, ParamSpec, Part, PartSpec,
-                                          Product, RunEntry, StateNeed, register_feed_forward, register_mixer,
+    from mini_hisparse_b200.parts import (FEED_FORWARDS, MIXERS, NORMS, Block, FeedForward, LayerSpec, Mixer,
+                                          ModelSpec, ParamSpec, PartSpec, Product, RunEntry, StateNeed,
+                                          register_block, register_feed_forward, register_mixer,
                                           register_position)
+    from mini_hisparse_b200.parts.position import Position
 
     @register_position("toy_stretched_rotary", replace=True)
-    class StretchedRotary(Part):
+    class StretchedRotary(Position):
         """Half-split rotation whose wavelengths are `stretch` times longer."""
-
-        rotates = True
 
         def __init__(self, spec, rt=None):
             super().__init__(spec, rt)
             d = spec["head_dim"]
+            self.rotary_dim = d
             inv = spec["theta"] ** (-torch.arange(0, d, 2).float() / d) / spec["stretch"]
             self.inv_freq = inv.to(rt.device) if rt is not None else inv
+
+    @register_block("toy_sandwich", replace=True)
+    class SandwichBlock(Block):
+        """x = x + post_norm(mixer(norm(x))); x = x + ff(norm2(x)): the built-in arrangement with a
+        fifth part, a norm on the mixer's output."""
+
+        graph_safe = False          # reduced() below is plain torch: a toy
+
+        def __init__(self, spec, rt):
+            self.spec = spec
+            self.mixer_norm = NORMS.build(spec.part("mixer_norm"), rt=rt)
+            self.mixer = MIXERS.build(spec.part("mixer"), rt=rt)
+            self.post_norm = NORMS.build(spec.part("post_norm"), rt=rt)
+            self.ff_norm = NORMS.build(spec.part("ff_norm"), rt=rt)
+            self.feed_forward = FEED_FORWARDS.build(spec.part("feed_forward"), rt=rt)
+
+        def parts(self):
+            return {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "post_norm": self.post_norm,
+                    "ff_norm": self.ff_norm, "feed_forward": self.feed_forward}
+
+        def forward(self, x, pending, ctx, cache):
+            h = self.mixer_norm.forward(x, ctx, delta=pending)
+            a = self.mixer.forward(h, ctx, cache).reduced().contiguous()     # float32 [T, H]
+            post = self.post_norm.forward(a, ctx, name="toy_post")
+            h = self.ff_norm.forward(x, ctx, delta=Product(post))
+            return self.feed_forward.forward(h, ctx)
 
     @register_feed_forward("toy_routed", replace=True)
     class Routed(FeedForward):
@@ -115,17 +145,25 @@ def register_toy():
         norm = PartSpec.make("rmsnorm", width=H, eps=c["eps"])
         ff = PartSpec.make("swiglu", hidden_size=H, intermediate_size=c["intermediate_size"])
 
-        def attn(position):
-            return PartSpec.make("gq_attention", hidden_size=H, q_heads=c["q_heads"], kv_heads=c["kv_heads"],
+        def attn(position, q_heads=c["q_heads"]):
+            return PartSpec.make("gq_attention", hidden_size=H, q_heads=q_heads, kv_heads=c["kv_heads"],
                                  head_dim=c["head_dim"], qkv_bias=False, window=None, position=position)
 
         rotary = PartSpec.make("toy_stretched_rotary", head_dim=c["head_dim"], theta=c["theta"], stretch=4.0)
+        pairs = PartSpec.make("rotary", head_dim=c["head_dim"], theta=c["theta"], style="interleaved",
+                              rotary_dim=c["head_dim"] // 2)
         routed = PartSpec.make("toy_routed", hidden_size=H, intermediate_size=c["intermediate_size"])
         mixers = [attn(rotary), PartSpec.make("toy_running_mean", hidden_size=H), attn(PartSpec.make("none"))]
         ffs = [ff, routed, ff]
-        layers = tuple(LayerSpec(f"toy.layers.{i}", "pre_norm", m, norm, f, norm)
-                       for i, (m, f) in enumerate(zip(mixers, ffs)))
-        order = (RunEntry(0), RunEntry(1), RunEntry(2), RunEntry(1), RunEntry(2, cache_of=2))
+        layers = [LayerSpec.pre_norm(f"toy.layers.{i}", mixer=m, mixer_norm=norm, feed_forward=f, ff_norm=norm)
+                  for i, (m, f) in enumerate(zip(mixers, ffs))]
+        # a fourth layer in an arrangement of its own: five parts, twice the query heads, other rotation
+        layers.append(LayerSpec.make("toy.layers.3", "toy_sandwich",
+                                     {"mixer_norm": norm, "mixer": attn(pairs, 2 * c["q_heads"]), "post_norm": norm,
+                                      "ff_norm": norm, "feed_forward": ff},
+                                     {"mixer": "self_attn", "feed_forward": "mlp"}))
+        layers = tuple(layers)
+        order = (RunEntry(0), RunEntry(1), RunEntry(2), RunEntry(1), RunEntry(2, cache_of=2), RunEntry(3))
         return ModelSpec("ToyForCausalLM", c["vocab_size"], H,
                          PartSpec.make("token_embedding", vocab_size=c["vocab_size"], hidden_size=H), "toy.embed",
                          layers, order, norm, "toy.norm",
@@ -142,12 +180,25 @@ def toy_reference(w, tokens):
     pos = torch.arange(T)
     shared_kv = {}
 
-    def attention(i, h, rotate, entry, reuse=None):
+    def interleaved_half(t):
+        """Pairs (2i, 2i + 1) of the first half of every head turned by pos * theta^(-2i / (d/2))."""
+        r = c["head_dim"] // 2
+        inv = c["theta"] ** (-torch.arange(0, r, 2).float() / r)
+        ang = pos.float()[:, None] * inv[None, :]
+        cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        out = t.clone()
+        a, b = t[..., 0:r:2], t[..., 1:r:2]
+        out[..., 0:r:2], out[..., 1:r:2] = a * cos - b * sin, b * cos + a * sin
+        return out
+
+    def attention(i, h, rotate, entry, reuse=None, q_heads=c["q_heads"]):
         p = f"toy.layers.{i}.self_attn."
-        q = (h @ w[p + "q_proj.weight"].T).view(T, c["q_heads"], c["head_dim"])
+        q = (h @ w[p + "q_proj.weight"].T).view(T, q_heads, c["head_dim"])
         k = (h @ w[p + "k_proj.weight"].T).view(T, c["kv_heads"], c["head_dim"])
         v = (h @ w[p + "v_proj.weight"].T).view(T, c["kv_heads"], c["head_dim"])
-        if rotate:
+        if rotate == "interleaved_half":
+            q, k = interleaved_half(q), interleaved_half(k)
+        elif rotate:
             inv = c["theta"] ** (-torch.arange(0, c["head_dim"], 2).float() / c["head_dim"]) / 4.0
             ang = pos.float()[:, None] * inv[None, :]
             ang = torch.cat((ang, ang), -1)[:, None, :]
@@ -183,6 +234,13 @@ def toy_reference(w, tokens):
     x = block(2, x, lambda h: attention(2, h, False, 2))
     x = block(1, x, lambda h: running_mean(1, h))
     x = block(2, x, lambda h: attention(2, h, False, 4, reuse=2))
+    # the sandwich arrangement: a norm on the mixer's output before it joins the residual
+    p = "toy.layers.3."
+    a = attention(3, P.rms_norm(x, w[p + "mixer_norm.weight"], c["eps"]), "interleaved_half", 5,
+                  q_heads=2 * c["q_heads"])
+    x = x + P.rms_norm(a, w[p + "post_norm.weight"], c["eps"])
+    x = x + P.swiglu(P.rms_norm(x, w[p + "ff_norm.weight"], c["eps"]), w[p + "mlp.gate_proj.weight"],
+                     w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
     return P.rms_norm(x, w["toy.norm.weight"], c["eps"]) @ w["toy.embed.weight"].T
 
 
@@ -195,12 +253,14 @@ def test_toy_model_registers_builds_and_steps(tmp_path, dtype):
     write_random_model(TOY, 5, tmp_path, dtype=torch.bfloat16, matrix_std=0.15)
     w = {k: v.float() for k, v in P.read_safetensors(tmp_path / "model.safetensors").items()}
     model = load_model(tmp_path, dtype=dtype)
-    assert len(model.cache_needs) == 4            # five run entries, one of them reads another's cache
+    assert len(model.cache_needs) == 5            # six run entries, one of them reads another's cache
     cache = CacheManager(model.cache_needs, CacheConfig(num_pages=12, page_size=16, max_requests=3,
                                                         dtype=model.rt.dtype))
+    # the layer with twice the query heads keeps the same keys and values: one pool, one block table
     assert len(cache.page_groups) == 1 and len(cache.state_groups) == 1
-    assert len(cache.page_groups[0].entries) == 2 and len(cache.state_groups[0].entries) == 2
+    assert len(cache.page_groups[0].entries) == 3 and len(cache.state_groups[0].entries) == 2
     runner = ModelRunner(model, cache)
+    assert len(runner.batch.slots) == 2           # ... but a plan of its own
     assert not runner.use_graphs                  # the toy mixer works on the host: no captured graph
     reqs = {"a": random_tokens(130, 70, 1), "b": random_tokens(130, 41, 2)}
     refs = {k: toy_reference(w, t) for k, t in reqs.items()}

@@ -52,7 +52,9 @@ def no_alloc(handle, a, w, out, nsplit):
 def test_no_alloc_product_matches_existing_entry_point_twice():
     handle = lib()
     g = torch.Generator().manual_seed(5)
-    cases = [((130, 333, 1000), torch.float32, 7), ((9, 77, 520), torch.bfloat16, 4)]
+    # the last two: more splits than K has elements (the empty ones must add zeros), and one split
+    cases = [((130, 333, 1000), torch.float32, 7), ((9, 77, 520), torch.bfloat16, 4), ((5, 40, 16), torch.float32, 20),
+             ((33, 20, 100), torch.float32, 1)]
     for (M, N, K), dtype, nsplit in cases:            # two calls in a row, the second one smaller
         a = torch.randn(M, K, generator=g).to(dtype).to(DEV)
         w = torch.randn(N, K, generator=g).to(dtype).to(DEV)
@@ -81,3 +83,9 @@ def test_no_alloc_product_refuses_what_does_not_fit():
     assert "scratch" in msg and str(SCRATCH_FLOATS) in msg
     torch.cuda.synchronize()
     assert float(out.min()) == 7.0                                    # nothing was launched
+    small = torch.zeros(4, 8, device=DEV)
+    assert no_alloc(handle, small, small, out, 70000) != 0 and "65535" in handle.mhb_last_error().decode()
+    narrow = torch.full((4, 2), 7.0, device=DEV)                      # a row stride of 2 for 4 columns
+    assert no_alloc(handle, small, small, narrow, 1) != 0 and "row stride" in handle.mhb_last_error().decode()
+    torch.cuda.synchronize()
+    assert float(narrow.min()) == 7.0
