@@ -328,6 +328,58 @@ def attention_tma(q, cache, out, part_acc, part_ml, items, num_items, rows, posi
         _stream()), "attention_tma")
 
 
+DECODE_MAX_SPLITS = 16      # key splits of a token that the fused decode kernel merges in one cluster
+
+
+def attention_decode_supports(d: int, page_size: int, groups: int, nsplit: int, rotary_dim: int) -> bool:
+    """Sizes the fused decode-attention kernel is built for."""
+    return (d in (64, 128) and 2 <= page_size <= 64 and 64 % page_size == 0 and 1 <= groups <= 16
+            and 1 <= nsplit <= DECODE_MAX_SPLITS and 0 <= rotary_dim <= d and rotary_dim % 8 == 0)
+
+
+_decode_clusters: dict[tuple[int, int], int] = {}
+
+
+def attention_decode_max_clusters(d: int, nsplit: int) -> int:
+    """How many clusters of ``nsplit`` CTAs of the fused decode kernel the device holds at once."""
+    key = (d, nsplit)
+    if key not in _decode_clusters:
+        lib = build.load("attention_decode")
+        n = lib.mhb_attention_decode_max_clusters(c_int(d), c_int(nsplit))
+        if n < 0:
+            raise KernelError(f"attention_decode: {lib.mhb_last_error().decode()}")
+        _decode_clusters[key] = n
+    return _decode_clusters[key]
+
+
+def attention_decode(qkv, bias, inv_freq, cache, out, positions, block_table, *, nq, nkv, d, page_size, nsplit,
+                     qkv_nsplit=1, qkv_split_stride=0, rotary_dim=None, interleaved=False, window=0, scale=None,
+                     status=None):
+    """A batch of single new tokens in one kernel: the q/k/v product's float32 partials ``qkv``
+    ([qkv_nsplit, T, (nq + 2 nkv) d], ``qkv_split_stride`` elements apart) are summed, biased and
+    rotated, k and v are appended to ``cache`` (one layer's pool), every token attends over its
+    ``nsplit`` equal shares of keys and the shares are merged inside a thread-block cluster.
+    Token i is segment i: ``block_table`` [T, width], ``positions`` [T]; ``out`` [T, nq d] bfloat16."""
+    lib = build.load("attention_decode")
+    T = out.shape[0]
+    if qkv.dtype != torch.float32 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attention_decode: the product's parts must be float32, cache and output bfloat16")
+    if not cache.is_contiguous() or not out.is_contiguous() or qkv.stride(-1) != 1 or qkv.stride(-2) != (nq + 2 * nkv) * d:
+        raise KernelError("attention_decode: the pool, the output and the rows of the product must be contiguous")
+    if rotary_dim is None:
+        rotary_dim = d if inv_freq is not None else 0
+    if rotary_dim and (inv_freq is None or inv_freq.numel() != rotary_dim // 2):
+        raise KernelError(f"attention_decode: {rotary_dim} rotated elements need {rotary_dim // 2} frequencies")
+    if scale is None:
+        scale = float(d) ** -0.5
+    _check(lib, lib.mhb_attention_decode(
+        _ptr(qkv), c_int(qkv_nsplit), c_longlong(qkv_split_stride), _ptr(bias), _ptr(inv_freq), c_int(rotary_dim),
+        c_int(1 if interleaved else 0), _ptr(cache), _ptr(out), _ptr(positions), _ptr(block_table),
+        c_int(block_table.shape[-1]), c_int(T), c_int(nq), c_int(nkv), c_int(d), c_int(page_size),
+        c_int(cache.shape[0]), c_int(window or 0), c_int(nsplit), c_float(scale), _ptr(status), _stream()),
+        "attention_decode")
+
+
 def attention_tc(q, cache, out, items, num_items, positions, block_table, *, nq, nkv, d, page_size,
                  window=0, scale=None, status=None, part_acc=None, part_ml=None, tok_part_row=None):
     """tcgen05 attention for long portions: ``items`` planned for tiles of 128 rows; items split

@@ -30,7 +30,8 @@ NVCC_FLAGS = [
 ]
 
 # Every module the package has; __graft_entry__.build() compiles all of them.
-MODULES = ("elementwise", "gemm_simt", "gemm_tc", "attention_simt", "attention_mma", "attention_tma", "attention_tc", "sampling")
+MODULES = ("elementwise", "gemm_simt", "gemm_tc", "attention_simt", "attention_mma", "attention_tma", "attention_decode",
+           "attention_tc", "sampling")
 
 
 class KernelBuildError(RuntimeError):

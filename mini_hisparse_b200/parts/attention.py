@@ -220,8 +220,11 @@ class AttentionPlanner(StepPlanner):
     """The plan of grouped-query attention for the step function: work items, and for every token
     the first of its partial rows and the number of its key splits."""
 
-    def __init__(self, shape: AttentionShape, sm_count: int):
+    def __init__(self, shape: AttentionShape, sm_count: int, clusters_of=None, max_cluster: int = 0):
+        """``clusters_of(n)``: how many clusters of n CTAs the mixer's decode kernel can run at once, if
+        it merges a token's key splits inside a cluster of up to ``max_cluster`` CTAs (None: it does not)."""
         self.shape, self.sm_count = shape, sm_count
+        self.clusters_of, self.max_cluster = clusters_of, max_cluster
         groups = shape.q_heads // shape.kv_heads
         self.chunks = 1 if groups <= ROW_TILE else -(-groups // ROW_TILE)
 
@@ -233,13 +236,20 @@ class AttentionPlanner(StepPlanner):
         return {"items": items * ITEM_INTS, "tok_part_row": max_tokens, "tok_nsplit": max_tokens}
 
     @staticmethod
-    def _out(plan: AttentionPlan):
+    def _out(plan: AttentionPlan, decode_nsplit: int = 0):
         arrays = {"items": plan.items.reshape(-1), "tok_part_row": plan.tok_part_row, "tok_nsplit": plan.tok_nsplit}
+        # decode_nsplit > 0: the step is single tokens only (token i = segment i), every one with
+        # exactly that many equal shares of keys: what a kernel that plans for itself needs to know
         facts = {"n_small": plan.n_small, "n_big": plan.n_big, "part_rows_cap": plan.part_rows,
-                 "any_split": bool(plan.part_rows), "big_split": plan.big_split}
+                 "any_split": bool(plan.part_rows), "big_split": plan.big_split, "decode_nsplit": decode_nsplit}
         return arrays, facts
 
     def plan(self, segments, T, fixed=None):
+        if fixed is None and T == len(segments) and all(s.offset == i for i, s in enumerate(segments)):
+            # single tokens only: the plan of a captured decode graph, so that a step does not
+            # depend on whether it is replayed or launched
+            starts = np.fromiter((s.start for s in segments), np.int64, T)
+            return self.plan_decode(starts, self.decode_fixed(T, int(starts.max()) + 1))
         return self._out(plan_attention(self.shape, segments, T, self.sm_count, fixed_nsplit=fixed))
 
     def decode_fixed(self, segments_count, max_positions):
@@ -247,10 +257,17 @@ class AttentionPlanner(StepPlanner):
         many CTAs as are resident at once (two per SM), never more, so that no CTA waits for a
         second wave, and no split shorter than MIN_KEYS_PER_SPLIT keys."""
         ctas = segments_count * self.shape.kv_heads * self.chunks
-        return max(1, min(MAX_SPLITS, (2 * self.sm_count) // ctas, max_positions // MIN_KEYS_PER_SPLIT))
+        n = max(1, min(MAX_SPLITS, (2 * self.sm_count) // ctas, max_positions // MIN_KEYS_PER_SPLIT))
+        if self.clusters_of is not None and self.chunks == 1 and 1 < n <= self.max_cluster:
+            # the splits of a token form a cluster, and clusters are placed inside one GPC: take the
+            # largest size of which all the step's clusters run at once (a second round of clusters
+            # costs more than shorter shares gain)
+            while n > 1 and self.clusters_of(n) < ctas:
+                n -= 1
+        return n
 
     def plan_decode(self, starts, fixed):
-        return self._out(plan_decode(self.shape, starts, fixed))
+        return self._out(plan_decode(self.shape, starts, fixed), fixed if self.chunks == 1 else 0)
 
 
 @register_mixer("gq_attention")
@@ -304,7 +321,7 @@ class GQAttention(Mixer):
         if not self.tensor_core_attention:
             return ("attention_simt",)
         if self.d in (64, 128):
-            return ("attention_simt", "attention_mma", "attention_tma", "attention_tc")
+            return ("attention_simt", "attention_mma", "attention_tma", "attention_decode", "attention_tc")
         return ("attention_simt", "attention_mma")
 
     def cache_need(self):
@@ -314,8 +331,11 @@ class GQAttention(Mixer):
         return ("gq_attention", self.nq, self.nkv, self.d, self.window)
 
     def planner(self, page_size: int, sm_count: int):
-        return AttentionPlanner(AttentionShape(self.nq, self.nkv, self.window, self.big_tile_rows(page_size)),
-                                sm_count)
+        shape = AttentionShape(self.nq, self.nkv, self.window, self.big_tile_rows(page_size))
+        if self.kernel_family(page_size) == "tc" and self.nq // self.nkv <= ROW_TILE:
+            return AttentionPlanner(shape, sm_count, lambda n: K.attention_decode_max_clusters(self.d, n),
+                                    K.DECODE_MAX_SPLITS)
+        return AttentionPlanner(shape, sm_count)
 
     def parameters(self):
         q, kv = self.nq * self.d, self.nkv * self.d
@@ -344,6 +364,22 @@ class GQAttention(Mixer):
     def forward(self, h, ctx: StepContext, cache: CacheView) -> Product:
         rt, ws, T = ctx.rt, ctx.ws, h.shape[0]
         meta = cache.meta
+        family = self.kernel_family(cache.page_size)
+        rdim = int(getattr(self.position, "rotary_dim", 0) or 0)
+        interleaved = bool(getattr(self.position, "interleaved", False))
+        nsplit = meta.get("decode_nsplit", 0)
+        if (family == "tc" and nsplit and cache.writable
+                and K.attention_decode_supports(self.d, cache.page_size, self.nq // self.nkv, nsplit, rdim)):
+            # single new tokens only: sum of the product's parts, bias, rotation, append, attention and
+            # the merge of the key splits are one kernel
+            qkv = rt.linear(h, self.qkv_weight, ws, "qkv", out_dtype=torch.float32)
+            attn = ws.get("attn", (T, self.nq * self.d), rt.dtype)
+            K.attention_decode(qkv.tensor, self.qkv_bias_vec, self.position.inv_freq, cache.storage, attn,
+                               ctx.positions, meta["block_table"], nq=self.nq, nkv=self.nkv, d=self.d,
+                               page_size=cache.page_size, nsplit=nsplit, qkv_nsplit=qkv.nsplit,
+                               qkv_split_stride=qkv.split_stride, rotary_dim=rdim, interleaved=interleaved,
+                               window=self.window or 0, scale=self.scale, status=ctx.status)
+            return rt.linear(attn, self.o_weight, ws, "mix_out")
         q = ws.get("q", (T, self.nq * self.d), rt.dtype)
         fused = rt.qkv_rope_append(h, self.qkv_weight, self.qkv_bias_vec, ctx, self.position, meta["block_table"],
                                    q, cache.storage, nq=self.nq, nkv=self.nkv, d=self.d,
@@ -353,9 +389,7 @@ class GQAttention(Mixer):
             K.rope_append(
                 qkv.tensor, self.qkv_bias_vec, ctx.positions, ctx.tok_seg, meta["block_table"],
                 self.position.inv_freq, q, cache.storage, nq=self.nq, nkv=self.nkv, d=self.d,
-                page_size=cache.page_size, write_kv=cache.writable,
-                rotary_dim=int(getattr(self.position, "rotary_dim", 0) or 0),
-                interleaved=bool(getattr(self.position, "interleaved", False)),
+                page_size=cache.page_size, write_kv=cache.writable, rotary_dim=rdim, interleaved=interleaved,
                 nsplit=qkv.nsplit, split_stride=qkv.split_stride, status=ctx.status,
             )
         attn = ws.get("attn", (T, self.nq * self.d), rt.dtype)
@@ -367,7 +401,6 @@ class GQAttention(Mixer):
         args = (q, cache.storage, attn, part_acc, part_ml)
         tail = (ctx.positions, meta["block_table"], meta["tok_part_row"])
         n_small, n_big = meta["n_small"], meta["n_big"]
-        family = self.kernel_family(cache.page_size)
         if family != "simt":
             tma = family == "tc"
             kernel = K.attention_tma if tma else K.attention_mma

@@ -100,20 +100,22 @@ def folders(tmp_path_factory):
 
 
 # bfloat16 against float32 (the plain implementation, or the engine's own float32 run), tiny models:
-# activations are rounded to 8 bits of mantissa after every part.  Two measures per logit row:
+# activations are rounded to 8 bits of mantissa after every part, and with widths of 64 to 128 and
+# matrices of standard deviation 0.1 the roundings do not average out.  Two measures per logit row:
 # the largest error as a share of the request's largest logit, and the root-mean-square error of
 # the row as a share of the row's root mean square.  The bounds are twice the worst that the replay
-# tests measured on a B200 over all shapes and cuts (TO BE SET from the first measured run).
-BF16_WORST = 0.05
-BF16_ROW_RMS = 0.05
+# tests measured on a B200 over all cuts, shape by shape (A 0.0110 / 0.0138, B 0.0176 / 0.0194,
+# C 0.0069 / 0.0087, D 0.0120 / 0.0150, E 0.0164 / 0.0205, F 0.0083 / 0.0104).
+BF16_BOUNDS = {"A": (0.022, 0.028), "B": (0.035, 0.039), "C": (0.014, 0.018), "D": (0.024, 0.030),
+               "E": (0.033, 0.041), "F": (0.017, 0.021)}
 
 
-def tolerances(dtype: str, ref: torch.Tensor) -> dict:
-    """float32: rounding of a different summation order.  bfloat16: 8 bits of mantissa through a
-    few layers, relative to the size of the logits."""
+def tolerances(dtype: str, ref: torch.Tensor, name: str) -> dict:
+    """float32: rounding of a different summation order.  bfloat16: the measured bound of the
+    shape ``name``, relative to the size of the request's logits."""
     if dtype == "float32":
         return dict(atol=3e-5, rtol=3e-5)
-    return dict(atol=BF16_WORST * float(ref.abs().max()), rtol=0.0)
+    return dict(atol=BF16_BOUNDS[name][0] * float(ref.abs().max()), rtol=0.0)
 
 
 def row_rms_error(got: torch.Tensor, ref: torch.Tensor) -> float:

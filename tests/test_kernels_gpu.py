@@ -522,6 +522,76 @@ def test_attention_tensor_core_splits_window_and_far_key(kernel):
     torch.testing.assert_close(out2, ref2, **tol(bf, 2))
 
 
+@pytest.mark.parametrize("nq,nkv,d,P_,nsplit,qkv_nsplit,rdim,interleaved,window", [
+    (28, 4, 128, 16, 8, 8, 128, False, None),       # the benchmark's shape: 7 heads per KV head, clusters of 8
+    (28, 4, 128, 16, 16, 3, 128, False, None),      # clusters of 16
+    (3, 1, 64, 32, 1, 1, 64, False, None),          # one share: nothing to merge
+    (32, 2, 128, 8, 5, 2, 64, True, None),          # 16 heads per KV head, interleaved pairs on half the head
+    (8, 8, 64, 64, 3, 4, 0, False, None),           # no rotation, one head per KV head, pages of a whole tile
+    (12, 4, 128, 4, 6, 1, 96, False, 300),          # a window, tiny pages
+])
+def test_attention_decode_fused(nq, nkv, d, P_, nsplit, qkv_nsplit, rdim, interleaved, window):
+    """The decode kernel that does everything between the q/k/v product and the output projection:
+    sums the product's parts, adds the bias, rotates, appends k and v to their pages, attends over
+    the cache and merges the key shares in its cluster.  Histories of 0, a few, one tile, and many
+    keys, some ending at a page's or a tile's edge; one far key among hundreds stands out."""
+    bf = torch.bfloat16
+    histories = [0, 5, 63, 64, 127, 700, 1023, 333]
+    T = len(histories)
+    theta = 10000.0
+    g = torch.Generator().manual_seed(3)
+    width_all = (nq + 2 * nkv) * d
+    parts = (torch.randn(qkv_nsplit, T, width_all, generator=g) / math.sqrt(qkv_nsplit)).to(DEV)
+    bias = (torch.randn(width_all, generator=g) * 0.1).to(DEV)
+    positions = torch.tensor(histories, dtype=torch.int32, device=DEV)
+    full = (parts.sum(0) + bias).cpu()
+    q = plain_rotation(full[:, : nq * d].view(T, nq, d), positions.cpu(), theta, rdim, interleaved).to(bf).float()
+    pages_of = [-(-(h + 1) // P_) for h in histories]
+    pool = sum(pages_of) + 5
+    perm = torch.randperm(pool, generator=g).tolist()
+    cache = torch.randn(pool, 2, nkv, P_, d, generator=g).to(bf).to(DEV)          # stale junk everywhere
+    table = torch.full((T, max(pages_of)), -1, dtype=torch.int32)
+    ks, vs = [], []
+    for i, h in enumerate(histories):
+        pages = [perm.pop() for _ in range(pages_of[i])]
+        table[i, : len(pages)] = torch.tensor(pages)
+        k = torch.randn(h, nkv, d, generator=g).to(bf)
+        v = torch.randn(h, nkv, d, generator=g).to(bf)
+        if h > 600:          # one far key that the first head of every group looks for: its score stands out
+            k[37] = (0.5 * q[i, :: nq // nkv]).to(bf)
+        for t in range(h):
+            cache[pages[t // P_], 0, :, t % P_] = k[t].to(DEV)
+            cache[pages[t // P_], 1, :, t % P_] = v[t].to(DEV)
+        ks.append(k), vs.append(v)
+    table = table.to(DEV)
+    inv = (theta ** (-torch.arange(0, rdim, 2).float() / rdim)).to(DEV) if rdim else None
+    before = cache.clone()
+    out = torch.full((T, nq * d), float("nan"), dtype=bf, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert K().attention_decode_supports(d, P_, nq // nkv, nsplit, rdim)
+    K().attention_decode(parts, bias, inv, cache, out, positions, table, nq=nq, nkv=nkv, d=d, page_size=P_,
+                         nsplit=nsplit, qkv_nsplit=qkv_nsplit, qkv_split_stride=parts.stride(0), rotary_dim=rdim,
+                         interleaved=interleaved, window=window or 0, status=status)
+    assert int(status) == 0
+    k_new = plain_rotation(full[:, nq * d: (nq + nkv) * d].view(T, nkv, d), positions.cpu(), theta, rdim, interleaved).to(bf)
+    v_new = full[:, (nq + nkv) * d:].view(T, nkv, d).to(bf)
+    touched = torch.zeros(pool, P_, dtype=torch.bool)
+    for i, h in enumerate(histories):
+        k_all = torch.cat((ks[i], k_new[i: i + 1])).float()
+        v_all = torch.cat((vs[i], v_new[i: i + 1])).float()
+        q_all = torch.zeros(h + 1, nq, d)
+        q_all[h] = q[i]
+        ref = P.causal_attention(q_all, k_all, v_all, window=window)[h].reshape(-1)
+        torch.testing.assert_close(out[i].float().cpu(), ref, **tol(bf, 2))
+        page = int(table[i, h // P_])
+        torch.testing.assert_close(cache[page, 0, :, h % P_].float().cpu(), k_new[i].float(), **tol(bf, 4))
+        torch.testing.assert_close(cache[page, 1, :, h % P_].float().cpu(), v_new[i].float(), **tol(bf, 4))
+        touched[page, h % P_] = True
+    # nothing but the tokens' own slots was written
+    same = (cache == before).all(-1).all(1).all(1).cpu()        # [pool, P]
+    assert bool(same[~touched].all())
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,d,P_", [(4, 2, 16, 16), (3, 1, 32, 32), (10, 2, 48, 16), (28, 4, 128, 16),
                                           (20, 1, 80, 8), (2, 2, 256, 16), (6, 3, 112, 7)])
