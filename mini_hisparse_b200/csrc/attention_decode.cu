@@ -59,7 +59,7 @@ struct Layout {
     static constexpr int KV_BYTES = KT * D * 2;
     static constexpr int STAGE_BYTES = 2 * KV_BYTES;
     static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-    static constexpr int MS = D + 2;                                    // a partial row: accumulator, max, sum
+    static constexpr int MS = D + 4;                                    // a partial row: accumulator, max, sum (16-byte rows)
     static constexpr int MERGE_BYTES = CWARPS * ROWS * MS * 4;          // the four warps' parts, in the ring
     static constexpr int PART_OFFSET = Q_BYTES + ((MERGE_BYTES + 1023) / 1024) * 1024;   // the CTA's part, in the ring
     static constexpr int PART_BYTES = ROWS * MS * 4;
@@ -166,6 +166,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const Decode
     constexpr int NT = 2;                       // each warp takes 16 of a tile's 64 keys
     constexpr int MS = L::MS;
     extern __shared__ uint8_t smem_raw[];
+    __shared__ int cta_failed;          // a bounded wait ran out somewhere in this CTA: it stores nothing
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
 
     pdl_launch_dependents();
@@ -198,6 +199,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const Decode
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), CWARPS); }
         mbar_fence_init();
+        cta_failed = 0;
     }
     __syncthreads();
 
@@ -226,21 +228,30 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const Decode
             prologue_sync();
             met = true;
         };
+        // Every page slot of a stage is filled: a slot past the last key (or before the first, inside
+        // a page that a window has given back) gets the page of key kv_begin again, so that the
+        // masked positions hold finite numbers.  The page ids of a tile are fetched one tile ahead:
+        // a look-up in the block table is a round trip to L2 that would otherwise sit between the
+        // release of a stage and its next copy.
+        const int spare = ntiles > 0 ? table[kv_begin / a.P] : -1;
+        auto page_of = [&](int itile) {
+            const int kp0 = tile_begin + itile * KT + lane * a.P;
+            return (lane < pages_per_tile && itile < ntiles && kp0 < kv_stop) ? table[kp0 / a.P] : -1;
+        };
+        int page_ahead = page_of(0);
         for (int itile = 0; itile < ntiles; ++itile) {
             const int stage = itile % STAGES;
             if (itile == STAGES) meet();
+            int page = page_ahead;
+            page_ahead = page_of(itile + 1);
             if (lane == 0) ok = mbar_wait(empty_bar(stage), ((itile / STAGES) & 1) ^ 1);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
-            // Every page slot of the stage is filled: a slot past the last key (or before the first,
-            // inside a page that a window has given back) gets the page of key kv_begin again, so
-            // that the masked positions hold finite numbers.
-            const int kp0 = tile_begin + itile * KT + lane * a.P;
-            int page = -1;
             if (lane < pages_per_tile) {
-                if (kp0 < kv_stop) page = table[kp0 / a.P];
-                if (page < 0 || page >= a.num_pages) page = table[kv_begin / a.P];
+                if (page < 0 || page >= a.num_pages) page = spare;
                 if (page >= a.num_pages) page = -1;
+            } else {
+                page = -1;
             }
             const unsigned have = __ballot_sync(0xffffffffu, page >= 0);
             if (lane == 0) mbar_expect_tx(full_bar(stage), __popc(have) * 2 * a.P * D * 2);
@@ -261,6 +272,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const Decode
             // nothing of ours may still be in flight when the ring is reused or the CTA leaves
             if (lane == 0)
                 for (int i = max(0, armed - STAGES); i < armed; ++i) mbar_wait(full_bar(i % STAGES), (i / STAGES) & 1);
+            if (lane == 0) cta_failed = 1;
             if (lane == 0 && a.status) atomicOr(a.status, 8);
         }
     } else {
@@ -328,9 +340,14 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const Decode
                 __syncwarp();
             }
 
-            float s[NT][4];
+            // scores: two accumulators per key group (even and odd steps along the head), so that the
+            // chain of dependent products is half as long; their sum is the score
+            float s[NT][4], s2[NT][4];
 #pragma unroll
-            for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+            for (int j = 0; j < NT; ++j) {
+                s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+                s2[j][0] = s2[j][1] = s2[j][2] = s2[j][3] = 0.f;
+            }
 #pragma unroll
             for (int k = 0; k < KSTEPS; k += 2) {
 #pragma unroll
@@ -339,8 +356,13 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const Decode
                     const int r = key0 + j * 8 + (lane & 7), c = k * 16 + 8 * (lane >> 3);
                     ldmatrix_x4(swz(k_s, KT, r, c), b0, b1, b2, b3);
                     mma_bf16(s[j], qf[k], b0, b1);
-                    mma_bf16(s[j], qf[k + 1], b2, b3);
+                    mma_bf16(s2[j], qf[k + 1], b2, b3);
                 }
+            }
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+#pragma unroll
+                for (int x = 0; x < 4; ++x) s[j][x] += s2[j][x];
             }
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -392,7 +414,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const Decode
             __syncwarp();
             if (lane == 0) mbar_arrive(empty_bar(stage));     // this warp is done with the stage
         }
-        if (!ok && lane == 0 && a.status) atomicOr(a.status, 8);
+        if (!ok && lane == 0) {
+            cta_failed = 1;
+            if (a.status) atomicOr(a.status, 8);
+        }
 
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -402,6 +427,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const Decode
         // the four warps' parts meet in the ring (every tile has been consumed; if a wait ran out the
         // TMA warp waits for its armed copies itself and nothing below is stored to global memory)
         compute_sync();
+        ok = cta_failed == 0;
         float* mg = (float*)(smem + L::Q_BYTES);
         if (ok) {
 #pragma unroll
@@ -409,43 +435,33 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const Decode
                 const int r = (lane >> 2) + 8 * h;
                 float* dst = mg + (warp * ROWS + r) * MS;
 #pragma unroll
-                for (int i = 0; i < DTILES; ++i) {
-                    dst[i * 8 + (lane & 3) * 2 + 0] = o[i][2 * h + 0];
-                    dst[i * 8 + (lane & 3) * 2 + 1] = o[i][2 * h + 1];
-                }
-                if ((lane & 3) == 0) { dst[D] = m_run[h]; dst[D + 1] = l_run[h]; }
+                for (int i = 0; i < DTILES; ++i)
+                    *(float2*)(dst + i * 8 + (lane & 3) * 2) = make_float2(o[i][2 * h + 0], o[i][2 * h + 1]);
+                if ((lane & 3) == 0) *(float2*)(dst + D) = make_float2(m_run[h], l_run[h]);
             }
         }
         compute_sync();
-        for (int idx = tid; idx < nrows * D; idx += CWARPS * 32) {
-            const int r = idx / D, e = idx - r * D;
+        // four columns of a row per thread and turn: the row's weights are worked out once per turn
+        for (int idx = tid; idx < nrows * (D / 4); idx += CWARPS * 32) {
+            const int r = idx / (D / 4), e = (idx - r * (D / 4)) * 4;
+            float2 ml[CWARPS];
+#pragma unroll
+            for (int w = 0; w < CWARPS; ++w) ml[w] = *(const float2*)(mg + (w * ROWS + r) * MS + D);
             float M = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < CWARPS; ++w) M = fmaxf(M, mg[(w * ROWS + r) * MS + D]);
-            float acc = 0.f, lsum = 0.f;
+            for (int w = 0; w < CWARPS; ++w) M = fmaxf(M, ml[w].x);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            float lsum = 0.f;
 #pragma unroll
             for (int w = 0; w < CWARPS; ++w) {
-                const float mw = mg[(w * ROWS + r) * MS + D];
-                const float wgt = mw == -INFINITY ? 0.f : exp2f((mw - M) * scale_log2);
-                acc += wgt * mg[(w * ROWS + r) * MS + e];
-                lsum += wgt * mg[(w * ROWS + r) * MS + D + 1];
+                const float wgt = ml[w].x == -INFINITY ? 0.f : exp2f((ml[w].x - M) * scale_log2);
+                const float4 v = *(const float4*)(mg + (w * ROWS + r) * MS + e);
+                acc.x += wgt * v.x; acc.y += wgt * v.y; acc.z += wgt * v.z; acc.w += wgt * v.w;
+                lsum += wgt * ml[w].y;
             }
-            if (!ok) { M = -INFINITY; acc = 0.f; lsum = 0.f; }
-            part[r * MS + e] = acc;
-            if (e == 0) { part[r * MS + D] = M; part[r * MS + D + 1] = lsum; }
-        }
-        if (owner && ok) {
-            // the token's own key and value go into their page for the steps to come
-            const int page = table[pos / a.P];
-            if (page < 0 || page >= a.num_pages) {
-                if (tid == 0 && a.status) atomicOr(a.status, 2);      // never write outside the pool
-            } else {
-                for (int c = tid; c < 2 * (D / 8); c += CWARPS * 32) {
-                    const int plane = c / (D / 8), ch = c % (D / 8);
-                    __nv_bfloat16* dst = a.cache + ((((size_t)page * 2 + plane) * a.nkv + kvh) * a.P + pos % a.P) * D;
-                    *(uint4*)(dst + ch * 8) = *(const uint4*)(kv_new + plane * D + ch * 8);
-                }
-            }
+            if (!ok) { M = -INFINITY; acc = make_float4(0.f, 0.f, 0.f, 0.f); lsum = 0.f; }
+            *(float4*)(part + r * MS + e) = acc;
+            if (e == 0) *(float2*)(part + r * MS + D) = make_float2(M, lsum);
         }
     }
 
@@ -482,6 +498,20 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const Decode
                     lsum += w * lp[p];
                 }
                 a.out[((size_t)t * a.nq + kvh * groups + r) * D + e] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+            }
+        }
+        if (owner && cta_failed == 0) {
+            // the token's own key and value go into their page for the steps to come (last, so that
+            // the peers do not wait for it at the barrier above)
+            const int page = table[pos / a.P];
+            if (page < 0 || page >= a.num_pages) {
+                if (tid == 0 && a.status) atomicOr(a.status, 2);      // never write outside the pool
+            } else {
+                for (int c = tid; c < 2 * (D / 8); c += CWARPS * 32) {
+                    const int plane = c / (D / 8), ch = c % (D / 8);
+                    __nv_bfloat16* dst = a.cache + ((((size_t)page * 2 + plane) * a.nkv + kvh) * a.P + pos % a.P) * D;
+                    *(uint4*)(dst + ch * 8) = *(const uint4*)(kv_new + plane * D + ch * 8);
+                }
             }
         }
     }
