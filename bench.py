@@ -9,6 +9,13 @@ context per request, timed on the device around K decode steps of the step funct
 out (its prompts are really prefilled); ``prefill`` times a 2,048-token prompt; ``roofline``
 relates the decode step to the bytes it has to read; ``points`` holds batch 1 and 64.
 For --gpus > 1 it prints one line that says so and exits with 2: this engine is single-GPU.
+
+    python bench.py --workload serving14b|long32b [--layers L]
+
+runs one of the two serving workloads instead and prints ITS one JSON line: 32 requests with prompts
+of 128 to 4,096 tokens in portions of 512 beside decoding at the Qwen2.5-14B shape, or 16 requests of
+8,192 prompt tokens plus 512 generated ones at the Qwen2.5-32B shape with the page pool sized from
+free memory; tokens a second, step-time percentiles, roofline fractions, clocks, and the layer count.
 """
 from __future__ import annotations
 
@@ -24,6 +31,7 @@ sys.path.insert(0, str(ROOT))
 
 # BASELINE.json configs[2]: Qwen2.5-7B shape, kept as data beside the package
 CONFIG_7B = json.loads((ROOT / "mini_hisparse_b200" / "configs" / "qwen2.5-7b-shape.json").read_text())
+WORKLOADS = {"serving14b": "qwen2.5-14b-shape.json", "long32b": "qwen2.5-32b-shape.json"}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 PAGE = 16
@@ -34,6 +42,20 @@ def reference_arm(args) -> int:
     from baseline.reference_arm import run_reference
 
     print(json.dumps(run_reference(CONFIG_7B, CONTEXT, args)))
+    return 0
+
+
+def workload(args) -> int:
+    from mini_hisparse_b200 import measure
+
+    config = json.loads((ROOT / "mini_hisparse_b200" / "configs" / WORKLOADS[args.workload]).read_text())
+    prompts, settings = measure.workload_prompts(args.workload, config["vocab_size"])
+    line = measure.serving_workload(config, prompts=prompts, layers=args.layers, page_size=PAGE,
+                                    label=args.workload, **settings)
+    line = {"metric": f"tokens/s of the {args.workload} workload (prompt and generated, through Engine.step)",
+            "value": line["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "impl": "ours",
+            **line}
+    print(json.dumps(line))
     return 0
 
 
@@ -48,6 +70,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the 28 of the config")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), help="run a serving workload instead of the decode bench")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -57,6 +80,8 @@ def main() -> int:
     if args.impl == "reference":
         return reference_arm(args)
     args.warmup = max(args.warmup, 3)
+    if args.workload:
+        return workload(args)
 
     import torch
 

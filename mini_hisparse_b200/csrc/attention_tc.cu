@@ -193,12 +193,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc(KT, false);      // S: N = 64 keys, both operands K-major
             constexpr uint32_t idesc_o = umma_idesc(D, true);        // O tile: N = head_dim, V is MN-major
+            // Descriptors are built once: a step inside a tile only moves the address field (units of 16
+            // bytes; the tiles are 1024-byte aligned, so the field never carries).  This thread runs
+            // alone in its warp, and every dependent instruction it saves is four or five cycles per MMA.
+            const uint64_t q_desc = smem_desc_kmajor(q_s), k_desc0 = smem_desc_kmajor(k_ring);
+            const uint64_t v_desc0 = smem_desc_mnmajor(v_ring, KT * 128, 1024);
             auto issue_s = [&](int j) {
-                const uint32_t k_s = k_ring + (j % K_STAGES) * L::K_BYTES;
+                const uint64_t k_desc = k_desc0 + (uint64_t)((j % K_STAGES) * (L::K_BYTES / 16));
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
-                    const uint64_t da = smem_desc_kmajor(q_s + (k >> 2) * (ROWS * 128) + (k & 3) * 32);
-                    const uint64_t db = smem_desc_kmajor(k_s + (k >> 2) * (KT * 128) + (k & 3) * 32);
+                    const uint64_t da = q_desc + (uint64_t)(((k >> 2) * (ROWS * 128) + (k & 3) * 32) / 16);
+                    const uint64_t db = k_desc + (uint64_t)(((k >> 2) * (KT * 128) + (k & 3) * 32) / 16);
                     umma_bf16(tmem + (j & 1) * KT, da, db, idesc_s, k > 0 ? 1u : 0u);
                 }
                 umma_commit(s_full(j & 1));
@@ -214,12 +219,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
                 if (ok && j + 2 < ntiles) ok = mbar_wait(k_full((j + 2) % K_STAGES), ((j + 2) / K_STAGES) & 1);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t v_s = v_ring + (j % V_STAGES) * L::K_BYTES;
+                const uint64_t v_desc = v_desc0 + (uint64_t)((j % V_STAGES) * (L::K_BYTES / 16));
 #pragma unroll
-                for (int k = 0; k < KT / 16; ++k) {
-                    const uint64_t db = smem_desc_mnmajor(v_s + k * 16 * 128, KT * 128, 1024);
-                    umma_bf16_tmem_a(tmem + 128, tmem + (j & 1) * KT + k * 8, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-                }
+                for (int k = 0; k < KT / 16; ++k)
+                    umma_bf16_tmem_a(tmem + 128, tmem + (j & 1) * KT + k * 8, v_desc + (uint64_t)(k * 16 * 128 / 16), idesc_o,
+                                     (j > 0 || k > 0) ? 1u : 0u);
                 umma_commit(o_done(j & 1));             // O holds tiles 0..j and V(j) is consumed when this completes
                 if (j + 1 == ntiles) umma_commit(o_final);
                 if (j + 2 < ntiles) issue_s(j + 2);

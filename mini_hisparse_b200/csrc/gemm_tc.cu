@@ -125,6 +125,13 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
     d |= (uint64_t)2 << 61;                           // layout: 128-byte swizzle
     return d;
 }
+// A step of 16 elements along K inside a 128-byte swizzled row moves the start address by 32 bytes,
+// i.e. the descriptor's address field (units of 16 bytes) by 2.  The tiles are 1024-byte aligned and
+// the steps stay inside a row, so the field never carries: a descriptor is built once per tile and
+// stepped with one addition (the thread that issues the MMAs runs alone in its warp; every dependent
+// instruction it saves is four or five cycles per MMA).
+__device__ __forceinline__ uint64_t desc_step(uint64_t desc, int k) { return desc + (uint64_t)(k * (UMMA_K * 2 / 16)); }
+
 // Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = BN.
 __host__ __device__ constexpr uint32_t make_idesc(int bn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -235,13 +242,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t a_addr = smem_base + s * S::STAGE_BYTES;
-                const uint32_t b_addr = a_addr + S::A_BYTES;
+                const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + S::A_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    const uint64_t da = make_smem_desc(a_addr + k * UMMA_K * 2);
-                    const uint64_t db = make_smem_desc(b_addr + k * UMMA_K * 2);
-                    umma_bf16(tmem_base, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
-                }
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    umma_bf16(tmem_base, desc_step(da, k), desc_step(db, k), idesc, (i > 0 || k > 0) ? 1u : 0u);
                 umma_commit(empty_bar(s));       // frees the stage when these MMAs have read it
             }
             if (ok) umma_commit(tmem_full_bar);  // the accumulator is complete
@@ -498,6 +502,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = make_idesc(bn);
+            // the operand descriptors of stage 0, built once; stage s is S::STAGE_BYTES / 16 address units on
+            const uint64_t desc_a0 = make_smem_desc(smem_base), desc_b0 = make_smem_desc(smem_base + S::A_BYTES);
             int it = 0, t, kb0, kb1, entry;
             for (int j = 0; ok && segment(j, t, kb0, kb1, entry); ++j) {
                 const int b = j & 1;
@@ -517,12 +523,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         if (h < n) {
-                            const uint32_t a_addr = smem_base + (h ? s1 : s0) * S::STAGE_BYTES;
-                            const uint32_t b_addr = a_addr + S::A_BYTES;
+                            const uint64_t step = (uint64_t)((h ? s1 : s0) * (S::STAGE_BYTES / 16));
+                            const uint64_t da = desc_a0 + step, db = desc_b0 + step;
 #pragma unroll
                             for (int k = 0; k < BK / UMMA_K; ++k)
-                                umma_bf16(acc, make_smem_desc(a_addr + k * UMMA_K * 2), make_smem_desc(b_addr + k * UMMA_K * 2),
-                                          idesc, (kb + h > kb0 || k > 0) ? 1u : 0u);
+                                umma_bf16(acc, desc_step(da, k), desc_step(db, k), idesc, (kb + h > kb0 || k > 0) ? 1u : 0u);
                             umma_commit(empty_bar(h ? s1 : s0));
                         }
                     }

@@ -75,6 +75,7 @@ class Engine:
                                    model.spec.vocab_size, model.spec.max_positions, eos)
         self.sampler = Sampler(model.rt.device, max_rows=cache_config.max_requests)
         self.timeline: list[dict] = []
+        self.last_step: list[tuple] = []
 
     # ---- the reference's five calls ------------------------------------------------------------
     @property
@@ -104,6 +105,9 @@ class Engine:
         planned = self.scheduler.plan()
         if not planned:
             return []
+        # what this step holds, for whoever measures it: (request, cached positions before, new tokens)
+        self.last_step = [(p.request.request_id, self.cache.length(p.request.request_id), len(p.tokens))
+                          for p in planned]
         try:
             sampled = self._run(planned)
         except StepError:

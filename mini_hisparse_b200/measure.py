@@ -197,3 +197,122 @@ def decode_benchmark(config: dict, *, batch=8, prompt_tokens=1024, steps=20, war
             "tokens_per_second": r["tokens_per_s"], "ms_per_step": r["ms_per_step"],
             "bytes_per_step": nbytes, "achieved_gbs": gbs,
             "hbm_fraction": gbs / p["hbm_gbs"], "peak_source": p["source"], "clocks": r["clocks"]}
+
+
+# ---- serving workloads: requests through Engine.step(), host tokens in and out -----------------------
+def step_flops(cfg, layers: int, segments: list[tuple[int, int]], logit_rows: int) -> float:
+    """Floating-point operations of one step: 2 per weight element and token for the products, 4 d per
+    (query head, query, key) pair for attention; ``segments`` holds (cached positions, new tokens)."""
+    H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    q, kv = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+    per_token = 2 * (H * (q + 2 * kv) + q * H + 3 * H * I)
+    tokens = sum(n for _, n in segments)
+    pairs = sum(n * start + n * (n + 1) // 2 for start, n in segments)
+    return layers * (per_token * tokens + 4 * q * pairs) + 2 * H * V * logit_rows
+
+
+def _percentile(sorted_values, p):
+    if not sorted_values:
+        return None
+    return sorted_values[min(len(sorted_values) - 1, int(p / 100.0 * len(sorted_values)))]
+
+
+def serving_workload(config: dict, *, prompts: list[list[int]], max_new_tokens: int, max_tokens_per_step: int,
+                     context: int, page_size: int = 16, dtype="bfloat16", device="cuda:0", weight_seed: int = 0,
+                     layers: int | None = None, num_pages: int | None = None, label: str = "") -> dict:
+    """Run ``prompts`` through the engine as a server would: all requests are queued at once, the
+    scheduler cuts the prompts into portions of at most ``max_tokens_per_step`` tokens beside the
+    decode tokens of the requests that are already generating, greedy sampling, until every request
+    has ``max_new_tokens`` tokens.  Wall-clock times per step (host work included: this is what a
+    client sees), and for the whole run the bytes that had to be read (every weight once per step and
+    the cache of the step's requests) and the floating-point operations, against the measured peaks.
+
+    ``num_pages`` None sizes the pool for the requests' whole lifetimes; "free" takes what the device
+    has left after the weights (less a reserve for the step's workspace)."""
+    from .config.registry import resolve
+    from .engine.engine import Engine, load_model
+
+    config = dict(config)
+    full_layers = config["num_hidden_layers"]
+    if layers is not None:
+        config["num_hidden_layers"] = layers
+    layers = config["num_hidden_layers"]
+    cfg, _ = resolve(config)
+    model = load_model(config, device=device, dtype=dtype, random_seed=weight_seed)
+    need_pages = sum(-(-(len(p) + max_new_tokens) // page_size) for p in prompts)
+    probe_engine_pages = need_pages
+    if num_pages == "free":
+        torch.cuda.synchronize()
+        free, _total = torch.cuda.mem_get_info(torch.device(device))
+        kv_heads, d = cfg.num_key_value_heads, cfg.head_dim
+        page_bytes = layers * 2 * kv_heads * page_size * d * (2 if dtype == "bfloat16" else 4)
+        reserve = 6 << 30                       # logits, activations and plans of the largest step
+        probe_engine_pages = max(need_pages, int((free - reserve) // page_bytes))
+    elif num_pages is not None:
+        probe_engine_pages = num_pages
+    engine = Engine(model, num_pages=probe_engine_pages, page_size=page_size, max_requests=len(prompts),
+                    max_tokens_per_step=max_tokens_per_step)
+    for i, prompt in enumerate(prompts):
+        engine.add_request(f"r{i}", prompt, max_new_tokens=max_new_tokens)
+    weights = decode_bytes(model, engine.cache, 0)
+    kv_per_token = sum(g.page_bytes() // page_size for g in engine.cache.page_groups)
+    step_ms, kinds, read_bytes, flops = [], [], 0, 0.0
+    generated = prompt_tokens = 0
+    torch.cuda.synchronize()
+    with ClockSampler() as clocks:
+        t_start = time.perf_counter()
+        while not engine.scheduler.idle:
+            t0 = time.perf_counter()
+            emitted = engine.step()
+            step_ms.append((time.perf_counter() - t0) * 1e3)
+            generated += len(emitted)
+            segs = [(start, n) for _, start, n in engine.last_step]
+            kinds.append("decode" if all(n == 1 for _, n in segs) else "mixed")
+            read_bytes += weights + kv_per_token * sum(start + n for start, n in segs)
+            flops += step_flops(cfg, layers, segs, len(emitted))
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t_start
+    engine.runner.check_status()
+    prompt_tokens = sum(len(p) for p in prompts)
+    p = peaks()
+    ordered = sorted(step_ms)
+    decode_ms = sorted(ms for ms, k in zip(step_ms, kinds) if k == "decode")
+    mixed_ms = sorted(ms for ms, k in zip(step_ms, kinds) if k == "mixed")
+    gbs, tflops = read_bytes / seconds / 1e9, flops / seconds / 1e12
+    hbm_frac, flop_frac = gbs / p["hbm_gbs"], tflops / p["bf16_tflops_sustained"]
+    snap = engine.snapshot()
+    return {
+        "workload": label, "requests": len(prompts), "prompt_tokens": prompt_tokens, "generated_tokens": generated,
+        "max_new_tokens": max_new_tokens, "max_tokens_per_step": max_tokens_per_step, "context": context,
+        "layers": layers, "layers_of_config": full_layers, "dtype": dtype, "page_size": page_size,
+        "seconds": seconds, "generated_tokens_per_s": generated / seconds,
+        "tokens_per_s": (generated + prompt_tokens) / seconds, "steps": len(step_ms),
+        "step_ms": {"p50": _percentile(ordered, 50), "p90": _percentile(ordered, 90), "p99": _percentile(ordered, 99),
+                    "max": ordered[-1] if ordered else None},
+        "decode_step_ms": {"steps": len(decode_ms), "p50": _percentile(decode_ms, 50), "p99": _percentile(decode_ms, 99)},
+        "mixed_step_ms": {"steps": len(mixed_ms), "p50": _percentile(mixed_ms, 50), "p99": _percentile(mixed_ms, 99)},
+        "roofline": {"bound": "hbm" if hbm_frac >= flop_frac else "bf16", "hbm": {"achieved": gbs, "peak": p["hbm_gbs"],
+                     "unit": "GB/s", "frac": hbm_frac}, "bf16": {"achieved": tflops, "peak": p["bf16_tflops_sustained"],
+                     "unit": "TFLOP/s (sustained)", "frac": flop_frac}, "frac": max(hbm_frac, flop_frac),
+                     "peaks": f"of {p['source']}"},
+        "clocks": clocks.result, "pages": snap["cache"]["page_groups"][0]["pages_total"],
+        "pages_peak": snap["cache"]["page_groups"][0]["pages_peak"], "gpu_launches": K.launches,
+        "data": "synthetic: seeded random weights, uniform-random token ids",
+    }
+
+
+def workload_prompts(name: str, vocab: int, seed: int = 0) -> tuple[list[list[int]], dict]:
+    """The token ids and settings of the two named serving workloads."""
+    g = torch.Generator().manual_seed(seed)
+    if name == "serving14b":
+        # 32 requests, prompts of 128 to 4,096 uniform-random tokens, portions of 512 beside decoding
+        lengths = torch.randint(128, 4097, (32,), generator=g).tolist()
+        settings = dict(max_new_tokens=128, max_tokens_per_step=512, context=8192, num_pages=None)
+    elif name == "long32b":
+        # 16 requests of 8,192 prompt tokens and 512 generated ones, the pool sized from free memory
+        lengths = [8192] * 16
+        settings = dict(max_new_tokens=512, max_tokens_per_step=2048, context=16384, num_pages="free")
+    else:
+        raise ValueError(f"unknown workload {name!r}: serving14b or long32b")
+    prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
+    return prompts, settings
