@@ -71,7 +71,7 @@ struct Layout {
     static constexpr int K_OFFSET = Q_BYTES;
     static constexpr int V_OFFSET = K_OFFSET + K_STAGES * K_BYTES;
     static constexpr int BAR_OFFSET = V_OFFSET + V_STAGES * K_BYTES;
-    static constexpr int NUM_BARS = 2 * K_STAGES + 1 + 2 + 2 + 3;   // k full/empty, q, s full, p+v full, o done, o final
+    static constexpr int NUM_BARS = 2 * K_STAGES + 1 + 2 + 2 + 3 + 1;   // k full/empty, q, s full, p+v full, o done, o final, drain
     static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16;
     static constexpr int TMEM_COLS = 256;                      // S/P: 2 x 64 columns, O tile: D columns from column 128
 };
@@ -109,6 +109,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
     // not in step with the value warp and a parity wait cannot tell phases two apart
     auto o_done = [&](int b) { return bars + 8 * (B0 + 5 + b); };
     const uint32_t o_final = bars + 8 * (B0 + 7);     // the last P V has completed
+    const uint32_t drain = bars + 8 * (B0 + 8);       // only used when a wait has run out (see the MMA warp)
     uint32_t* tmem_slot = (uint32_t*)(smem + L::BAR_OFFSET + 8 * L::NUM_BARS);
 
     pdl_launch_dependents();
@@ -140,6 +141,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
         for (int b = 0; b < 2; ++b) mbar_init(pv_full(b), 5);
         for (int b = 0; b < 2; ++b) mbar_init(o_done(b), 1);
         mbar_init(o_final, 1);
+        mbar_init(drain, 1);
         mbar_fence_init();
     }
     if (warp == 1) tmem_alloc(smem_addr(tmem_slot), L::TMEM_COLS);
@@ -158,6 +160,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
         const bool values = warp == 6;
         const int pages_per_tile = KT / a.P;
         const int stages = values ? V_STAGES : K_STAGES;
+        int armed = 0;
         for (int j = 0; j < ntiles && ok; ++j) {
             const int stage = j % stages;
             const uint32_t full = values ? pv_full(stage) : k_full(stage);
@@ -181,6 +184,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h) tma_load_2d(dst + h * KT * 128, &kv_map, h * 64, row0, full);
             }
+            armed = j + 1;
+        }
+        if (!ok && lane == 0 && !values) {
+            // a wait ran out: the key copies this warp armed must have landed before the CTA leaves (a
+            // value tile's barrier also counts the softmax warps' arrivals, so its copies are waited
+            // for by time alone: the same bounded wait on the last key stage covers them, since the
+            // value warp armed them no later)
+            for (int i = max(0, armed - K_STAGES); i < armed; ++i) mbar_wait(k_full(i % K_STAGES), (i / K_STAGES) & 1);
         }
     } else if (warp == 1) {
         // ---- MMA warp ----------------------------------------------------------------------------------
@@ -227,6 +238,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs a
                 umma_commit(o_done(j & 1));             // O holds tiles 0..j and V(j) is consumed when this completes
                 if (j + 1 == ntiles) umma_commit(o_final);
                 if (j + 2 < ntiles) issue_s(j + 2);
+            }
+            if (!ok) {
+                // leaving early: tensor memory must not be freed under a product that still runs
+                umma_commit(drain);
+                mbar_wait(drain, 0);
             }
         }
     } else {

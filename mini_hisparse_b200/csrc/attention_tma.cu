@@ -77,6 +77,7 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
     constexpr int NT = SPLIT_KEYS ? 2 : 8;
     extern __shared__ uint8_t smem_raw[];
     __shared__ int row_pos[ROWS];
+    __shared__ int cta_failed;      // a bounded wait ran out somewhere in this CTA: it merges and stores nothing
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
 
     // Programmatic dependent launch: this kernel may start while the append of this step's keys
@@ -105,6 +106,7 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), CWARPS); }
         mbar_fence_init();
+        cta_failed = 0;
     }
     __syncthreads();
 
@@ -112,6 +114,7 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
         // ---- TMA warp: one lane per page of the tile ----------------------------------------------
         const int pages_per_tile = KT / a.P;
         bool ok = true, waited = false;
+        int armed = 0;
         const int first_fresh = a.fresh > 0 ? a.positions[tok0] - (a.fresh - 1) : -0x7fffffff;
         for (int itile = 0; itile < ntiles && ok; ++itile) {
             const int stage = itile % STAGES;
@@ -145,8 +148,15 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
                     tma_load_2d(dst + L::KV_BYTES + h * KT * 128, &kv_map, h * 64, row0 + a.nkv * a.P, full_bar(stage));
                 }
             }
+            armed = itile + 1;
         }
-        if (!ok && lane == 0 && a.status) atomicOr(a.status, 8);
+        if (!ok && lane == 0) {
+            // Nothing of ours may still be in flight when the CTA leaves (the copies would land in shared
+            // memory that belongs to the next CTA on this SM): wait, bounded again, for the armed stages.
+            cta_failed = 1;
+            for (int i = max(0, armed - STAGES); i < armed; ++i) mbar_wait(full_bar(i % STAGES), (i / STAGES) & 1);
+            if (a.status) atomicOr(a.status, 8);
+        }
         return;
     }
 
@@ -257,8 +267,12 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
         if (lane == 0) mbar_arrive(empty_bar(stage));     // this warp is done with the stage
     }
     // A wait that ran out is reported; the warp still walks through the barriers below so that
-    // the others are not left waiting for it (what it writes is inside its own rows either way).
-    if (!ok && lane == 0 && a.status) atomicOr(a.status, 8);
+    // the others are not left waiting for it, but the CTA then merges and stores nothing: the ring
+    // may still receive copies (the TMA warp waits for them before it leaves).
+    if (!ok && lane == 0) {
+        cta_failed = 1;
+        if (a.status) atomicOr(a.status, 8);
+    }
 
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -267,6 +281,7 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
     }
     if (SPLIT_KEYS) {
         compute_sync();     // all warps are past their last tile: the ring can become merge scratch
+        if (cta_failed) return;
         float* mg = (float*)smem;
         constexpr int MS = D + 2;
 #pragma unroll
@@ -378,6 +393,7 @@ attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnArgs 
             }
         }
     } else {
+        if (!ok) return;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int row = wrow + (lane >> 2) + 8 * h;

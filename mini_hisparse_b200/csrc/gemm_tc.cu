@@ -22,7 +22,11 @@
 // but a K block of four MMAs costs 480 cycles as soon as the loop waits on a barrier, whatever
 // N): tiles narrower than 256 are not faster per K block, only their last round may fit better.
 // Every wait on an mbarrier is bounded; a wait that runs out sets bit 4 of *status and the CTA
-// leaves through the common exit, which frees its tensor memory.
+// leaves through the common exit, which frees its tensor memory.  What holds on that path: the
+// thread that issued MMAs commits them to a barrier of its own and waits (bounded) for it before
+// the CTA's final barrier, so tensor memory is not freed under a product that still runs; the
+// TMA warp waits (bounded) for the stages it armed, so no copy lands in shared memory that the
+// SM's next CTA owns; and the epilogue stores nothing once its wait has run out.
 #include <cuda.h>
 #include <climits>
 #include <map>
@@ -54,8 +58,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 // Bounded wait: false if the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = WAIT_LIMIT) {
+    for (uint32_t i = 0; i < limit; ++i) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -143,7 +147,7 @@ struct Smem {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BARRIER_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int TOTAL = BARRIER_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;   // + alignment slack
+    static constexpr int TOTAL = BARRIER_OFFSET + (2 * STAGES + 2) * 8 + 16 + 1024;   // + alignment slack
 };
 
 template <typename OT> __device__ __forceinline__ void store_out(OT* p, float v);
@@ -171,7 +175,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     auto full_bar = [&](int s) { return bar_base + 8 * s; };
     auto empty_bar = [&](int s) { return bar_base + 8 * (STAGES + s); };
     const uint32_t tmem_full_bar = bar_base + 8 * (2 * STAGES);
-    uint32_t* tmem_slot = (uint32_t*)(smem + S::BARRIER_OFFSET + 8 * (2 * STAGES + 1));
+    const uint32_t drain_bar = bar_base + 8 * (2 * STAGES + 1);      // only used when a wait has run out
+    uint32_t* tmem_slot = (uint32_t*)(smem + S::BARRIER_OFFSET + 8 * (2 * STAGES + 2));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ra0 = blockIdx.x * BM, rb0 = blockIdx.y * BN;
@@ -184,6 +189,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         mbar_init(tmem_full_bar, 1);
+        mbar_init(drain_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -248,7 +254,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     umma_bf16(tmem_base, desc_step(da, k), desc_step(db, k), idesc, (i > 0 || k > 0) ? 1u : 0u);
                 umma_commit(empty_bar(s));       // frees the stage when these MMAs have read it
             }
-            if (ok) umma_commit(tmem_full_bar);  // the accumulator is complete
+            if (ok) {
+                umma_commit(tmem_full_bar);      // the accumulator is complete
+            } else {
+                umma_commit(drain_bar);          // leaving early: not before what was issued has run
+                mbar_wait(drain_bar, 0);
+            }
         }
     } else {
         // epilogue: warp w reads TMEM lanes 32*(w%4) .. +31 = rows of the A operand
@@ -385,7 +396,7 @@ struct PSmem {
     static constexpr int B_BYTES = P_BN_MAX * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BARRIER_OFFSET = P_STAGES * STAGE_BYTES;
-    static constexpr int TOTAL = BARRIER_OFFSET + (2 * P_STAGES + 4) * 8 + 16 + 1024;
+    static constexpr int TOTAL = BARRIER_OFFSET + (2 * P_STAGES + 5) * 8 + 16 + 1024;
 };
 
 // Epilogue 2: the tile is a run of tokens x two (head size 128) or four (head size 64) heads of the
@@ -411,7 +422,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                           OT* __restrict__ C, int Ra, int Rb, int K, long long ldc, int bn, int tiles_m,
                           int whole_tiles, int tail_tiles, int ways, float* __restrict__ partials,
-                          int* __restrict__ flags, int* __restrict__ status, const QkvRopeArgs qr) {
+                          int* __restrict__ flags, int* __restrict__ status, const QkvRopeArgs qr,
+                          const uint32_t wait_limit) {
     using S = PSmem;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -421,8 +433,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     auto empty_bar = [&](int s) { return bar_base + 8 * (P_STAGES + s); };
     auto acc_full_bar = [&](int b) { return bar_base + 8 * (2 * P_STAGES + b); };
     auto acc_empty_bar = [&](int b) { return bar_base + 8 * (2 * P_STAGES + 2 + b); };
-    uint32_t* tmem_slot = (uint32_t*)(smem + S::BARRIER_OFFSET + 8 * (2 * P_STAGES + 4));
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t drain_bar = bar_base + 8 * (2 * P_STAGES + 4);       // only used when a wait has run out
+    uint32_t* tmem_slot = (uint32_t*)(smem + S::BARRIER_OFFSET + 8 * (2 * P_STAGES + 5));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_kb = (K + BK - 1) / BK;
     // First the ways * tail_tiles parts of the tiles [whole_tiles, + tail_tiles) (entry e is part
     // e / tail_tiles of tile e % tail_tiles), then the tiles [0, whole_tiles) as whole tiles, both
@@ -452,6 +465,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     if (threadIdx.x == 0) {
         for (int s = 0; s < P_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 4); }
+        mbar_init(drain_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -486,7 +500,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                         tma_load_2d(a_dst, &map_a, kb * BK, ra0, full_bar(s));
                         continue;
                     }
-                    ok = mbar_wait(empty_bar(s), ((it / P_STAGES) & 1) ^ 1);
+                    ok = mbar_wait(empty_bar(s), ((it / P_STAGES) & 1) ^ 1, wait_limit);
                     if (!ok) break;
                     mbar_expect_tx(full_bar(s), stage_tx);
                     tma_load_2d(a_dst, &map_a, kb * BK, ra0, full_bar(s));
@@ -496,7 +510,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             // nothing of ours may still be in flight when the CTA leaves: wait for the last stages
             for (int back = 1; back <= P_STAGES && back <= it; ++back) {
                 const int i = it - back;
-                mbar_wait(full_bar(i % P_STAGES), (i / P_STAGES) & 1);
+                mbar_wait(full_bar(i % P_STAGES), (i / P_STAGES) & 1, wait_limit);
             }
         }
     } else if (warp == 1) {
@@ -507,7 +521,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             int it = 0, t, kb0, kb1, entry;
             for (int j = 0; ok && segment(j, t, kb0, kb1, entry); ++j) {
                 const int b = j & 1;
-                ok = mbar_wait(acc_empty_bar(b), ((j >> 1) & 1) ^ 1);     // the epilogue has read this buffer
+                ok = mbar_wait(acc_empty_bar(b), ((j >> 1) & 1) ^ 1, wait_limit);     // the epilogue has read this buffer
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc = tmem_base + b * P_BN_MAX;
@@ -516,7 +530,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 // landed as well, both are issued in one round (never waiting for the second).
                 for (int kb = kb0; kb < kb1 && ok;) {
                     const int s0 = it % P_STAGES, s1 = (it + 1) % P_STAGES;
-                    ok = mbar_wait(full_bar(s0), (it / P_STAGES) & 1);
+                    ok = mbar_wait(full_bar(s0), (it / P_STAGES) & 1, wait_limit);
                     if (!ok) break;
                     const int n = (kb1 - kb >= 2 && mbar_test(full_bar(s1), ((it + 1) / P_STAGES) & 1)) ? 2 : 1;
                     tc_fence_after();
@@ -535,6 +549,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                     it += n;
                 }
                 if (ok) umma_commit(acc_full_bar(b));
+            }
+            if (!ok) {
+                umma_commit(drain_bar);          // leaving early: not before what was issued has run
+                mbar_wait(drain_bar, 0, wait_limit);
             }
         }
     } else {
@@ -595,8 +613,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             const int ts = whole_tiles + tail_index, parts = ways;
             const volatile int* flag = flags + 4 * ts + quarter;
             uint32_t spins = 0;
-            while (*flag < parts && ++spins < WAIT_LIMIT) __nanosleep(32);
-            if (spins >= WAIT_LIMIT) { ok = false; break; }
+            while (*flag < parts && ++spins < wait_limit) __nanosleep(32);
+            if (spins >= wait_limit) { ok = false; break; }
             __threadfence();
             const int ra0 = (ts % tiles_m) * BM, rb0 = (ts / tiles_m) * bn;
 #pragma unroll 1
@@ -665,7 +683,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             if (j < my_parts) segment(j, t, kb0, kb1, entry);
             const int b = j & 1;
             const int ra0 = (t % tiles_m) * BM, rb0 = (t / tiles_m) * bn;
-            ok = mbar_wait(acc_full_bar(b), (j >> 1) & 1);
+            ok = mbar_wait(acc_full_bar(b), (j >> 1) & 1, wait_limit);
             if (!ok) break;
             tc_fence_after();
             const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + b * P_BN_MAX;
@@ -954,6 +972,9 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* C, i
     return fail("gemm_tc: no tile for BN %d", bn);
 }
 
+// Iterations a bounded wait of the persistent product may take; tests shorten it to see a wait run out.
+uint32_t g_wait_limit = WAIT_LIMIT;
+
 // Tile width (multiple of 16, 128..256; for the SwiGLU epilogue a multiple of 32) that wastes the
 // least of the last round of whole tiles on `sms` persistent CTAs.
 int choose_persistent_bn(int tiles_m, int N, int sms, int step) {
@@ -1029,10 +1050,19 @@ int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K
     }
     QkvRopeArgs none = {};
     launch_kernel(kern, dim3((unsigned)grid), dim3(THREADS), PSmem::TOTAL, stream, ma, mb, (OT*)C, M, N, K, ldc, bn,
-                  tiles_m, (int)whole_tiles, (int)tail_tiles, ways, partials, flags, status, qr ? *qr : none);
+                  tiles_m, (int)whole_tiles, (int)tail_tiles, ways, partials, flags, status, qr ? *qr : none, g_wait_limit);
     return check_launch("gemm_tc_persistent");
 }
 }  // namespace
+
+// The iteration limit of the persistent product's bounded waits (0: the default).  For tests that make a
+// wait run out on purpose (a flag that nothing sets): with a short limit the kernel gives up within
+// milliseconds, sets bit 4 of the status word and leaves in order.  Returns the limit that was in force.
+MHB_EXPORT unsigned mhb_gemm_tc_wait_limit(unsigned limit) {
+    const unsigned before = g_wait_limit;
+    g_wait_limit = limit ? limit : WAIT_LIMIT;
+    return before;
+}
 
 // C[M, N] = X[M, K] * W[N, K]^T, bfloat16 in, float32 accumulation, C float32 or bfloat16.
 // swap != 0 streams W through the 128-row operand (few tokens); bn is the tile width along the

@@ -183,6 +183,24 @@ def _scratch_ptrs(scratch):
     return _ptr(partials), _ptr(flags)
 
 
+class gemm_tc_wait_limit:
+    """Inside the block the bounded waits of the persistent product give up after ``limit`` iterations
+    instead of about a million: for tests that make a wait run out on purpose (a flag that nothing
+    sets) and check that the kernel reports it (status bit 4) and leaves in order."""
+
+    def __init__(self, limit: int):
+        self.limit = limit
+
+    def __enter__(self):
+        lib = build.load("gemm_tc")
+        lib.mhb_gemm_tc_wait_limit.restype = ctypes.c_uint
+        self.before = lib.mhb_gemm_tc_wait_limit(ctypes.c_uint(self.limit))
+        return self
+
+    def __exit__(self, *exc):
+        build.load("gemm_tc").mhb_gemm_tc_wait_limit(ctypes.c_uint(self.before))
+
+
 def gemm_tc(a, w, out, *, swap: bool, bn: int, nsplit=1, split_stride=0, status=None, scratch=None):
     """out[M, N] = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulate).
 

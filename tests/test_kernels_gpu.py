@@ -180,6 +180,33 @@ def test_gemm_persistent(M, N, K_, shared, out_dtype):
         torch.testing.assert_close(outs[0], ref, atol=1e-2 * float(ref.abs().max()), rtol=1e-2)
 
 
+def test_gemm_persistent_wait_that_runs_out_is_reported_and_the_kernel_stays_usable():
+    """A bounded wait made to run out by a flag that nothing sets: the counters through which the CTAs
+    that share a tile's K range meet are preset so that their count is never reached.  With a short
+    limit the CTAs give up within milliseconds: status bit 4 is set, the kernel returns (its MMAs
+    drained, its copies landed, its tensor memory freed), and after the flags are put back to zero
+    (what the runner does after such an error) the same product is right again."""
+    M, N, K_ = 2300, 2304, 8960                       # its last round of tiles is shared eight ways along K
+    a = rnd(M, K_, dtype=torch.bfloat16, seed=1)
+    w = rnd(N, K_, dtype=torch.bfloat16, seed=2)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scratch = K().stream_k_scratch(DEV)
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    scratch[1].fill_(-1000)
+    with K().gemm_tc_wait_limit(2000):
+        K().gemm_tc(a, w, out, swap=False, bn=0, status=status, scratch=scratch)
+        torch.cuda.synchronize()
+    assert int(status) & 4
+    from mini_hisparse_b200.engine.step import ModelRunner
+    assert "tensor-core matrix product" in ModelRunner.status_message(int(status))
+    status.zero_()
+    scratch[1].zero_()
+    K().gemm_tc(a, w, out, swap=False, bn=0, status=status, scratch=scratch)
+    assert int(status) == 0 and int(scratch[1].abs().sum()) == 0
+    ref = a.float() @ w.float().T
+    torch.testing.assert_close(out.float(), ref, atol=1e-2 * float(ref.abs().max()), rtol=1e-2)
+
+
 @pytest.mark.parametrize("M,I,K_,swap,bn", [(200, 176, 64, False, 256), (2048, 1184, 512, False, 256),
                                               (200, 176, 64, False, 0), (2048, 1184, 512, False, 0), (130, 2000, 3584, False, 0),
                                               (2048, 1312, 8192, False, 0),

@@ -174,3 +174,14 @@ def test_engine_fails_the_requests_of_a_step_that_raised():
     assert cache.snapshot()["page_groups"][0]["pages_free"] == 16
     engine.add_request("d", [1, 2], max_new_tokens=2)       # the engine goes on
     assert engine.run()["d"] == [3, 3]
+
+
+def test_status_bits_have_messages():
+    """Every bit a kernel can set has a text, several bits give several texts, unknown bits are named."""
+    from mini_hisparse_b200.engine.step import ModelRunner
+
+    for bit, text in ModelRunner.STATUS_BITS.items():
+        assert ModelRunner.status_message(bit) == text
+    both = ModelRunner.status_message(4 | 8)
+    assert "matrix product" in both and "TMA-fed attention" in both
+    assert "0x40" in ModelRunner.status_message(64 | 1) and "vocabulary" in ModelRunner.status_message(64 | 1)
