@@ -58,6 +58,8 @@ def build_parser() -> argparse.ArgumentParser:
             c.add_argument("--prompt-tokens", type=int, default=1024)
             c.add_argument("--steps", type=int, default=20)
             c.add_argument("--layers", type=int, help="run fewer layers than the config has")
+            c.add_argument("--prefill", action="store_true",
+                           help="time one prompt of --prompt-tokens in portions of --max-tokens-per-step instead of decoding")
     return parser
 
 
@@ -103,8 +105,18 @@ def main(argv=None) -> int:
     from .engine.engine import Engine, load_model
 
     if args.command == "bench":
-        from .measure import decode_benchmark
+        from .measure import decode_benchmark, prefill_benchmark
 
+        if args.prefill:
+            result = prefill_benchmark(json.loads(args.config.read_text()), prompt_tokens=args.prompt_tokens,
+                                       max_tokens_per_step=args.max_tokens_per_step, dtype=args.dtype,
+                                       device=args.device, page_size=args.page_size, weight_seed=args.weight_seed,
+                                       layers=args.layers)
+            text = json.dumps(result, indent=2)
+            if args.output:
+                args.output.write_text(text + "\n")
+            print(text)
+            return 0
         result = decode_benchmark(json.loads(args.config.read_text()), batch=args.requests,
                                   prompt_tokens=args.prompt_tokens, steps=args.steps, dtype=args.dtype,
                                   device=args.device, page_size=args.page_size, weight_seed=args.weight_seed,

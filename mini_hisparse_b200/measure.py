@@ -199,6 +199,47 @@ def decode_benchmark(config: dict, *, batch=8, prompt_tokens=1024, steps=20, war
             "hbm_fraction": gbs / p["hbm_gbs"], "peak_source": p["source"], "clocks": r["clocks"]}
 
 
+def prefill_benchmark(config: dict, *, prompt_tokens=2048, max_tokens_per_step=2048, repeats=3, dtype="bfloat16",
+                      device="cuda:0", page_size=16, weight_seed=0, layers: int | None = None) -> dict:
+    """What ``bench --prefill`` prints: one prompt of ``prompt_tokens`` through ``Engine.step()`` in
+    portions of at most ``max_tokens_per_step`` (wall clock, host work included), best of ``repeats``."""
+    from .config.registry import resolve
+
+    engine = build_engine(config, batch=1, context=prompt_tokens + 2, dtype=dtype, device=device,
+                          page_size=page_size, weight_seed=weight_seed, layers=layers,
+                          max_tokens_per_step=max_tokens_per_step, extra_pages=2)
+    config = dict(config)
+    if layers is not None:
+        config["num_hidden_layers"] = layers
+    cfg, _ = resolve(config)
+    vocab = engine.model.spec.vocab_size
+    g = torch.Generator().manual_seed(7)
+    times = []
+    with ClockSampler() as clocks:
+        for i in range(repeats + 1):
+            prompt = torch.randint(0, vocab, (prompt_tokens,), generator=g).tolist()
+            engine.add_request(f"p{i}", prompt, max_new_tokens=1)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            engine.run()
+            torch.cuda.synchronize()
+            times.append(time.perf_counter() - t0)
+    sec = min(times[1:])
+    segs, start = [], 0
+    while start < prompt_tokens:
+        n = min(max_tokens_per_step, prompt_tokens - start)
+        segs.append((start, n))
+        start += n
+    flops = sum(step_flops(cfg, config["num_hidden_layers"], [sg], 0) for sg in segs) + 2 * cfg.hidden_size * cfg.vocab_size
+    p = peaks()
+    return {"metric": "prefill tokens/s (one prompt through Engine.step)", "prompt_tokens": prompt_tokens,
+            "max_tokens_per_step": max_tokens_per_step, "layers": config["num_hidden_layers"], "dtype": dtype,
+            "tokens_per_second": prompt_tokens / sec, "ms": sec * 1e3, "tflops": flops / sec / 1e12,
+            "bf16_fraction_of_burst": flops / sec / 1e12 / p["bf16_tflops"],
+            "bf16_fraction_of_sustained": flops / sec / 1e12 / p["bf16_tflops_sustained"], "peak_source": p["source"],
+            "clocks": clocks.result}
+
+
 # ---- serving workloads: requests through Engine.step(), host tokens in and out -----------------------
 def step_flops(cfg, layers: int, segments: list[tuple[int, int]], logit_rows: int) -> float:
     """Floating-point operations of one step: 2 per weight element and token for the products, 4 d per
