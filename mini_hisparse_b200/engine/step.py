@@ -334,14 +334,21 @@ class ModelRunner:
 
     # ---- the step -----------------------------------------------------------------------------
     @torch.inference_mode()
-    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+    def step(self, entries: list[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor | None:
         """Run one batch.  Returns logits [wanted, vocab] float32 in the order of the entries and
         of their ``want`` lists, or None if nothing is wanted.  The tensor is scratch: it is
-        overwritten by the next step."""
+        overwritten by the next step.
+
+        ``device_tokens`` (int32 on the device, one per entry, every entry a single token): the token
+        ids are taken from there instead of from the entries, in stream order: a step can be queued
+        behind the step that samples its input, before those tokens have reached the host."""
         if not entries:
             return None
         vocab = self.model.spec.vocab_size
-        for e in entries:
+        if device_tokens is not None:
+            if any(len(e.tokens) != 1 for e in entries) or device_tokens.numel() != len(entries):
+                raise StepError("tokens on the device stand for single-token entries, one each")
+        for e in entries if device_tokens is None else ():
             if len(e.tokens) > 32:          # a prompt portion: one pass in numpy
                 arr = np.asarray(e.tokens)
                 bad = np.flatnonzero((arr < 0) | (arr >= vocab))
@@ -365,17 +372,19 @@ class ModelRunner:
         ahead, self._ahead = self._ahead, None       # what was packed ahead serves this step or none
         logits = None
         if self.use_graphs and decode_only and self.observer is None:   # a hook's calls are not replayed
-            logits = self._step_graph(entries, segments, ahead)
+            logits = self._step_graph(entries, segments, ahead, device_tokens)
         if logits is None:
-            logits = self._step_eager(entries, segments, T)
+            logits = self._step_eager(entries, segments, T, device_tokens)
         for s in segments:
             self.cache.advance(s.request, s.count)
         self.stats["steps"] += 1
         self.stats["tokens"] += T
         return logits
 
-    def _step_eager(self, entries, segments, T):
+    def _step_eager(self, entries, segments, T, device_tokens=None):
         views = self.batch.eager(entries, segments)
+        if device_tokens is not None:
+            views["tokens"].copy_(device_tokens)
         return self._forward(self.ws, views, segments, T, side=True)
 
     def _forward(self, ws, views, segments, T, side: bool = False):
@@ -405,7 +414,7 @@ class ModelRunner:
         self.graphs[(B, width)] = g
         return g
 
-    def _step_graph(self, entries, segments, ahead=None):
+    def _step_graph(self, entries, segments, ahead=None, device_tokens=None):
         """The step through a captured graph, or None if a planner cannot hold its plan constant
         (then the step runs eagerly)."""
         B = len(segments)
@@ -428,6 +437,8 @@ class ModelRunner:
                 raise StepError(f"a decode plan changed after its graph was captured: {facts} vs {g.facts}")
         g.meta.copy_(stage[: layout.total], non_blocking=True)
         self.batch.staging.mark(turn)
+        if device_tokens is not None:
+            g.meta[layout.tokens : layout.tokens + B].copy_(device_tokens)
         if g.graph is None:
             views = self.batch._views(g.meta, layout, B, B, B, g.facts)
             # one eager run sizes the workspace and warms the kernels up, then the capture

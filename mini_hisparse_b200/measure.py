@@ -298,19 +298,26 @@ def serving_workload(config: dict, *, prompts: list[list[int]], max_new_tokens: 
     weights = decode_bytes(model, engine.cache, 0)
     kv_per_token = sum(g.page_bytes() // page_size for g in engine.cache.page_groups)
     step_ms, kinds, read_bytes, flops = [], [], 0, 0.0
-    generated = prompt_tokens = 0
+    generated = prompt_tokens = seen = 0
     torch.cuda.synchronize()
     with ClockSampler() as clocks:
         t_start = time.perf_counter()
-        while not engine.scheduler.idle:
+        while not engine.scheduler.idle or engine._queued is not None:
             t0 = time.perf_counter()
             emitted = engine.step()
             step_ms.append((time.perf_counter() - t0) * 1e3)
             generated += len(emitted)
-            segs = [(start, n) for _, start, n in engine.last_step]
-            kinds.append("decode" if all(n == 1 for _, n in segs) else "mixed")
-            read_bytes += weights + kv_per_token * sum(start + n for start, n in segs)
-            flops += step_flops(cfg, layers, segs, len(emitted))
+            # a call may launch no step, one, or two (a decode step queued behind the one it waits for)
+            new = engine.launches - seen
+            seen = engine.launches
+            kind = "decode"
+            for held in list(engine.launch_log)[len(engine.launch_log) - new:] if new else []:
+                segs = [(start, n) for _, start, n in held]
+                if not all(n == 1 for _, n in segs):
+                    kind = "mixed"
+                read_bytes += weights + kv_per_token * sum(start + n for start, n in segs)
+                flops += step_flops(cfg, layers, segs, sum(1 for _ in segs))
+            kinds.append(kind)
         torch.cuda.synchronize()
         seconds = time.perf_counter() - t_start
     engine.runner.check_status()

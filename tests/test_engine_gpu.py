@@ -47,7 +47,7 @@ def test_greedy_generation_equals_plain(folders, name, dtype):
         r = engine.requests[rid]
         assert r.prefill_count == 1 and r.decode_count == 15 and r.finished
     assert engine.runner.stats["graph_steps"] > 0        # decoding went through captured graphs
-    assert engine.runner.stats["prepared_steps"] > 0     # and some steps' index arrays were packed ahead
+    assert engine.stats["queued_steps"] > 0              # and steps were queued behind the step that fed them
     engine.cache.assert_invariants()
     assert not engine.cache.requests
     assert engine.cache.page_groups[0].allocator.free_pages == 64
@@ -119,10 +119,12 @@ def test_most_requests_in_one_step_on_the_engine(folders):
     prompts = {str(n): random_tokens(cfg["vocab_size"], n, seed=n) for n in (5, 21, 34, 9)}
     for rid, prompt in prompts.items():
         engine.add_request(rid, prompt, max_new_tokens=6)
-    while not engine.scheduler.idle:
-        before = engine.runner.stats["steps"]
+    seen = 0
+    while not engine.scheduler.idle or engine._queued is not None:
         engine.step()
-        assert engine.runner.stats["steps"] == before + 1
+        for held in list(engine.launch_log)[len(engine.launch_log) - (engine.launches - seen):]:
+            assert 1 <= len(held) <= 2, held             # no step holds more than two requests
+        seen = engine.launches
     assert all(t["tokens"] >= 1 for t in engine.timeline)
     for rid, prompt in prompts.items():
         assert engine.requests[rid].generated == P.generate(pc, w, prompt, 6)
@@ -260,6 +262,44 @@ def test_cancel_and_eos(folders):
     stop = want.index(want[4])
     assert out["a"] == want[: stop + 1]                   # the EOS token is kept
     assert engine.requests["b"].cancelled and not engine.cache.requests
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_queued_decode_steps_change_nothing(folders, dtype):
+    """Decode steps queued behind the step that samples their input (token ids handed over on the
+    device) against the same engine waiting for the host between steps: the same tokens, greedy and
+    drawn at a temperature, with requests of different lengths and one that ends on an end token in
+    the middle (found out one step late: one token is dropped).  In bfloat16 the step that still
+    carries the ended request has other key splits than its counterpart, so there only the lengths
+    and the end token are compared."""
+    from mini_hisparse_b200 import Engine
+
+    cfg, page = TINY["B"]
+    model = load(folders["B"], dtype)
+    prompts = {f"r{i}": random_tokens(cfg["vocab_size"], n, seed=40 + i) for i, n in enumerate((3, 50, 17, 90))}
+    new_tokens, temperatures = (9, 30, 22, 14), (0.0, 0.7, 0.0, 1.1)
+
+    def run(pipeline, eos):
+        engine = Engine(model, num_pages=40, page_size=page, max_requests=5, max_tokens_per_step=64, pipeline=pipeline)
+        for i, (rid, prompt) in enumerate(prompts.items()):
+            engine.add_request(rid, prompt, max_new_tokens=new_tokens[i], temperature=temperatures[i], seed=7 + i,
+                               eos_token_id=eos)
+        out = engine.run()
+        engine.cache.assert_invariants()
+        assert not engine.cache.requests and engine._queued is None
+        return out, engine.stats
+
+    free_run, _ = run(False, None)
+    eos = free_run["r1"][10]                     # r1's 11th token becomes everybody's end token
+    waiting, stats0 = run(False, eos)
+    queued, stats1 = run(True, eos)
+    assert stats0["queued_steps"] == 0 and stats1["queued_steps"] > 5 and stats1["dropped_tokens"] >= 1
+    assert waiting["r1"][-1] == eos and len(waiting["r1"]) <= 11
+    if dtype == "float32":
+        assert queued == waiting
+    else:
+        assert {k: len(v) for k, v in queued.items()} == {k: len(v) for k, v in waiting.items()}
+        assert queued["r1"] == waiting["r1"]
 
 
 def test_bad_weights_fail_with_one_clear_error(folders, tmp_path):

@@ -130,8 +130,12 @@ def test_engine_fails_the_requests_of_a_step_that_raised():
             self.fail_next = False
             self.resets = 0
             self.stats = {}
+            self.device_tokens_seen = 0
 
-        def step(self, entries):
+        use_graphs = True
+
+        def step(self, entries, device_tokens=None):
+            self.device_tokens_seen += device_tokens is not None
             for e in entries:                  # what the real runner does before and after its launches
                 cache.ensure(e.request, cache.length(e.request) + len(e.tokens))
                 cache.advance(e.request, len(e.tokens))
@@ -152,15 +156,38 @@ def test_engine_fails_the_requests_of_a_step_that_raised():
             self.resets += 1
 
     class FakeSampler:
+        """Tickets as the real one; request i's k-th token is 10 i + k (from the counter it is given)."""
+
+        def __init__(self):
+            self.rows = {}
+            self.ticket = 0
+
         def launch(self, logits, temps, seeds, counters):
-            self.n = logits.shape[0]
+            self.ticket += 1
+            self.rows[self.ticket] = [3 + c for c in counters]
+            return self.ticket
 
-        def collect(self):
-            return [3] * self.n
+        def device_tokens(self, ticket):
+            return torch.tensor(self.rows[ticket], dtype=torch.int32)
 
-    engine = object.__new__(Engine)
-    engine.cache, engine.runner, engine.sampler, engine.timeline = cache, FakeRunner(), FakeSampler(), []
-    engine.scheduler = Scheduler(cache, SchedulerConfig(max_tokens_per_step=6), 50)
+        def reset(self):
+            self.rows.clear()
+
+        def collect(self, ticket):
+            return self.rows.pop(ticket)
+
+    def make_engine(pipeline):
+        from collections import deque
+
+        engine = object.__new__(Engine)
+        engine.cache, engine.runner, engine.sampler, engine.timeline = cache, FakeRunner(), FakeSampler(), []
+        engine.scheduler = Scheduler(cache, SchedulerConfig(max_tokens_per_step=6), 50, eos_token_id=6)
+        engine.pipeline, engine._queued, engine.launch_log, engine.launches = pipeline, None, deque(maxlen=8), 0
+        engine.stats = {"queued_steps": 0, "dropped_tokens": 0}
+        engine.model = None
+        return engine
+
+    engine = make_engine(pipeline=False)
     engine.add_request("a", [1, 2, 3], max_new_tokens=3)
     engine.add_request("b", [4, 5], max_new_tokens=3)
     engine.add_request("c", [6, 7, 8, 9], max_new_tokens=2)
@@ -173,7 +200,25 @@ def test_engine_fails_the_requests_of_a_step_that_raised():
     cache.assert_invariants()
     assert cache.snapshot()["page_groups"][0]["pages_free"] == 16
     engine.add_request("d", [1, 2], max_new_tokens=2)       # the engine goes on
-    assert engine.run()["d"] == [3, 3]
+    assert engine.run()["d"] == [3, 4]
+
+    # Decode steps queued behind one another: a step's tokens reach the host's books one call later,
+    # every call returns one step's tokens, and a request that draws its end token (6 = 3 + 3) while
+    # the next step is already queued costs one dropped token and no more.
+    engine = make_engine(pipeline=True)
+    engine.add_request("x", [1, 2], max_new_tokens=8)
+    engine.add_request("y", [4], max_new_tokens=5)
+    out = []
+    while not engine.scheduler.idle or engine._queued is not None:
+        out.append(engine.step())
+    assert engine.requests["x"].generated == [3, 4, 5, 6]        # ended by its end token, kept
+    assert engine.requests["y"].generated == [3, 4, 5, 6]
+    assert [len(o) for o in out[:4]] == [2, 2, 2, 2] and all(len(o) == 0 for o in out[4:])
+    assert engine.stats["queued_steps"] >= 2 and engine.stats["dropped_tokens"] == 2
+    assert engine.runner.device_tokens_seen == engine.stats["queued_steps"]
+    assert not cache.requests
+    cache.assert_invariants()
+    assert cache.snapshot()["page_groups"][0]["pages_free"] == 16
 
 
 def test_status_bits_have_messages():
