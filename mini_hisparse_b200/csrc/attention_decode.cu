@@ -16,10 +16,13 @@
 //     the 7B shape) from the product's partials, and the CTA that owns the token's own position
 //     builds the new k and v, patches them into its last tile in shared memory and, when it has
 //     walked its keys, stores them into the page for the steps to come.
-//   * the splits' (max, sum, accumulator) meet in distributed shared memory: after a cluster
-//     barrier CTA r merges the rows r, r + nsplit, ... from all peers in split order (so the result
-//     does not depend on timing) and writes them; no partial goes through global memory.
-// Head size 64 or 128, pages that divide 64, at most 16 heads per KV head, at most 16 splits.
+//   * the splits' (max, sum, accumulator) meet in distributed shared memory: a CTA that has walked
+//     its keys sends every row of its part to the CTA that owns that row (CTA r owns the rows r,
+//     r + nsplit, ...; plain st.shared::cluster), one cluster barrier follows, and each owner merges
+//     what it received in split order (so the result does not depend on timing) from its own shared
+//     memory and writes the row; no partial goes through global memory.
+// Head size 64 or 128, pages that divide 64, at most 16 heads per KV head, at most 16 splits, and at
+// most 16 received rows per CTA (splits x rows owned).
 // Every mbarrier wait is bounded (status bit 8); a CTA whose wait ran out still walks through the
 // cluster barriers, waits for its armed copies, and writes nothing.
 #include "mma_helpers.cuh"
@@ -61,13 +64,14 @@ struct Layout {
     static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
     static constexpr int MS = D + 4;                                    // a partial row: accumulator, max, sum (16-byte rows)
     static constexpr int MERGE_BYTES = CWARPS * ROWS * MS * 4;          // the four warps' parts, in the ring
-    static constexpr int PART_OFFSET = Q_BYTES + ((MERGE_BYTES + 1023) / 1024) * 1024;   // the CTA's part, in the ring
-    static constexpr int PART_BYTES = ROWS * MS * 4;
+    static constexpr int RECV_ROWS = 16;                                // rows this CTA receives: splits x rows it owns
     static constexpr int BAR_OFFSET = Q_BYTES + RING_BYTES;
     static constexpr int CS_OFFSET = BAR_OFFSET + 2 * STAGES * 8 + 16;  // cos, sin of this token
     static constexpr int NEW_OFFSET = CS_OFFSET + D * 4;                // the token's own k and v (bfloat16)
-    static constexpr int TOTAL = NEW_OFFSET + 2 * D * 2 + 1024;
-    static_assert(PART_OFFSET + PART_BYTES <= BAR_OFFSET, "the parts must fit in the ring");
+    // what the peers send: not in the ring, since a peer may be done while this CTA still streams tiles
+    static constexpr int RECV_OFFSET = NEW_OFFSET + 2 * D * 2;
+    static constexpr int TOTAL = RECV_OFFSET + RECV_ROWS * MS * 4 + 1024;
+    static_assert(MERGE_BYTES <= RING_BYTES, "the four warps' parts must fit in the ring");
 };
 
 __device__ __forceinline__ uint32_t swz(uint32_t base, int rows_per_half, int r, int e) {
@@ -78,20 +82,16 @@ __device__ __forceinline__ void prologue_sync() { asm volatile("bar.sync 2, %0;"
 __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
 __device__ __forceinline__ uint32_t peer_addr(uint32_t local, uint32_t rank) {
     uint32_t a;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local), "r"(rank));
     return a;
 }
-__device__ __forceinline__ float ld_peer(uint32_t addr) {
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-    return v;
+__device__ __forceinline__ void st_peer4(uint32_t addr, float4 v) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void st_peer2(uint32_t addr, float2 v) {
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(v.x), "f"(v.y) : "memory");
 }
 __device__ __forceinline__ void st_smem_8(uint32_t addr, uint32_t lo, uint32_t hi) {
     asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(lo), "r"(hi) : "memory");
@@ -193,7 +193,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const Decode
     auto empty_bar = [&](int s) { return bar0 + 8 * (STAGES + s); };
     float* cs = (float*)(smem + L::CS_OFFSET);
     __nv_bfloat16* kv_new = (__nv_bfloat16*)(smem + L::NEW_OFFSET);
-    float* part = (float*)(smem + L::PART_OFFSET);
+    float* recv = (float*)(smem + L::RECV_OFFSET);        // [split][row this CTA owns][MS]
+    const int owned = (nrows + a.nsplit - 1) / a.nsplit;   // rows a CTA owns at most
     const int* table = a.block_table + (size_t)t * a.width;
 
     if (tid == 0) {
@@ -460,42 +461,28 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const Decode
                 lsum += wgt * ml[w].y;
             }
             if (!ok) { M = -INFINITY; acc = make_float4(0.f, 0.f, 0.f, 0.f); lsum = 0.f; }
-            *(float4*)(part + r * MS + e) = acc;
-            if (e == 0) *(float2*)(part + r * MS + D) = make_float2(M, lsum);
+            // to the CTA that owns row r, into the place of this split
+            const uint32_t dst = peer_addr(smem_addr(recv + (split * owned + r / a.nsplit) * MS), r % a.nsplit);
+            st_peer4(dst + e * 4, acc);
+            if (e == 0) st_peer2(dst + D * 4, make_float2(M, lsum));
         }
     }
 
-    // ---- the splits of the token meet: CTA r merges rows r, r + nsplit, ... of all peers ------------------
+    // ---- the splits of the token meet: every part has been sent when the barrier completes; CTA r
+    // merges the rows r, r + nsplit, ... from its own shared memory ----------------------------------------
     cluster_sync();
     if (warp < CWARPS) {
-        const uint32_t part_s = smem_addr(part);
         const float scale_log2 = a.scale * 1.4426950408889634f;
-        for (int r = (int)cluster_rank(); r < nrows; r += a.nsplit) {
+        for (int r = split, k = 0; r < nrows; r += a.nsplit, ++k) {
             for (int e = tid; e < D; e += CWARPS * 32) {
-                // all loads from the peers are issued together (one round trip through the cluster's
-                // shared memory); the sum runs in split order
-                float mp[MAX_CLUSTER], lp[MAX_CLUSTER], ap[MAX_CLUSTER];
-#pragma unroll
-                for (int p = 0; p < MAX_CLUSTER; ++p) {
-                    if (p < a.nsplit) {
-                        const uint32_t base = peer_addr(part_s + r * MS * 4, p);
-                        mp[p] = ld_peer(base + D * 4);
-                        lp[p] = ld_peer(base + (D + 1) * 4);
-                        ap[p] = ld_peer(base + e * 4);
-                    } else {
-                        mp[p] = -INFINITY;
-                        lp[p] = ap[p] = 0.f;
-                    }
-                }
                 float M = -INFINITY;
-#pragma unroll
-                for (int p = 0; p < MAX_CLUSTER; ++p) M = fmaxf(M, mp[p]);
+                for (int p = 0; p < a.nsplit; ++p) M = fmaxf(M, recv[(p * owned + k) * MS + D]);
                 float acc = 0.f, lsum = 0.f;
-#pragma unroll
-                for (int p = 0; p < MAX_CLUSTER; ++p) {
-                    const float w = mp[p] == -INFINITY ? 0.f : exp2f((mp[p] - M) * scale_log2);
-                    acc += w * ap[p];
-                    lsum += w * lp[p];
+                for (int p = 0; p < a.nsplit; ++p) {           // in split order
+                    const float* src = recv + (p * owned + k) * MS;
+                    const float w = src[D] == -INFINITY ? 0.f : exp2f((src[D] - M) * scale_log2);
+                    acc += w * src[e];
+                    lsum += w * src[D + 1];
                 }
                 a.out[((size_t)t * a.nq + kvh * groups + r) * D + e] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
             }
@@ -515,7 +502,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const Decode
             }
         }
     }
-    cluster_sync();        // nobody leaves while a peer may still read its part
+    // no second barrier: after the one above nobody touches another CTA's shared memory
 }
 
 template <int D>
@@ -585,7 +572,8 @@ int launch(const CUtensorMap& map, const DecodeArgs& a, cudaStream_t stream) {
 
 MHB_EXPORT int mhb_attention_decode_supports(int d, int P, int groups, int nsplit, int rotary_dim) {
     return (d == 64 || d == 128) && P >= 2 && P <= KT && KT % P == 0 && groups >= 1 && groups <= ROWS && nsplit >= 1 &&
-           nsplit <= MAX_CLUSTER && rotary_dim >= 0 && rotary_dim <= d && rotary_dim % 8 == 0;
+           nsplit <= MAX_CLUSTER && nsplit * ((groups + nsplit - 1) / nsplit) <= 16 && rotary_dim >= 0 &&
+           rotary_dim <= d && rotary_dim % 8 == 0;
 }
 
 // Clusters of nsplit CTAs that run at once on the current device (0: such clusters cannot be placed); < 0: error.
@@ -608,7 +596,7 @@ MHB_EXPORT int mhb_attention_decode(const float* qkv, int qkv_nsplit, long long 
     if (!mhb_attention_decode_supports(d, P, nq / nkv, nsplit, rotary_dim))
         return fail("attention_decode: head_dim %d, pages of %d keys, %d heads per KV head, %d key splits, %d rotated "
                     "elements is not built (head_dim 64 or 128, page size dividing 64, at most 16 heads per KV head, "
-                    "at most 16 splits, rotated elements a multiple of 8)", d, P, nq / nkv, nsplit, rotary_dim);
+                    "at most 16 splits and 16 received rows per CTA, rotated elements a multiple of 8)", d, P, nq / nkv, nsplit, rotary_dim);
     if (rotary_dim > 0 && inv_freq == nullptr) return fail("attention_decode: a rotation needs its frequencies");
     if (qkv_nsplit < 1 || (qkv_nsplit > 1 && qkv_split_stride % 4) || ((uintptr_t)qkv & 15) || ((uintptr_t)bias & 15) ||
         ((uintptr_t)cache & 15))

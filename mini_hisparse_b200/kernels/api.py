@@ -352,7 +352,8 @@ DECODE_MAX_SPLITS = 16      # key splits of a token that the fused decode kernel
 def attention_decode_supports(d: int, page_size: int, groups: int, nsplit: int, rotary_dim: int) -> bool:
     """Sizes the fused decode-attention kernel is built for."""
     return (d in (64, 128) and 2 <= page_size <= 64 and 64 % page_size == 0 and 1 <= groups <= 16
-            and 1 <= nsplit <= DECODE_MAX_SPLITS and 0 <= rotary_dim <= d and rotary_dim % 8 == 0)
+            and 1 <= nsplit <= DECODE_MAX_SPLITS and nsplit * -(-groups // nsplit) <= 16
+            and 0 <= rotary_dim <= d and rotary_dim % 8 == 0)
 
 
 _decode_clusters: dict[tuple[int, int], int] = {}

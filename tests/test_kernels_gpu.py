@@ -553,9 +553,10 @@ def test_attention_tensor_core_splits_window_and_far_key(kernel):
     (28, 4, 128, 16, 8, 8, 128, False, None),       # the benchmark's shape: 7 heads per KV head, clusters of 8
     (28, 4, 128, 16, 16, 3, 128, False, None),      # clusters of 16
     (3, 1, 64, 32, 1, 1, 64, False, None),          # one share: nothing to merge
-    (32, 2, 128, 8, 5, 2, 64, True, None),          # 16 heads per KV head, interleaved pairs on half the head
+    (32, 2, 128, 8, 4, 2, 64, True, None),          # 16 heads per KV head, interleaved pairs on half the head
     (8, 8, 64, 64, 3, 4, 0, False, None),           # no rotation, one head per KV head, pages of a whole tile
-    (12, 4, 128, 4, 6, 1, 96, False, 300),          # a window, tiny pages
+    (12, 4, 128, 4, 6, 1, 96, False, 300),          # a window, tiny pages; 3 heads over 6 shares: some CTAs own no row
+    (20, 4, 64, 16, 3, 5, 64, False, None),         # 5 heads over 3 shares: a CTA owns two rows
 ])
 def test_attention_decode_fused(nq, nkv, d, P_, nsplit, qkv_nsplit, rdim, interleaved, window):
     """The decode kernel that does everything between the q/k/v product and the output projection:
