@@ -417,6 +417,235 @@ struct QkvRopeArgs {
     int table_width, nq, nkv, d, P, num_pages, write_kv;
 };
 
+// Store one unit of a row of a tile: 16 sums (or, for the SwiGLU epilogue, 16 gate and 16 up sums) at
+// columns c0.. of the tile whose first column is rb0.
+template <typename OT, int EPI>
+__device__ __forceinline__ void emit_unit(OT* __restrict__ C, long long ldc, int Ra, int Rb, int ra, int rb0, int c0,
+                                          const uint32_t (&r)[16], const uint32_t (&r2)[16]) {
+    if (ra >= Ra) return;
+    if constexpr (EPI == 1) {
+        OT* row = C + (size_t)ra * ldc + (rb0 + c0) / 2;
+        float v[16];
+#pragma unroll
+        for (int x = 0; x < 16; ++x) v[x] = silu_mul(__uint_as_float(r[x]), __uint_as_float(r2[x]));
+        if (rb0 + c0 + 32 <= Rb && ((uintptr_t)row & 15) == 0 && sizeof(OT) == 2) {
+            uint32_t p[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+                __nv_bfloat162 t2 = __floats2bfloat162_rn(v[2 * x], v[2 * x + 1]);
+                p[x] = *(uint32_t*)&t2;
+            }
+            *(uint4*)(row) = make_uint4(p[0], p[1], p[2], p[3]);
+            *(uint4*)((uint8_t*)row + 16) = make_uint4(p[4], p[5], p[6], p[7]);
+        } else {
+#pragma unroll
+            for (int x = 0; x < 16; ++x)
+                if (rb0 + c0 + 16 + x < Rb) store_out<OT>(row + x, v[x]);
+        }
+    } else {
+        OT* row = C + (size_t)ra * ldc + rb0 + c0;
+        if (rb0 + c0 + 16 <= Rb && ((uintptr_t)row & 15) == 0) {
+            if constexpr (sizeof(OT) == 4) {
+#pragma unroll
+                for (int x = 0; x < 16; x += 4)
+                    *(uint4*)(row + x) = make_uint4(r[x], r[x + 1], r[x + 2], r[x + 3]);
+            } else {
+                uint32_t p[8];
+#pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                    __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(r[2 * x]), __uint_as_float(r[2 * x + 1]));
+                    p[x] = *(uint32_t*)&v2;
+                }
+                *(uint4*)(row) = make_uint4(p[0], p[1], p[2], p[3]);
+                *(uint4*)(row + 8) = make_uint4(p[4], p[5], p[6], p[7]);
+            }
+        } else {
+#pragma unroll
+            for (int x = 0; x < 16; ++x)
+                if (rb0 + c0 + x < Rb) store_out<OT>(row + x, __uint_as_float(r[x]));
+        }
+    }
+}
+
+// The epilogue of one whole tile: this thread's row (row_in_tile of the 128 rows at ra0) of the accumulator at
+// `acc` (tensor memory, this warp's lanes) goes to C, through the SwiGLU gate (EPI 1), or, rotated, to q and
+// the cache pages (EPI 2).
+template <typename OT, int EPI>
+__device__ __forceinline__ void store_tile(uint32_t acc, int ra0, int rb0, int bn, int row_in_tile, OT* __restrict__ C,
+                                           long long ldc, int Ra, int Rb, const QkvRopeArgs& qr,
+                                           int* __restrict__ status) {
+    constexpr int UNIT = EPI == 1 ? 32 : 16;        // columns that are stored together
+    if constexpr (EPI == 2) {
+        const int ra = ra0 + row_in_tile;
+        const bool live = ra < Ra;
+        const int d = qr.d, rdim = qr.rdim, half = rdim >> 1;
+        const int pos = live ? qr.positions[ra] : 0;
+        const float* cs = qr.cos_sin + (size_t)(live ? ra : 0) * rdim;
+        const int head0 = rb0 / d;
+        int page = -1;
+        if (live && qr.write_kv && head0 + bn / d > qr.nq) {        // the tile holds k or v heads
+            page = qr.block_table[(size_t)qr.tok_seg[ra] * qr.table_width + pos / qr.P];
+            if (page < 0 || page >= qr.num_pages) {                 // never write outside the pool
+                if (status) atomicOr(status, 2);
+                page = -1;
+            }
+        }
+        const int within = pos % qr.P;
+        const int total_heads = qr.nq + 2 * qr.nkv;
+        auto head_dst = [&](int head) -> __nv_bfloat16* {
+            return head < qr.nq ? qr.q_out + (size_t)ra * qr.nq * d + head * d
+                                : qr.cache + ((((size_t)page * 2 + 0) * qr.nkv + (head - qr.nq)) * qr.P + within) * d;
+        };
+        auto load_bias16 = [&](float (&b)[16], int col) {
+            if (qr.bias) {
+#pragma unroll
+                for (int x = 0; x < 4; ++x) *(float4*)(b + 4 * x) = *(const float4*)(qr.bias + col + 4 * x);
+            } else {
+#pragma unroll
+                for (int x = 0; x < 16; ++x) b[x] = 0.f;
+            }
+        };
+        auto store16 = [&](__nv_bfloat16* dst, const float (&v)[16]) {
+            uint32_t pk[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+                __nv_bfloat162 t2 = __floats2bfloat162_rn(v[2 * x], v[2 * x + 1]);
+                pk[x] = *(uint32_t*)&t2;
+            }
+            *(uint4*)(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *(uint4*)(dst + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        };
+        // rotated heads: the chunk of angles is the outer loop, so that a row's cos and
+        // sin are fetched once (16-byte loads) for all heads of the tile
+        if (!qr.interleaved) {
+#pragma unroll 1
+            for (int c = 0; c < half; c += 16) {
+                float4 cs4[4], sn4[4];
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    cs4[x] = *(const float4*)(cs + c + 4 * x);
+                    sn4[x] = *(const float4*)(cs + half + c + 4 * x);
+                }
+                const float* cf = (const float*)cs4;
+                const float* sf = (const float*)sn4;
+#pragma unroll 1
+                for (int hh = 0; hh < bn / d; ++hh) {
+                    const int head = head0 + hh;
+                    if (head >= qr.nq + qr.nkv) break;               // value heads and the edge: below
+                    const bool is_q = head < qr.nq;
+                    uint32_t ra16[16], rb16[16];
+                    tmem_ld16(acc + hh * d + c, ra16);
+                    tmem_ld16(acc + hh * d + half + c, rb16);
+                    tmem_ld_wait();
+                    if (!live || (!is_q && page < 0)) continue;
+                    __nv_bfloat16* dst = head_dst(head);
+                    float ba[16], bb[16], oa[16], ob[16];
+                    load_bias16(ba, head * d + c);
+                    load_bias16(bb, head * d + half + c);
+#pragma unroll
+                    for (int x = 0; x < 16; ++x) {
+                        const float a0 = __uint_as_float(ra16[x]) + ba[x], b0 = __uint_as_float(rb16[x]) + bb[x];
+                        oa[x] = a0 * cf[x] - b0 * sf[x];
+                        ob[x] = b0 * cf[x] + a0 * sf[x];
+                    }
+                    store16(dst + c, oa);
+                    store16(dst + half + c, ob);
+                }
+            }
+        } else {
+#pragma unroll 1
+            for (int c = 0; c < rdim; c += 16) {        // 16 columns = 8 pairs = angles c/2 .. c/2 + 7
+                float4 cs4[2], sn4[2];
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    cs4[x] = *(const float4*)(cs + (c >> 1) + 4 * x);
+                    sn4[x] = *(const float4*)(cs + half + (c >> 1) + 4 * x);
+                }
+                const float* cf = (const float*)cs4;
+                const float* sf = (const float*)sn4;
+#pragma unroll 1
+                for (int hh = 0; hh < bn / d; ++hh) {
+                    const int head = head0 + hh;
+                    if (head >= qr.nq + qr.nkv) break;
+                    const bool is_q = head < qr.nq;
+                    uint32_t r16[16];
+                    tmem_ld16(acc + hh * d + c, r16);
+                    tmem_ld_wait();
+                    if (!live || (!is_q && page < 0)) continue;
+                    float bv[16], o[16];
+                    load_bias16(bv, head * d + c);
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) {
+                        const float a0 = __uint_as_float(r16[2 * x]) + bv[2 * x], b0 = __uint_as_float(r16[2 * x + 1]) + bv[2 * x + 1];
+                        o[2 * x] = a0 * cf[x] - b0 * sf[x];
+                        o[2 * x + 1] = b0 * cf[x] + a0 * sf[x];
+                    }
+                    store16(head_dst(head) + c, o);
+                }
+            }
+        }
+        // the elements of q and k heads behind the rotated ones: bias only
+#pragma unroll 1
+        for (int c = rdim; c < d; c += 16) {
+#pragma unroll 1
+            for (int hh = 0; hh < bn / d; ++hh) {
+                const int head = head0 + hh;
+                if (head >= qr.nq + qr.nkv) break;
+                uint32_t r16[16];
+                tmem_ld16(acc + hh * d + c, r16);
+                tmem_ld_wait();
+                if (!live || (head >= qr.nq && page < 0)) continue;
+                float bv[16], o[16];
+                load_bias16(bv, head * d + c);
+#pragma unroll
+                for (int x = 0; x < 16; ++x) o[x] = __uint_as_float(r16[x]) + bv[x];
+                store16(head_dst(head) + c, o);
+            }
+        }
+        // value heads: bias, no rotation
+#pragma unroll 1
+        for (int hh = 0; hh < bn / d; ++hh) {
+            const int head = head0 + hh;
+            if (head < qr.nq + qr.nkv) continue;
+            if (head >= total_heads) break;
+            const int col0 = head * d;
+            __nv_bfloat16* dst = qr.cache + ((((size_t)(page < 0 ? 0 : page) * 2 + 1) * qr.nkv + (head - qr.nq - qr.nkv)) * qr.P + within) * d;
+#pragma unroll 1
+            for (int c = 0; c < d; c += 16) {
+                uint32_t r[16];
+                tmem_ld16(acc + hh * d + c, r);
+                tmem_ld_wait();
+                if (page < 0) continue;
+                float bv[16];
+                if (qr.bias) {
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) *(float4*)(bv + 4 * x) = *(const float4*)(qr.bias + col0 + c + 4 * x);
+                } else {
+#pragma unroll
+                    for (int x = 0; x < 16; ++x) bv[x] = 0.f;
+                }
+                uint32_t pk[8];
+#pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                    __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(r[2 * x]) + bv[2 * x], __uint_as_float(r[2 * x + 1]) + bv[2 * x + 1]);
+                    pk[x] = *(uint32_t*)&t2;
+                }
+                *(uint4*)(dst + c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *(uint4*)(dst + c + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            }
+        }
+    } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < bn; c0 += UNIT) {
+            uint32_t r[16], r2[16];
+            tmem_ld16(acc + c0, r);
+            if constexpr (EPI == 1) tmem_ld16(acc + c0 + 16, r2);
+            tmem_ld_wait();
+            emit_unit<OT, EPI>(C, ldc, Ra, Rb, ra0 + row_in_tile, rb0, c0, r, r2);
+        }
+    }
+}
+
 template <typename OT, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -559,52 +788,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
         constexpr int UNIT = EPI == 1 ? 32 : 16;        // columns that are stored together
-        // Store one unit of a row: 16 sums (or 16 gate and 16 up sums) at columns c0.. of tile (ra0, rb0).
-        auto emit = [&](int ra, int rb0, int c0, const uint32_t (&r)[16], const uint32_t (&r2)[16]) {
-            if (ra >= Ra) return;
-            if constexpr (EPI == 1) {
-                OT* row = C + (size_t)ra * ldc + (rb0 + c0) / 2;
-                float v[16];
-#pragma unroll
-                for (int x = 0; x < 16; ++x) v[x] = silu_mul(__uint_as_float(r[x]), __uint_as_float(r2[x]));
-                if (rb0 + c0 + 32 <= Rb && ((uintptr_t)row & 15) == 0 && sizeof(OT) == 2) {
-                    uint32_t p[8];
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) {
-                        __nv_bfloat162 t2 = __floats2bfloat162_rn(v[2 * x], v[2 * x + 1]);
-                        p[x] = *(uint32_t*)&t2;
-                    }
-                    *(uint4*)(row) = make_uint4(p[0], p[1], p[2], p[3]);
-                    *(uint4*)((uint8_t*)row + 16) = make_uint4(p[4], p[5], p[6], p[7]);
-                } else {
-#pragma unroll
-                    for (int x = 0; x < 16; ++x)
-                        if (rb0 + c0 + 16 + x < Rb) store_out<OT>(row + x, v[x]);
-                }
-            } else {
-                OT* row = C + (size_t)ra * ldc + rb0 + c0;
-                if (rb0 + c0 + 16 <= Rb && ((uintptr_t)row & 15) == 0) {
-                    if constexpr (sizeof(OT) == 4) {
-#pragma unroll
-                        for (int x = 0; x < 16; x += 4)
-                            *(uint4*)(row + x) = make_uint4(r[x], r[x + 1], r[x + 2], r[x + 3]);
-                    } else {
-                        uint32_t p[8];
-#pragma unroll
-                        for (int x = 0; x < 8; ++x) {
-                            __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(r[2 * x]), __uint_as_float(r[2 * x + 1]));
-                            p[x] = *(uint32_t*)&v2;
-                        }
-                        *(uint4*)(row) = make_uint4(p[0], p[1], p[2], p[3]);
-                        *(uint4*)(row + 8) = make_uint4(p[4], p[5], p[6], p[7]);
-                    }
-                } else {
-#pragma unroll
-                    for (int x = 0; x < 16; ++x)
-                        if (rb0 + c0 + x < Rb) store_out<OT>(row + x, __uint_as_float(r[x]));
-                }
-            }
-        };
         // ---- second pass: the shared tiles.  The CTAs that hold parts of a tile divide its columns
         // among themselves; each adds the parts in the order of their K ranges and stores. ---------
         auto reduce_shared = [&](const int (&shared_entry)[2], int shared_count) {
@@ -660,7 +843,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 uint32_t r[16], r2[16];
 #pragma unroll
                 for (int x = 0; x < 16; ++x) { r[x] = __float_as_uint(s[x]); r2[x] = __float_as_uint(s2[x]); }
-                emit(ra0 + row_in_tile, rb0, c0, r, r2);
+                emit_unit<OT, EPI>(C, ldc, Ra, Rb, ra0 + row_in_tile, rb0, c0, r, r2);
             }
             __syncwarp();
             // the last quarter-warp to have read puts the counter back to zero for the next launch
@@ -709,175 +892,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 if (shared_count < 2) shared_entry[shared_count++] = entry;
                 continue;
             }
-            if constexpr (EPI == 2) {
-                const int ra = ra0 + row_in_tile;
-                const bool live = ra < Ra;
-                const int d = qr.d, rdim = qr.rdim, half = rdim >> 1;
-                const int pos = live ? qr.positions[ra] : 0;
-                const float* cs = qr.cos_sin + (size_t)(live ? ra : 0) * rdim;
-                const int head0 = rb0 / d;
-                int page = -1;
-                if (live && qr.write_kv && head0 + bn / d > qr.nq) {        // the tile holds k or v heads
-                    page = qr.block_table[(size_t)qr.tok_seg[ra] * qr.table_width + pos / qr.P];
-                    if (page < 0 || page >= qr.num_pages) {                 // never write outside the pool
-                        if (status) atomicOr(status, 2);
-                        page = -1;
-                    }
-                }
-                const int within = pos % qr.P;
-                const int total_heads = qr.nq + 2 * qr.nkv;
-                auto head_dst = [&](int head) -> __nv_bfloat16* {
-                    return head < qr.nq ? qr.q_out + (size_t)ra * qr.nq * d + head * d
-                                        : qr.cache + ((((size_t)page * 2 + 0) * qr.nkv + (head - qr.nq)) * qr.P + within) * d;
-                };
-                auto load_bias16 = [&](float (&b)[16], int col) {
-                    if (qr.bias) {
-#pragma unroll
-                        for (int x = 0; x < 4; ++x) *(float4*)(b + 4 * x) = *(const float4*)(qr.bias + col + 4 * x);
-                    } else {
-#pragma unroll
-                        for (int x = 0; x < 16; ++x) b[x] = 0.f;
-                    }
-                };
-                auto store16 = [&](__nv_bfloat16* dst, const float (&v)[16]) {
-                    uint32_t pk[8];
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) {
-                        __nv_bfloat162 t2 = __floats2bfloat162_rn(v[2 * x], v[2 * x + 1]);
-                        pk[x] = *(uint32_t*)&t2;
-                    }
-                    *(uint4*)(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                    *(uint4*)(dst + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-                };
-                // rotated heads: the chunk of angles is the outer loop, so that a row's cos and
-                // sin are fetched once (16-byte loads) for all heads of the tile
-                if (!qr.interleaved) {
-#pragma unroll 1
-                    for (int c = 0; c < half; c += 16) {
-                        float4 cs4[4], sn4[4];
-#pragma unroll
-                        for (int x = 0; x < 4; ++x) {
-                            cs4[x] = *(const float4*)(cs + c + 4 * x);
-                            sn4[x] = *(const float4*)(cs + half + c + 4 * x);
-                        }
-                        const float* cf = (const float*)cs4;
-                        const float* sf = (const float*)sn4;
-#pragma unroll 1
-                        for (int hh = 0; hh < bn / d; ++hh) {
-                            const int head = head0 + hh;
-                            if (head >= qr.nq + qr.nkv) break;               // value heads and the edge: below
-                            const bool is_q = head < qr.nq;
-                            uint32_t ra16[16], rb16[16];
-                            tmem_ld16(acc + hh * d + c, ra16);
-                            tmem_ld16(acc + hh * d + half + c, rb16);
-                            tmem_ld_wait();
-                            if (!live || (!is_q && page < 0)) continue;
-                            __nv_bfloat16* dst = head_dst(head);
-                            float ba[16], bb[16], oa[16], ob[16];
-                            load_bias16(ba, head * d + c);
-                            load_bias16(bb, head * d + half + c);
-#pragma unroll
-                            for (int x = 0; x < 16; ++x) {
-                                const float a0 = __uint_as_float(ra16[x]) + ba[x], b0 = __uint_as_float(rb16[x]) + bb[x];
-                                oa[x] = a0 * cf[x] - b0 * sf[x];
-                                ob[x] = b0 * cf[x] + a0 * sf[x];
-                            }
-                            store16(dst + c, oa);
-                            store16(dst + half + c, ob);
-                        }
-                    }
-                } else {
-#pragma unroll 1
-                    for (int c = 0; c < rdim; c += 16) {        // 16 columns = 8 pairs = angles c/2 .. c/2 + 7
-                        float4 cs4[2], sn4[2];
-#pragma unroll
-                        for (int x = 0; x < 2; ++x) {
-                            cs4[x] = *(const float4*)(cs + (c >> 1) + 4 * x);
-                            sn4[x] = *(const float4*)(cs + half + (c >> 1) + 4 * x);
-                        }
-                        const float* cf = (const float*)cs4;
-                        const float* sf = (const float*)sn4;
-#pragma unroll 1
-                        for (int hh = 0; hh < bn / d; ++hh) {
-                            const int head = head0 + hh;
-                            if (head >= qr.nq + qr.nkv) break;
-                            const bool is_q = head < qr.nq;
-                            uint32_t r16[16];
-                            tmem_ld16(acc + hh * d + c, r16);
-                            tmem_ld_wait();
-                            if (!live || (!is_q && page < 0)) continue;
-                            float bv[16], o[16];
-                            load_bias16(bv, head * d + c);
-#pragma unroll
-                            for (int x = 0; x < 8; ++x) {
-                                const float a0 = __uint_as_float(r16[2 * x]) + bv[2 * x], b0 = __uint_as_float(r16[2 * x + 1]) + bv[2 * x + 1];
-                                o[2 * x] = a0 * cf[x] - b0 * sf[x];
-                                o[2 * x + 1] = b0 * cf[x] + a0 * sf[x];
-                            }
-                            store16(head_dst(head) + c, o);
-                        }
-                    }
-                }
-                // the elements of q and k heads behind the rotated ones: bias only
-#pragma unroll 1
-                for (int c = rdim; c < d; c += 16) {
-#pragma unroll 1
-                    for (int hh = 0; hh < bn / d; ++hh) {
-                        const int head = head0 + hh;
-                        if (head >= qr.nq + qr.nkv) break;
-                        uint32_t r16[16];
-                        tmem_ld16(acc + hh * d + c, r16);
-                        tmem_ld_wait();
-                        if (!live || (head >= qr.nq && page < 0)) continue;
-                        float bv[16], o[16];
-                        load_bias16(bv, head * d + c);
-#pragma unroll
-                        for (int x = 0; x < 16; ++x) o[x] = __uint_as_float(r16[x]) + bv[x];
-                        store16(head_dst(head) + c, o);
-                    }
-                }
-                // value heads: bias, no rotation
-#pragma unroll 1
-                for (int hh = 0; hh < bn / d; ++hh) {
-                    const int head = head0 + hh;
-                    if (head < qr.nq + qr.nkv) continue;
-                    if (head >= total_heads) break;
-                    const int col0 = head * d;
-                    __nv_bfloat16* dst = qr.cache + ((((size_t)(page < 0 ? 0 : page) * 2 + 1) * qr.nkv + (head - qr.nq - qr.nkv)) * qr.P + within) * d;
-#pragma unroll 1
-                    for (int c = 0; c < d; c += 16) {
-                        uint32_t r[16];
-                        tmem_ld16(acc + hh * d + c, r);
-                        tmem_ld_wait();
-                        if (page < 0) continue;
-                        float bv[16];
-                        if (qr.bias) {
-#pragma unroll
-                            for (int x = 0; x < 4; ++x) *(float4*)(bv + 4 * x) = *(const float4*)(qr.bias + col0 + c + 4 * x);
-                        } else {
-#pragma unroll
-                            for (int x = 0; x < 16; ++x) bv[x] = 0.f;
-                        }
-                        uint32_t pk[8];
-#pragma unroll
-                        for (int x = 0; x < 8; ++x) {
-                            __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(r[2 * x]) + bv[2 * x], __uint_as_float(r[2 * x + 1]) + bv[2 * x + 1]);
-                            pk[x] = *(uint32_t*)&t2;
-                        }
-                        *(uint4*)(dst + c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                        *(uint4*)(dst + c + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-                    }
-                }
-            } else {
-#pragma unroll 1
-                for (int c0 = 0; c0 < bn; c0 += UNIT) {
-                    uint32_t r[16], r2[16];
-                    tmem_ld16(acc + c0, r);
-                    if constexpr (EPI == 1) tmem_ld16(acc + c0 + 16, r2);
-                    tmem_ld_wait();
-                    emit(ra0 + row_in_tile, rb0, c0, r, r2);
-                }
-            }
+            store_tile<OT, EPI>(acc, ra0, rb0, bn, row_in_tile, C, ldc, Ra, Rb, qr, status);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_plain(acc_empty_bar(b));    // this warp has read its quarter
@@ -887,6 +902,212 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ---- two SMs on one tile ---------------------------------------------------------------------------------
+// The persistent kernel above is paced by shared memory, not by the tensor pipe: per K block of 64 a CTA's
+// TMA writes 48 KB into shared memory and its MMAs read 48 KB back, some 190 bytes a cycle against the 512
+// cycles the four 128 x 256 x 16 MMAs take (measured: 600 to 670 cycles per K block).  Here two CTAs on
+// neighbouring SMs (a cluster of two) share a tile of 256 tokens x bn features: tcgen05.mma with
+// cta_group::2 multiplies each CTA's 128 rows of activations by ALL bn weight rows, of which each CTA holds
+// and loads only half; the tensor cores fetch the other half from the partner's shared memory.  A stage is
+// 32 KB per CTA instead of 48, so six stages fit instead of four.
+//   * every CTA loads its halves with cp.async.bulk.tensor ... .cta_group::2 (no multicast) whose bytes are
+//     counted by the full barrier of the pair's first CTA (the leader), which alone arms it;
+//   * the leader's MMA thread issues for both, and commits with tcgen05.commit ... .multicast::cluster to the
+//     barriers of both CTAs (stage free, accumulator complete);
+//   * both CTAs' epilogue warps read their own 128 lanes of tensor memory and tell the LEADER's barrier when
+//     an accumulator may be overwritten (mbarrier.arrive on the leader's shared memory);
+//   * tensor memory is allocated and freed with cta_group::2 by the same warp of both CTAs, and a cluster
+//     barrier before the end keeps either CTA's shared and tensor memory alive while the other may use it.
+// Whole tiles only (no sharing of a tile's K range); every wait is bounded as above.
+constexpr int PAIR_STAGES = 6;
+constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;     // clears the bit that tells the pair's second CTA from its first
+struct PairSmem {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = (P_BN_MAX / 2) * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BARRIER_OFFSET = PAIR_STAGES * STAGE_BYTES;
+    static constexpr int TOTAL = BARRIER_OFFSET + (2 * PAIR_STAGES + 5) * 8 + 16 + 1024;
+};
+
+__device__ __forceinline__ uint32_t pair_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void pair_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+// a tile for this CTA's shared memory whose bytes are counted by `bar`, which may be the partner's
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    const uint32_t zero = 0;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(zero) : "memory");
+}
+// arrive on the barrier at this offset in BOTH CTAs when every MMA issued so far has completed
+__device__ __forceinline__ void umma_commit_both(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & PEER_MASK) : "memory");
+}
+// D float32, A and B bfloat16, both K-major, M = 256 over the two CTAs, N = bn
+__host__ __device__ constexpr uint32_t make_idesc_pair(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+template <typename OT, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    OT* __restrict__ C, int Ra, int Rb, int K, long long ldc, int bn, int tiles_m, int num_tiles,
+                    int* __restrict__ status, const QkvRopeArgs qr, const uint32_t wait_limit) {
+    using S = PairSmem;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_base = smem_base + S::BARRIER_OFFSET;
+    auto full_bar = [&](int s) { return bar_base + 8 * s; };                                  // the leader's counts
+    auto empty_bar = [&](int s) { return bar_base + 8 * (PAIR_STAGES + s); };                 // each CTA's own
+    auto acc_full_bar = [&](int b) { return bar_base + 8 * (2 * PAIR_STAGES + b); };          // each CTA's own
+    auto acc_empty_bar = [&](int b) { return bar_base + 8 * (2 * PAIR_STAGES + 2 + b); };     // the leader's counts
+    const uint32_t drain_bar = bar_base + 8 * (2 * PAIR_STAGES + 4);
+    uint32_t* tmem_slot = (uint32_t*)(smem + S::BARRIER_OFFSET + 8 * (2 * PAIR_STAGES + 5));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = (int)pair_rank();
+    const bool leader = rank == 0;
+    const int pair = (int)blockIdx.x >> 1, npairs = (int)gridDim.x >> 1;
+    const int total_kb = (K + BK - 1) / BK;
+    const int half_bn = bn >> 1;
+    const uint32_t half_tx = S::A_BYTES + half_bn * BK * 2;       // what one CTA loads per stage
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 8); }
+        mbar_init(drain_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc_pair(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    pair_sync();            // the partner's barriers exist before anything is sent to them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+            const uint32_t count_bar0 = full_bar(0) & PEER_MASK;      // the leader's barrier of stage 0
+            int it = 0, early = 0;
+            // the weight halves of the first stages are asked for while the kernel before this one still runs
+            if (pair < num_tiles) {
+                const int rbh0 = (pair / tiles_m) * bn + rank * half_bn;
+                for (int kb = 0; kb < total_kb && early < PAIR_STAGES; ++kb, ++early) {
+                    if (leader) mbar_expect_tx(full_bar(early), 2 * half_tx);
+                    tma_load_2d_pair(smem_base + early * S::STAGE_BYTES + S::A_BYTES, &map_b, kb * BK, rbh0, count_bar0 + 8 * early);
+                }
+            }
+            pdl_wait();
+            for (int t = pair; ok && t < num_tiles; t += npairs) {
+                const int ra0 = (t % tiles_m) * 2 * BM + rank * BM, rbh0 = (t / tiles_m) * bn + rank * half_bn;
+                for (int kb = 0; kb < total_kb; ++kb, ++it) {
+                    const int s = it % PAIR_STAGES;
+                    const uint32_t a_dst = smem_base + s * S::STAGE_BYTES;
+                    if (it < early) {                   // the weight half is on its way already
+                        tma_load_2d_pair(a_dst, &map_a, kb * BK, ra0, count_bar0 + 8 * s);
+                        continue;
+                    }
+                    ok = mbar_wait(empty_bar(s), ((it / PAIR_STAGES) & 1) ^ 1, wait_limit);
+                    if (!ok) break;
+                    if (leader) mbar_expect_tx(full_bar(s), 2 * half_tx);
+                    tma_load_2d_pair(a_dst, &map_a, kb * BK, ra0, count_bar0 + 8 * s);
+                    tma_load_2d_pair(a_dst + S::A_BYTES, &map_b, kb * BK, rbh0, count_bar0 + 8 * s);
+                }
+            }
+            // nothing may still be in flight when the CTAs leave: the leader's barriers count both CTAs' bytes
+            if (leader)
+                for (int back = 1; back <= PAIR_STAGES && back <= it; ++back) {
+                    const int i = it - back;
+                    mbar_wait(full_bar(i % PAIR_STAGES), (i / PAIR_STAGES) & 1, wait_limit);
+                }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            const uint32_t idesc = make_idesc_pair(bn);
+            const uint64_t desc_a0 = make_smem_desc(smem_base), desc_b0 = make_smem_desc(smem_base + S::A_BYTES);
+            int it = 0, j = 0;
+            for (int t = pair; ok && t < num_tiles; t += npairs, ++j) {
+                const int b = j & 1;
+                ok = mbar_wait(acc_empty_bar(b), ((j >> 1) & 1) ^ 1, wait_limit);     // both epilogues have read this buffer
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = tmem_base + b * P_BN_MAX;
+                for (int kb = 0; kb < total_kb; ++kb, ++it) {
+                    const int s = it % PAIR_STAGES;
+                    ok = mbar_wait(full_bar(s), (it / PAIR_STAGES) & 1, wait_limit);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t step = (uint64_t)(s * (S::STAGE_BYTES / 16));
+                    const uint64_t da = desc_a0 + step, db = desc_b0 + step;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16_pair(acc, desc_step(da, k), desc_step(db, k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_both(empty_bar(s));         // frees the stage in both CTAs
+                }
+                if (!ok) break;
+                umma_commit_both(acc_full_bar(b));          // the accumulator is complete in both CTAs
+            }
+            if (!ok) {
+                umma_commit_pair(drain_bar);                // leaving early: not before what was issued has run
+                mbar_wait(drain_bar, 0, wait_limit);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        int j = 0;
+        for (int t = pair; ok && t < num_tiles; t += npairs, ++j) {
+            const int b = j & 1;
+            const int ra0 = (t % tiles_m) * 2 * BM + rank * BM, rb0 = (t / tiles_m) * bn;
+            ok = mbar_wait(acc_full_bar(b), (j >> 1) & 1, wait_limit);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + b * P_BN_MAX;
+            store_tile<OT, EPI>(acc, ra0, rb0, bn, row_in_tile, C, ldc, Ra, Rb, qr, status);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(acc_empty_bar(b));    // this warp has read its quarter
+        }
+    }
+    if (!ok && status) atomicOr(status, 4);
+    tc_fence_before();
+    __syncthreads();
+    pair_sync();            // the partner may still read this CTA's shared memory or write its tensor memory
+    if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
 }
 
 // ---- host: tensor maps ----------------------------------------------------------------------------
@@ -975,6 +1196,16 @@ int dispatch_bn(int bn, const CUtensorMap& ma, const CUtensorMap& mb, void* C, i
 // Iterations a bounded wait of the persistent product may take; tests shorten it to see a wait run out.
 uint32_t g_wait_limit = WAIT_LIMIT;
 
+// MHB_GEMM_PAIR=0 in the environment keeps every tile on one SM (the kernel with cta_group::1 only).
+inline bool pair_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("MHB_GEMM_PAIR");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
 // Tile width (multiple of 16, 128..256; for the SwiGLU epilogue a multiple of 32) that wastes the
 // least of the last round of whole tiles on `sms` persistent CTAs.
 int choose_persistent_bn(int tiles_m, int N, int sms, int step) {
@@ -1031,6 +1262,44 @@ int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K
         }
     }
     const bool share = ways > 1;
+    if (pair_enabled() && !share && M > BM) {
+        // two SMs on one tile of 256 tokens: whole tiles only
+        const int pairs = sms / 2;
+        int pbn = N >= P_BN_MAX ? P_BN_MAX : (N + 31) / 32 * 32;
+        const int tiles_m2 = (M + 2 * BM - 1) / (2 * BM);
+        if (EPI != 2 && N >= P_BN_MAX) pbn = choose_persistent_bn(tiles_m2, N, pairs, 32);
+        const long long pair_tiles = (long long)tiles_m2 * ((N + pbn - 1) / pbn);
+        CUtensorMap pa, pb;
+        int prc;
+        if ((prc = make_map(&pa, X, M, K, lda, BM))) return prc;
+        if ((prc = make_map(&pb, W, N, K, ldw, pbn / 2))) return prc;
+        auto pkern = gemm_tc_pair_kernel<OT, EPI>;
+        static bool pair_configured = false;
+        if (!pair_configured) {
+            cudaError_t e = cudaFuncSetAttribute(pkern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL);
+            if (e != cudaSuccess) return fail("gemm_tc: cannot set %d bytes of shared memory: %s", PairSmem::TOTAL, cudaGetErrorString(e));
+            pair_configured = true;
+        }
+        QkvRopeArgs none = {};
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(2 * (pair_tiles < pairs ? pair_tiles : pairs)));
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = PairSmem::TOTAL;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_enabled() ? 2 : 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, pkern, pa, pb, (OT*)C, M, N, K, ldc, pbn, tiles_m2, (int)pair_tiles, status,
+                                           qr ? *qr : none, g_wait_limit);
+        if (e != cudaSuccess) return fail("gemm_tc: launch of the two-SM kernel: %s", cudaGetErrorString(e));
+        return check_launch("gemm_tc_pair");
+    }
     if (EPI != 2 && !share && N >= P_BN_MAX) {     // (epilogue 2 needs tiles that begin and end on heads)
         // whole tiles only: a narrower tile may fill the last round better
         bn = choose_persistent_bn(tiles_m, N, sms, step);
