@@ -51,7 +51,7 @@ def workload(args) -> int:
     config = json.loads((ROOT / "mini_hisparse_b200" / "configs" / WORKLOADS[args.workload]).read_text())
     prompts, settings = measure.workload_prompts(args.workload, config["vocab_size"])
     line = measure.serving_workload(config, prompts=prompts, layers=args.layers, page_size=PAGE,
-                                    label=args.workload, **settings)
+                                    label=args.workload, graph_after=args.graph_after, **settings)
     line = {"metric": f"tokens/s of the {args.workload} workload (prompt and generated, through Engine.step)",
             "value": line["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "impl": "ours",
             **line}
@@ -71,6 +71,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), help="run a serving workload instead of the decode bench")
+    ap.add_argument("--graph-after", type=int, default=8,
+                    help="with --workload: capture a decode graph at the N-th step that asks for it")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")

@@ -56,7 +56,8 @@ class Engine:
     def __init__(self, model: DecoderModel, cache_config: CacheConfig | None = None, *,
                  num_pages: int | None = None, page_size: int = 16, max_requests: int = 8,
                  max_tokens_per_step: int = 2048, eos_token_id: int | None = None,
-                 use_graphs: bool = True, max_step_requests: int | None = None, pipeline: bool = True):
+                 use_graphs: bool = True, max_step_requests: int | None = None, pipeline: bool = True,
+                 graph_after: int = 8):
         self.model = model
         if cache_config is None:
             if num_pages is None:
@@ -70,7 +71,10 @@ class Engine:
         if cache_config.dtype != model.rt.dtype or torch.device(cache_config.device) != model.rt.device:
             raise ValueError("model/cache dtype or device differ")   # mini_hisparse/engine.py:36-38
         self.cache = CacheManager(model.cache_needs, cache_config)
-        self.runner = ModelRunner(model, self.cache, use_graphs=use_graphs)
+        # graph_after: a batch of decoding requests gets its captured graph at the graph_after-th step that
+        # could use it; until then its steps are launched kernel by kernel (a capture costs several steps'
+        # time, which a batch that changes every few steps never earns back)
+        self.runner = ModelRunner(model, self.cache, use_graphs=use_graphs, graph_after=graph_after)
         eos = eos_token_id if eos_token_id is not None else model.spec.eos_token_id
         self.scheduler = Scheduler(self.cache, SchedulerConfig(max_tokens_per_step, max_step_requests),
                                    model.spec.vocab_size, model.spec.max_positions, eos)

@@ -106,14 +106,14 @@ class _PlanSlot:
 
 
 class _DecodeGraph:
-    """A captured step for exactly B single-token segments whose block tables are ``width`` wide."""
+    """A captured step for exactly B single-token segments whose block tables are ``width`` wide, with
+    what the planners hold constant in it (``fixed``, one value per plan slot)."""
 
-    def __init__(self, runner: "ModelRunner", B: int, width: int):
+    def __init__(self, runner: "ModelRunner", B: int, width: int, fixed: tuple):
         self.B = B
         self.ws = Workspace(runner.device)
         batch = runner.batch
-        max_keys = width * runner.cache.cfg.page_size
-        self.fixed = [slot.planner.decode_fixed(B, max_keys) for slot in batch.slots]
+        self.fixed = list(fixed)
         self.capturable = all(f is not None for f in self.fixed)
         caps = [slot.planner.capacity(B, B, f) for slot, f in zip(batch.slots, self.fixed)]
         self.layout = _Layout(B, B, B, [min(width, g.width) for g in runner.cache.page_groups], caps)
@@ -303,7 +303,8 @@ class BatchBuilder:
 class ModelRunner:
     MAX_GRAPHS = 16      # captured decode graphs kept (each holds a workspace of its own); least recently used goes
 
-    def __init__(self, model, cache: CacheManager, use_graphs: bool = True, sm_count: int | None = None):
+    def __init__(self, model, cache: CacheManager, use_graphs: bool = True, sm_count: int | None = None,
+                 graph_after: int = 1):
         self.model, self.cache = model, cache
         self.rt = model.rt
         self.device = self.rt.device
@@ -319,12 +320,17 @@ class ModelRunner:
         if hasattr(self.rt, "status"):
             self.rt.status = self.status
         self.use_graphs = use_graphs and model.graph_safe
-        self.graphs: dict[tuple[int, int], _DecodeGraph] = {}
+        # A decode graph is captured at the ``graph_after``-th step that asks for it (a capture costs
+        # several steps' time: a batch whose size changes every few steps is served faster without);
+        # the steps before run launch by launch, with the same plans and kernels.
+        self.graph_after = max(1, int(graph_after))
+        self._asked: dict[tuple, int] = {}
+        self.graphs: dict[tuple, _DecodeGraph] = {}
         self.observer = None
         self.side_stream = None
         self.side_events = None
         self.stats = {"steps": 0, "tokens": 0, "graph_steps": 0, "graph_captures": 0, "two_stream_layers": 0,
-                      "prepared_steps": 0}
+                      "prepared_steps": 0, "graph_deferred": 0}
         self._ahead = None      # index arrays of the next decode step, packed while the GPU ran this one
         build.build_all(model.kernel_modules())
 
@@ -403,22 +409,39 @@ class ModelRunner:
         self.stats["two_stream_layers"] += ctx.extras.get("two_stream_layers", 0)
         return out
 
-    def _graph_for(self, B: int, width: int) -> _DecodeGraph:
-        g = self.graphs.pop((B, width), None)
+    def _graph_key(self, segments) -> tuple:
+        """What a captured decode graph is made for: the batch size, the block-table width and what the
+        planners want to hold constant for these histories."""
+        B, width = len(segments), self._table_width(segments)
+        starts = np.fromiter((s.start for s in segments), np.int64, B)
+        max_keys = width * self.cache.cfg.page_size
+        return B, width, tuple(slot.planner.decode_fixed_for(starts, max_keys) for slot in self.batch.slots)
+
+    def _graph_for(self, key: tuple) -> _DecodeGraph:
+        g = self.graphs.pop(key, None)
         if g is None:
-            g = _DecodeGraph(self, B, width)
+            g = _DecodeGraph(self, *key)
             while len(self.graphs) >= self.MAX_GRAPHS:          # the dict keeps the order of last use
                 old = self.graphs.pop(next(iter(self.graphs)))
                 if self._ahead is not None and self._ahead["graph"] is old:
                     self._ahead = None
-        self.graphs[(B, width)] = g
+        self.graphs[key] = g
         return g
 
     def _step_graph(self, entries, segments, ahead=None, device_tokens=None):
         """The step through a captured graph, or None if a planner cannot hold its plan constant
         (then the step runs eagerly)."""
         B = len(segments)
-        g = self._graph_for(B, self._table_width(segments))
+        key = self._graph_key(segments)
+        if key not in self.graphs and self.graph_after > 1:
+            asked = self._asked.pop(key, 0) + 1
+            if asked < self.graph_after:
+                if len(self._asked) >= 256:
+                    self._asked.pop(next(iter(self._asked)))
+                self._asked[key] = asked
+                self.stats["graph_deferred"] += 1
+                return None
+        g = self._graph_for(key)
         if not g.capturable:
             return None
         layout = g.layout
@@ -488,7 +511,7 @@ class ModelRunner:
             except CapacityError:
                 return          # the step itself will say so, if it comes to that
         segments, _ = self.batch.segments(entries)
-        g = self.graphs.get((len(segments), self._table_width(segments)))
+        g = self.graphs.get(self._graph_key(segments))
         if g is None or g.graph is None:
             return              # that step will capture its graph: nothing to gain
         stage, turn = self.batch.staging.next(g.layout.total)

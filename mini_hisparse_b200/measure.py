@@ -124,8 +124,9 @@ def build_engine(config: dict, *, batch: int, context: int, dtype="bfloat16", de
         config["num_hidden_layers"] = layers
     model = load_model(config, device=device, dtype=dtype, random_seed=weight_seed)
     pages = batch * -(-context // page_size) + extra_pages
+    # graph_after=1: the benchmarks time the steady state, and their warm-up is a few steps
     engine = Engine(model, num_pages=pages, page_size=page_size, max_requests=batch,
-                    max_tokens_per_step=max_tokens_per_step)
+                    max_tokens_per_step=max_tokens_per_step, graph_after=1)
     return engine
 
 
@@ -260,7 +261,8 @@ def _percentile(sorted_values, p):
 
 def serving_workload(config: dict, *, prompts: list[list[int]], max_new_tokens: int, max_tokens_per_step: int,
                      context: int, page_size: int = 16, dtype="bfloat16", device="cuda:0", weight_seed: int = 0,
-                     layers: int | None = None, num_pages: int | None = None, label: str = "") -> dict:
+                     layers: int | None = None, num_pages: int | None = None, label: str = "",
+                     graph_after: int = 8) -> dict:
     """Run ``prompts`` through the engine as a server would: all requests are queued at once, the
     scheduler cuts the prompts into portions of at most ``max_tokens_per_step`` tokens beside the
     decode tokens of the requests that are already generating, greedy sampling, until every request
@@ -292,7 +294,7 @@ def serving_workload(config: dict, *, prompts: list[list[int]], max_new_tokens: 
     elif num_pages is not None:
         probe_engine_pages = num_pages
     engine = Engine(model, num_pages=probe_engine_pages, page_size=page_size, max_requests=len(prompts),
-                    max_tokens_per_step=max_tokens_per_step)
+                    max_tokens_per_step=max_tokens_per_step, graph_after=graph_after)
     for i, prompt in enumerate(prompts):
         engine.add_request(f"r{i}", prompt, max_new_tokens=max_new_tokens)
     weights = decode_bytes(model, engine.cache, 0)
@@ -345,6 +347,8 @@ def serving_workload(config: dict, *, prompts: list[list[int]], max_new_tokens: 
                      "peaks": f"of {p['source']}"},
         "clocks": clocks.result, "pages": snap["cache"]["page_groups"][0]["pages_total"],
         "pages_peak": snap["cache"]["page_groups"][0]["pages_peak"], "gpu_launches": K.launches,
+        "graph_after": graph_after,
+        "graphs": {k: engine.runner.stats[k] for k in ("graph_steps", "graph_captures", "graph_deferred")},
         "data": "synthetic: seeded random weights, uniform-random token ids",
     }
 

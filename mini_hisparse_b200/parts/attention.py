@@ -225,6 +225,7 @@ class AttentionPlanner(StepPlanner):
         it merges a token's key splits inside a cluster of up to ``max_cluster`` CTAs (None: it does not)."""
         self.shape, self.sm_count = shape, sm_count
         self.clusters_of, self.max_cluster = clusters_of, max_cluster
+        self._uneven = {}        # decode_fixed_for's answers
         groups = shape.q_heads // shape.kv_heads
         self.chunks = 1 if groups <= ROW_TILE else -(-groups // ROW_TILE)
 
@@ -249,7 +250,7 @@ class AttentionPlanner(StepPlanner):
             # single tokens only: the plan of a captured decode graph, so that a step does not
             # depend on whether it is replayed or launched
             starts = np.fromiter((s.start for s in segments), np.int64, T)
-            return self.plan_decode(starts, self.decode_fixed(T, int(starts.max()) + 1))
+            return self.plan_decode(starts, self.decode_fixed_for(starts, int(starts.max()) + 1))
         return self._out(plan_attention(self.shape, segments, T, self.sm_count, fixed_nsplit=fixed))
 
     def decode_fixed(self, segments_count, max_positions):
@@ -265,6 +266,57 @@ class AttentionPlanner(StepPlanner):
             while n > 1 and self.clusters_of(n) < ctas:
                 n -= 1
         return n
+
+    # a CTA's start and end (the query and the merge), in key tiles of streaming time
+    CTA_FIXED_TILES = 3.5
+    UNEVEN_CANDIDATES = (2, 3, 4, 6, 8, 12, 16)
+
+    def decode_fixed_for(self, starts, max_positions):
+        """More key splits than decode_fixed gives when the histories are uneven: with one CTA per token
+        and KV head a batch waits for its longest history while most SMs have run out of work.  The
+        duration of the launch is estimated by dealing its CTAs (each as long as its share of keys
+        plus a fixed cost) to the resident slots in launch order, for decode_fixed's splits and for a
+        few larger numbers; a larger number is only taken when it is a sixth faster, and the answer is
+        remembered per rounded histories, so a captured graph is replaced seldom."""
+        n0 = self.decode_fixed(len(starts), max_positions)
+        B = len(starts)
+        limit = min(max_positions // MIN_KEYS_PER_SPLIT, self.max_cluster or MAX_SPLITS)
+        if B < 2 or n0 >= limit:
+            return n0
+        tiles = (np.asarray(starts, np.int64) + KEY_TILE) // KEY_TILE
+        key = (n0, limit) + tuple(((tiles + 7) // 8).tolist())
+        hit = self._uneven.get(key)
+        if hit is not None:
+            return hit
+        ctas = B * self.shape.kv_heads * self.chunks
+        best, best_time = n0, self._launch_time(tiles, n0)
+        for n in self.UNEVEN_CANDIDATES:
+            if n <= n0 or n > limit or ctas * n > 4096:
+                continue
+            t = self._launch_time(tiles, n)
+            if t < best_time and t < self._launch_time(tiles, n0) / 1.2:
+                best, best_time = n, t
+        if len(self._uneven) > 512:
+            self._uneven.clear()
+        self._uneven[key] = best
+        return best
+
+    def _launch_time(self, tiles, n: int) -> float:
+        """Key tiles of time until the last CTA of a decode launch with n key splits is done: CTAs start
+        in launch order (splits of a token together, tokens in order, KV heads outermost) on two
+        slots per SM, and a slot takes the next CTA when its own is done."""
+        import heapq
+
+        per_cta = np.repeat(-(-tiles // n) + self.CTA_FIXED_TILES, n)
+        order = np.tile(per_cta, self.shape.kv_heads * self.chunks).tolist()
+        slots = 2 * self.sm_count
+        if len(order) <= slots:
+            return max(order)
+        busy = order[:slots]
+        heapq.heapify(busy)
+        for d in order[slots:]:
+            heapq.heapreplace(busy, busy[0] + d)
+        return max(busy)
 
     def plan_decode(self, starts, fixed):
         return self._out(plan_decode(self.shape, starts, fixed), fixed if self.chunks == 1 else 0)

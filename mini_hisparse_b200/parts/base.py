@@ -245,6 +245,12 @@ class StepPlanner:
         with at most ``max_positions`` cached positions each (None: nothing)."""
         return None
 
+    def decode_fixed_for(self, starts: np.ndarray, max_positions: int):
+        """decode_fixed for a step whose single-token segments sit at positions ``starts``: a planner
+        may choose by the histories it actually sees (a graph is captured per value, so the value
+        should change seldom).  It must be hashable.  Default: decode_fixed."""
+        return self.decode_fixed(len(starts), max_positions)
+
     def plan_decode(self, starts: np.ndarray, fixed) -> tuple[dict[str, np.ndarray], dict]:
         """plan() for single-token segments at positions ``starts`` (segment i = token i = slot
         row i), as a fast path without per-token loops.  Default: the general plan."""

@@ -110,3 +110,29 @@ def test_decode_plan_for_a_captured_graph(nsplit):
     assert plan.items.shape == (4 * nsplit, ITEM_INTS)
     assert plan.part_rows == (4 * nsplit if nsplit > 1 else 0)
     check_cover(need, [(int(s), 1) for s in starts], plan)
+
+
+def test_uneven_histories_get_more_key_splits_than_even_ones():
+    """A decode batch that fills the GPU with one CTA per token and KV head waits for its longest
+    history; the planner then cuts every token's keys into a few parts (the same number for all: a
+    captured graph has a fixed launch size).  Even histories keep what decode_fixed gives, the answer
+    does not change from step to step, and the plan with more parts still covers every key once."""
+    from mini_hisparse_b200.parts.attention import AttentionPlanner
+
+    resident = {1: 296, 2: 148, 3: 98, 4: 74, 5: 59, 6: 49, 7: 42, 8: 33, 9: 30, 10: 24, 11: 24, 12: 20, 13: 20,
+                14: 20, 15: 16, 16: 16}
+    need = AttentionShape(40, 8, None, 128)
+    planner = AttentionPlanner(need, 148, lambda n: resident[n], 16)
+    uneven = np.random.default_rng(1).integers(128, 4224, 29)
+    base = planner.decode_fixed(29, 8192)
+    more = planner.decode_fixed_for(uneven, 8192)
+    assert base == 1 and 2 <= more <= 16
+    assert planner._launch_time((uneven + 64) // 64, more) < planner._launch_time((uneven + 64) // 64, base) / 1.2
+    assert all(planner.decode_fixed_for(uneven + step, 8192) == more for step in range(1, 40))
+    arrays, facts = planner.plan_decode(uneven, more)
+    assert facts["decode_nsplit"] == more
+    check_cover(need, [(int(s), 1) for s in uneven], plan_decode(need, uneven, more))
+    for B in (1, 2, 8, 16, 32, 64):        # even histories: nothing to gain
+        even = np.full(B, 4095)
+        small = AttentionPlanner(AttentionShape(28, 4, None, 128), 148, lambda n: resident[n], 16)
+        assert small.decode_fixed_for(even, 4096) == small.decode_fixed(B, 4096)

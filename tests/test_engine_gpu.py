@@ -28,7 +28,8 @@ def test_greedy_generation_equals_plain(folders, name, dtype):
     cfg, page = TINY[name]
     pc, w = P.load_folder(folders[name])
     model = load(folders[name], dtype)
-    engine = Engine(model, num_pages=64, page_size=page, max_requests=4, max_tokens_per_step=48)
+    # graph_after=2: a batch's first decode step runs launch by launch, the later ones from its graph
+    engine = Engine(model, num_pages=64, page_size=page, max_requests=4, max_tokens_per_step=48, graph_after=2)
     prompts = {str(n): random_tokens(cfg["vocab_size"], n, seed=n) for n in (7, 33, 64)}
     for rid, prompt in prompts.items():
         engine.add_request(rid, prompt, max_new_tokens=16)
@@ -47,6 +48,7 @@ def test_greedy_generation_equals_plain(folders, name, dtype):
         r = engine.requests[rid]
         assert r.prefill_count == 1 and r.decode_count == 15 and r.finished
     assert engine.runner.stats["graph_steps"] > 0        # decoding went through captured graphs
+    assert engine.runner.stats["graph_deferred"] > 0     # after steps that were launched one by one
     assert engine.stats["queued_steps"] > 0              # and steps were queued behind the step that fed them
     engine.cache.assert_invariants()
     assert not engine.cache.requests
