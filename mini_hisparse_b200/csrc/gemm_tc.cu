@@ -921,14 +921,26 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 //   * tensor memory is allocated and freed with cta_group::2 by the same warp of both CTAs, and a cluster
 //     barrier before the end keeps either CTA's shared and tensor memory alive while the other may use it.
 // Whole tiles only (no sharing of a tile's K range); every wait is bounded as above.
-constexpr int PAIR_STAGES = 6;
+//
+// A stage of the ring holds one or two K blocks of 64 (`kbs`).  The thread that issues the MMAs pays some
+// 250 cycles for the barrier it looks at before a stage, whatever the stage holds: with tiles 256 wide
+// the four MMAs of one K block (512 cycles) hide that, with narrower tiles they do not (a K block took
+// some 600 cycles at any width).  Two K blocks per stage halve the looks, so a tile half as wide takes
+// about half as long, and tile widths that fill one round of pairs (few tokens, short weight matrices)
+// pay off.  The ring has as many stages as fit (at most PAIR_MAX_STAGES); a stage is
+// [A block 0 | A block 1 | B block 0 | B block 1] with each CTA's half of the B rows.
+constexpr int PAIR_MAX_STAGES = 8;
+constexpr int PAIR_DATA_BYTES = 216 * 1024;     // operand stages of one CTA
 constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;     // clears the bit that tells the pair's second CTA from its first
 struct PairSmem {
     static constexpr int A_BYTES = BM * BK * 2;
-    static constexpr int B_BYTES = (P_BN_MAX / 2) * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int BARRIER_OFFSET = PAIR_STAGES * STAGE_BYTES;
-    static constexpr int TOTAL = BARRIER_OFFSET + (2 * PAIR_STAGES + 5) * 8 + 16 + 1024;
+    static constexpr int BARRIER_OFFSET = PAIR_DATA_BYTES;
+    static constexpr int TOTAL = BARRIER_OFFSET + (2 * PAIR_MAX_STAGES + 5) * 8 + 16 + 1024;
+};
+struct PairRing {
+    int kbs;                 // K blocks of 64 per stage: 1 or 2
+    int stages;              // stages in the ring
+    uint32_t stage_bytes;    // kbs * (A_BYTES + half_bn * 128)
 };
 
 __device__ __forceinline__ uint32_t pair_rank() {
@@ -981,29 +993,34 @@ template <typename OT, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     OT* __restrict__ C, int Ra, int Rb, int K, long long ldc, int bn, int tiles_m, int num_tiles,
-                    int* __restrict__ status, const QkvRopeArgs qr, const uint32_t wait_limit) {
+                    const PairRing ring, int* __restrict__ status, const QkvRopeArgs qr,
+                    const uint32_t wait_limit) {
     using S = PairSmem;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t bar_base = smem_base + S::BARRIER_OFFSET;
     auto full_bar = [&](int s) { return bar_base + 8 * s; };                                  // the leader's counts
-    auto empty_bar = [&](int s) { return bar_base + 8 * (PAIR_STAGES + s); };                 // each CTA's own
-    auto acc_full_bar = [&](int b) { return bar_base + 8 * (2 * PAIR_STAGES + b); };          // each CTA's own
-    auto acc_empty_bar = [&](int b) { return bar_base + 8 * (2 * PAIR_STAGES + 2 + b); };     // the leader's counts
-    const uint32_t drain_bar = bar_base + 8 * (2 * PAIR_STAGES + 4);
-    uint32_t* tmem_slot = (uint32_t*)(smem + S::BARRIER_OFFSET + 8 * (2 * PAIR_STAGES + 5));
+    auto empty_bar = [&](int s) { return bar_base + 8 * (PAIR_MAX_STAGES + s); };                 // each CTA's own
+    auto acc_full_bar = [&](int b) { return bar_base + 8 * (2 * PAIR_MAX_STAGES + b); };          // each CTA's own
+    auto acc_empty_bar = [&](int b) { return bar_base + 8 * (2 * PAIR_MAX_STAGES + 2 + b); };     // the leader's counts
+    const uint32_t drain_bar = bar_base + 8 * (2 * PAIR_MAX_STAGES + 4);
+    uint32_t* tmem_slot = (uint32_t*)(smem + S::BARRIER_OFFSET + 8 * (2 * PAIR_MAX_STAGES + 5));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rank = (int)pair_rank();
     const bool leader = rank == 0;
     const int pair = (int)blockIdx.x >> 1, npairs = (int)gridDim.x >> 1;
     const int total_kb = (K + BK - 1) / BK;
     const int half_bn = bn >> 1;
-    const uint32_t half_tx = S::A_BYTES + half_bn * BK * 2;       // what one CTA loads per stage
+    const int kbs = ring.kbs, nstages = ring.stages;
+    const int total_st = (total_kb + kbs - 1) / kbs;              // stages a tile takes (the last may hold a K block of zeros)
+    const uint32_t b_bytes = half_bn * BK * 2;                    // this CTA's rows of one K block of the weights
+    const uint32_t half_tx = kbs * (S::A_BYTES + b_bytes);        // what one CTA loads per stage
+    const uint32_t b_offset = kbs * S::A_BYTES;                   // the weights' place in a stage
 
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
-        for (int s = 0; s < PAIR_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < PAIR_MAX_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 8); }
         mbar_init(drain_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -1024,59 +1041,78 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const uint32_t count_bar0 = full_bar(0) & PEER_MASK;      // the leader's barrier of stage 0
             int it = 0, early = 0;
             // the weight halves of the first stages are asked for while the kernel before this one still runs
+            // (a K block beyond the matrix is a box outside the tensor map: zeros, counted like any other)
             if (pair < num_tiles) {
                 const int rbh0 = (pair / tiles_m) * bn + rank * half_bn;
-                for (int kb = 0; kb < total_kb && early < PAIR_STAGES; ++kb, ++early) {
+                for (int st = 0; st < total_st && early < nstages; ++st, ++early) {
                     if (leader) mbar_expect_tx(full_bar(early), 2 * half_tx);
-                    tma_load_2d_pair(smem_base + early * S::STAGE_BYTES + S::A_BYTES, &map_b, kb * BK, rbh0, count_bar0 + 8 * early);
+                    for (int kk = 0; kk < kbs; ++kk)
+                        tma_load_2d_pair(smem_base + early * ring.stage_bytes + b_offset + kk * b_bytes, &map_b,
+                                         (st * kbs + kk) * BK, rbh0, count_bar0 + 8 * early);
                 }
             }
             pdl_wait();
+            // (the stage and its turn of the ring are counted, not divided out: this thread's loop is what
+            // feeds the tensor pipe, and a division by a run-time number costs it dozens of cycles)
+            int s = 0;
+            uint32_t turn = 0;
             for (int t = pair; ok && t < num_tiles; t += npairs) {
                 const int ra0 = (t % tiles_m) * 2 * BM + rank * BM, rbh0 = (t / tiles_m) * bn + rank * half_bn;
-                for (int kb = 0; kb < total_kb; ++kb, ++it) {
-                    const int s = it % PAIR_STAGES;
-                    const uint32_t a_dst = smem_base + s * S::STAGE_BYTES;
+                for (int st = 0; st < total_st; ++st, ++it, turn ^= (s + 1 == nstages), s = (s + 1 == nstages) ? 0 : s + 1) {
+                    const uint32_t a_dst = smem_base + s * ring.stage_bytes;
                     if (it < early) {                   // the weight half is on its way already
-                        tma_load_2d_pair(a_dst, &map_a, kb * BK, ra0, count_bar0 + 8 * s);
+                        for (int kk = 0; kk < kbs; ++kk)
+                            tma_load_2d_pair(a_dst + kk * S::A_BYTES, &map_a, (st * kbs + kk) * BK, ra0, count_bar0 + 8 * s);
                         continue;
                     }
-                    ok = mbar_wait(empty_bar(s), ((it / PAIR_STAGES) & 1) ^ 1, wait_limit);
+                    ok = mbar_wait(empty_bar(s), turn ^ 1, wait_limit);
                     if (!ok) break;
                     if (leader) mbar_expect_tx(full_bar(s), 2 * half_tx);
-                    tma_load_2d_pair(a_dst, &map_a, kb * BK, ra0, count_bar0 + 8 * s);
-                    tma_load_2d_pair(a_dst + S::A_BYTES, &map_b, kb * BK, rbh0, count_bar0 + 8 * s);
+                    for (int kk = 0; kk < kbs; ++kk) {
+                        tma_load_2d_pair(a_dst + kk * S::A_BYTES, &map_a, (st * kbs + kk) * BK, ra0, count_bar0 + 8 * s);
+                        tma_load_2d_pair(a_dst + b_offset + kk * b_bytes, &map_b, (st * kbs + kk) * BK, rbh0, count_bar0 + 8 * s);
+                    }
                 }
             }
             // nothing may still be in flight when the CTAs leave: the leader's barriers count both CTAs' bytes
             if (leader)
-                for (int back = 1; back <= PAIR_STAGES && back <= it; ++back) {
+                for (int back = 1; back <= nstages && back <= it; ++back) {
                     const int i = it - back;
-                    mbar_wait(full_bar(i % PAIR_STAGES), (i / PAIR_STAGES) & 1, wait_limit);
+                    mbar_wait(full_bar(i % nstages), (i / nstages) & 1, wait_limit);
                 }
         }
     } else if (warp == 1) {
         if (lane == 0 && leader) {
             const uint32_t idesc = make_idesc_pair(bn);
-            const uint64_t desc_a0 = make_smem_desc(smem_base), desc_b0 = make_smem_desc(smem_base + S::A_BYTES);
-            int it = 0, j = 0;
+            const uint64_t desc_a0 = make_smem_desc(smem_base), desc_b0 = make_smem_desc(smem_base + b_offset);
+            const uint64_t a_step = (uint64_t)(S::A_BYTES / 16), b_step = (uint64_t)(b_bytes / 16);
+            const uint64_t stage_step = (uint64_t)(ring.stage_bytes / 16);
+            int j = 0, s = 0;
+            uint32_t turn = 0;
+            uint64_t step = 0;
             for (int t = pair; ok && t < num_tiles; t += npairs, ++j) {
                 const int b = j & 1;
                 ok = mbar_wait(acc_empty_bar(b), ((j >> 1) & 1) ^ 1, wait_limit);     // both epilogues have read this buffer
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc = tmem_base + b * P_BN_MAX;
-                for (int kb = 0; kb < total_kb; ++kb, ++it) {
-                    const int s = it % PAIR_STAGES;
-                    ok = mbar_wait(full_bar(s), (it / PAIR_STAGES) & 1, wait_limit);
+                for (int st = 0; st < total_st; ++st) {
+                    ok = mbar_wait(full_bar(s), turn, wait_limit);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint64_t step = (uint64_t)(s * (S::STAGE_BYTES / 16));
-                    const uint64_t da = desc_a0 + step, db = desc_b0 + step;
+                    uint64_t da = desc_a0 + step, db = desc_b0 + step;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_bf16_pair(acc, desc_step(da, k), desc_step(db, k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_bf16_pair(acc, desc_step(da, k), desc_step(db, k), idesc, (st > 0 || k > 0) ? 1u : 0u);
+                    if (kbs > 1) {
+                        da += a_step;
+                        db += b_step;
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k)
+                            umma_bf16_pair(acc, desc_step(da, k), desc_step(db, k), idesc, 1u);
+                    }
                     umma_commit_both(empty_bar(s));         // frees the stage in both CTAs
+                    if (++s == nstages) { s = 0; turn ^= 1; step = 0; } else { step += stage_step; }
                 }
                 if (!ok) break;
                 umma_commit_both(acc_full_bar(b));          // the accumulator is complete in both CTAs
@@ -1206,6 +1242,16 @@ inline bool pair_enabled() {
     return on == 1;
 }
 
+// MHB_GEMM_KBS=1|2 in the environment fixes the K blocks per stage of the two-SM kernel (default: by tile width).
+inline int pair_kbs() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("MHB_GEMM_KBS");
+        v = (e && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
+    }
+    return v;
+}
+
 // Tile width (multiple of 16, 128..256; for the SwiGLU epilogue a multiple of 32) that wastes the
 // least of the last round of whole tiles on `sms` persistent CTAs.
 int choose_persistent_bn(int tiles_m, int N, int sms, int step) {
@@ -1268,7 +1314,20 @@ int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K
         int pbn = N >= P_BN_MAX ? P_BN_MAX : (N + 31) / 32 * 32;
         const int tiles_m2 = (M + 2 * BM - 1) / (2 * BM);
         if (EPI != 2 && N >= P_BN_MAX) pbn = choose_persistent_bn(tiles_m2, N, pairs, 32);
+        if (EPI == 2 && qr && qr->d <= 128 && N >= P_BN_MAX) {
+            // tiles begin and end on heads: 256 wide, or 128 where that fills the rounds of pairs better
+            const long long wide = ((long long)tiles_m2 * ((N + 255) / 256) + pairs - 1) / pairs * (256 + 24);
+            const long long narrow = ((long long)tiles_m2 * ((N + 127) / 128) + pairs - 1) / pairs * (128 + 24);
+            if (narrow < wide) pbn = 128;
+        }
         const long long pair_tiles = (long long)tiles_m2 * ((N + pbn - 1) / pbn);
+        // two K blocks per stage (see PairRing): three stages of 64 KB with tiles 256 wide, four or more below 176
+        PairRing ring;
+        ring.kbs = pair_kbs() ? pair_kbs() : 2;
+        ring.stage_bytes = (uint32_t)ring.kbs * (PairSmem::A_BYTES + (pbn / 2) * BK * 2);
+        ring.stages = PAIR_DATA_BYTES / (int)ring.stage_bytes;
+        if (ring.stages > PAIR_MAX_STAGES) ring.stages = PAIR_MAX_STAGES;
+        if (ring.stages < 2) return fail("gemm_tc: a stage of %u bytes leaves no ring", ring.stage_bytes);
         CUtensorMap pa, pb;
         int prc;
         if ((prc = make_map(&pa, X, M, K, lda, BM))) return prc;
@@ -1295,8 +1354,8 @@ int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = pdl_enabled() ? 2 : 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, pkern, pa, pb, (OT*)C, M, N, K, ldc, pbn, tiles_m2, (int)pair_tiles, status,
-                                           qr ? *qr : none, g_wait_limit);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, pkern, pa, pb, (OT*)C, M, N, K, ldc, pbn, tiles_m2, (int)pair_tiles, ring,
+                                           status, qr ? *qr : none, g_wait_limit);
         if (e != cudaSuccess) return fail("gemm_tc: launch of the two-SM kernel: %s", cudaGetErrorString(e));
         return check_launch("gemm_tc_pair");
     }
