@@ -1313,7 +1313,7 @@ int launch_persistent(const void* X, const void* W, void* C, int M, int N, int K
         const int pairs = sms / 2;
         int pbn = N >= P_BN_MAX ? P_BN_MAX : (N + 31) / 32 * 32;
         const int tiles_m2 = (M + 2 * BM - 1) / (2 * BM);
-        if (EPI != 2 && N >= P_BN_MAX) pbn = choose_persistent_bn(tiles_m2, N, pairs, 32);
+        if (EPI != 2 && N >= P_BN_MAX) pbn = choose_persistent_bn(tiles_m2, N, pairs, EPI == 1 ? 32 : 16);
         if (EPI == 2 && qr && qr->d <= 128 && N >= P_BN_MAX) {
             // tiles begin and end on heads: 256 wide, or 128 where that fills the rounds of pairs better
             const long long wide = ((long long)tiles_m2 * ((N + 255) / 256) + pairs - 1) / pairs * (256 + 24);
