@@ -910,8 +910,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 // cycles the four 128 x 256 x 16 MMAs take (measured: 600 to 670 cycles per K block).  Here two CTAs on
 // neighbouring SMs (a cluster of two) share a tile of 256 tokens x bn features: tcgen05.mma with
 // cta_group::2 multiplies each CTA's 128 rows of activations by ALL bn weight rows, of which each CTA holds
-// and loads only half; the tensor cores fetch the other half from the partner's shared memory.  A stage is
-// 32 KB per CTA instead of 48, so six stages fit instead of four.
+// and loads only half; the tensor cores fetch the other half from the partner's shared memory.  A K block
+// is 32 KB per CTA instead of 48.
 //   * every CTA loads its halves with cp.async.bulk.tensor ... .cta_group::2 (no multicast) whose bytes are
 //     counted by the full barrier of the pair's first CTA (the leader), which alone arms it;
 //   * the leader's MMA thread issues for both, and commits with tcgen05.commit ... .multicast::cluster to the
