@@ -259,12 +259,21 @@ class AttentionPlanner(StepPlanner):
         second wave, and no split shorter than MIN_KEYS_PER_SPLIT keys."""
         ctas = segments_count * self.shape.kv_heads * self.chunks
         n = max(1, min(MAX_SPLITS, (2 * self.sm_count) // ctas, max_positions // MIN_KEYS_PER_SPLIT))
-        if self.clusters_of is not None and self.chunks == 1 and 1 < n <= self.max_cluster:
-            # the splits of a token form a cluster, and clusters are placed inside one GPC: take the
-            # largest size of which all the step's clusters run at once (a second round of clusters
-            # costs more than shorter shares gain)
-            while n > 1 and self.clusters_of(n) < ctas:
-                n -= 1
+        if self.clusters_of is not None and self.chunks == 1 and n > 1:
+            # The splits of a token form a cluster, and a cluster is placed inside one GPC: take the
+            # largest size of which all the step's clusters run at once (a second round of clusters costs
+            # more than shorter shares gain).  The driver's count of resident clusters holds when nothing
+            # else is on the GPU; the kernel before this one is still leaving, so large clusters, of which
+            # a GPC holds two or three and has no room left, get two clusters of margin (measured at the
+            # 7B shape: 16 clusters of 13, of which 17 should fit, and 20 of 12, of which 21 should, took
+            # as long as two rounds; 16 of 12, 20 and 24 of 10 and 32 of 8, of which 33 should fit, did not).
+            # More splits than the largest cluster would go through four launches (rotary and append,
+            # attention, merge); the one fused launch wins as long as its shares are not four times longer.
+            m = min(n, self.max_cluster)
+            while m > 1 and self.clusters_of(m) < ctas + (2 if m > 10 else 0):
+                m -= 1
+            if m > 1 and 4 * m >= n:
+                n = m
         return n
 
     # a CTA's start and end (the query and the merge), in key tiles of streaming time
@@ -281,7 +290,7 @@ class AttentionPlanner(StepPlanner):
         n0 = self.decode_fixed(len(starts), max_positions)
         B = len(starts)
         limit = min(max_positions // MIN_KEYS_PER_SPLIT, self.max_cluster or MAX_SPLITS)
-        if B < 2 or n0 >= limit:
+        if n0 > 1 or B < 2 or limit < 2:       # fewer requests: their splits are sized for one round of CTAs
             return n0
         tiles = (np.asarray(starts, np.int64) + KEY_TILE) // KEY_TILE
         key = (n0, limit) + tuple(((tiles + 7) // 8).tolist())

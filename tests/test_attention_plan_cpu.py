@@ -136,3 +136,21 @@ def test_uneven_histories_get_more_key_splits_than_even_ones():
         even = np.full(B, 4095)
         small = AttentionPlanner(AttentionShape(28, 4, None, 128), 148, lambda n: resident[n], 16)
         assert small.decode_fixed_for(even, 4096) == small.decode_fixed(B, 4096)
+
+
+def test_cluster_sizes_of_a_decode_step():
+    """decode_fixed with the resident-cluster counts that the driver reports for the decode kernel on a
+    B200 (two CTAs per SM): the largest cluster of which all of a step's clusters run at once, with
+    two clusters to spare above ten CTAs a cluster, and never more splits than the largest cluster
+    when the fused launch's shares are at most four times longer."""
+    from mini_hisparse_b200.parts.attention import AttentionPlanner
+
+    reported = {1: 296, 2: 148, 3: 93, 4: 71, 5: 56, 6: 45, 7: 37, 8: 33, 9: 30, 10: 26, 11: 21, 12: 21, 13: 17,
+                14: 14, 15: 14, 16: 14}
+    planner = AttentionPlanner(AttentionShape(28, 4, None, 128), 148, lambda n: reported[n], 16)
+    assert [planner.decode_fixed(B, 4096) for B in (1, 2, 3, 4, 5, 6, 8, 16, 32, 64)] == [16, 16, 16, 12, 10, 10, 8, 4, 2, 1]
+    assert planner.decode_fixed(1, 32768) == 16          # 64 shorter shares would need the unfused launches
+    assert planner.decode_fixed(4, 32768) == 12
+    assert planner.decode_fixed(8, 512) == 2             # no share shorter than 256 keys
+    plain = AttentionPlanner(AttentionShape(28, 4, None, 128), 148)      # a kernel without clusters
+    assert plain.decode_fixed(1, 32768) == 64 and plain.decode_fixed(4, 4096) == 16
