@@ -21,8 +21,13 @@
 //     r + nsplit, ...; plain st.shared::cluster), one cluster barrier follows, and each owner merges
 //     what it received in split order (so the result does not depend on timing) from its own shared
 //     memory and writes the row; no partial goes through global memory.
-// Head size 64 or 128, pages that divide 64, at most 16 heads per KV head, at most 16 splits, and at
-// most 16 received rows per CTA (splits x rows owned).
+//   * one request far into a long context has too few clusters of 16 to keep the memory busy (four
+//     KV heads: 64 CTAs).  Its keys can then be cut into ngroups x nsplit shares: ngroups clusters per
+//     token and KV head, each merging its own nsplit shares as above and leaving ONE unnormalised part
+//     per query head (accumulator, scaled maximum, sum) in the partial buffers that attention_combine
+//     merges; the cluster that owns the token's position appends its key and value.
+// Head size 64 or 128, pages that divide 64, at most 16 heads per KV head, at most 16 splits a cluster, and
+// at most 16 received rows per CTA (splits x rows owned).
 // Every mbarrier wait is bounded (status bit 8); a CTA whose wait ran out still walks through the
 // cluster barriers, waits for its armed copies, and writes nothing.
 #include "mma_helpers.cuh"
@@ -46,12 +51,14 @@ struct DecodeArgs {
     const float* inv_freq;     // [rdim / 2] or null
     __nv_bfloat16* cache;      // this layer's pool [pages, 2, nkv, P, D]
     __nv_bfloat16* out;        // [T, nq D]
+    float* part_acc;           // ngroups > 1: [T * ngroups, nq, D] unnormalised sums of each cluster
+    float* part_ml;            // ngroups > 1: [T * ngroups, nq, 2] scaled maximum and sum of exponentials
     const int* positions;      // [T]
     const int* block_table;    // [T, width]: token i is segment i
     int* status;
     long long qkv_split_stride;
     int qkv_nsplit, rdim, interleaved;
-    int T, width, nq, nkv, P, num_pages, window, nsplit;
+    int T, width, nq, nkv, P, num_pages, window, nsplit, ngroups;
     float scale;
 };
 
@@ -171,7 +178,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const Decode
 
     pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int t = blockIdx.x / a.nsplit, split = blockIdx.x - t * a.nsplit;   // split == rank in the cluster
+    // blockIdx.x = (token, group of shares, share in the group); the share in the group is the rank in the cluster
+    const int per_token = a.ngroups * a.nsplit;
+    const int t = blockIdx.x / per_token, share = blockIdx.x - t * per_token;
+    const int group = share / a.nsplit, split = share - group * a.nsplit;
     const int kvh = blockIdx.y;
     const int groups = a.nq / a.nkv, nrows = groups;
     const int pos = a.positions[t];
@@ -179,8 +189,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const Decode
     const int kv_first = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     // the split's keys: equal shares rounded up to whole tiles, as the host's plan for such a batch
     const int span = kv_end - kv_first;
-    const int chunk = (((span + a.nsplit - 1) / a.nsplit + KT - 1) / KT) * KT;
-    const int kv_begin = min(kv_end, kv_first + split * chunk);
+    const int chunk = (((span + per_token - 1) / per_token + KT - 1) / KT) * KT;
+    const int kv_begin = min(kv_end, kv_first + share * chunk);
     const int kv_stop = min(kv_end, kv_begin + chunk);
     const bool owner = kv_stop == kv_end && kv_stop > kv_begin;             // this CTA sees the token's own key
     const int tile_begin = (kv_begin / KT) * KT;
@@ -484,7 +494,19 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, const Decode
                     acc += w * src[e];
                     lsum += w * src[D + 1];
                 }
-                a.out[((size_t)t * a.nq + kvh * groups + r) * D + e] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+                const size_t head = (size_t)kvh * groups + r;
+                if (a.ngroups == 1) {
+                    a.out[((size_t)t * a.nq + head) * D + e] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+                } else if (cta_failed == 0) {
+                    // this cluster's part of the token: attention_combine merges the groups in order
+                    const size_t prow = (size_t)t * a.ngroups + group;
+                    a.part_acc[(prow * a.nq + head) * D + e] = acc;
+                    if (e == 0) {
+                        float* ml = a.part_ml + (prow * a.nq + head) * 2;
+                        ml[0] = (lsum > 0.f && M > -INFINITY) ? M * a.scale : -INFINITY;
+                        ml[1] = lsum;
+                    }
+                }
             }
         }
         if (owner && cta_failed == 0) {
@@ -551,7 +573,7 @@ int launch(const CUtensorMap& map, const DecodeArgs& a, cudaStream_t stream) {
     int rc = configure<D>();
     if (rc) return rc;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(a.T * a.nsplit, a.nkv);
+    cfg.gridDim = dim3(a.T * a.ngroups * a.nsplit, a.nkv);
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -585,13 +607,17 @@ MHB_EXPORT int mhb_attention_decode_max_clusters(int d, int nsplit) {
 // qkv: the stacked q/k/v product of T single tokens as qkv_nsplit float32 partial matrices
 // [T, (nq + 2 nkv) d], qkv_split_stride elements apart; cache: one layer's pool [num_pages, 2, nkv, P, d]
 // bfloat16, block_table [T, width] (row i: the pages of token i's request), positions [T].
-// Every token's keys are cut into nsplit equal shares (whole tiles of 64); out [T, nq d] bfloat16.
+// Every token's keys are cut into ngroups * nsplit equal shares (whole tiles of 64), nsplit of them to a
+// cluster; out [T, nq d] bfloat16.  With ngroups > 1 nothing is written to out: each cluster leaves its part
+// in part_acc [T * ngroups, nq, d] and part_ml [T * ngroups, nq, 2] (row t * ngroups + g) for attention_combine.
 MHB_EXPORT int mhb_attention_decode(const float* qkv, int qkv_nsplit, long long qkv_split_stride, const float* bias,
                                     const float* inv_freq, int rotary_dim, int interleaved, void* cache, void* out,
                                     const int* positions, const int* block_table, int width, int T, int nq, int nkv,
-                                    int d, int P, int num_pages, int window, int nsplit, float scale, int* status,
-                                    cudaStream_t stream) {
+                                    int d, int P, int num_pages, int window, int nsplit, int ngroups, float* part_acc,
+                                    float* part_ml, float scale, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (ngroups < 1 || ngroups > 64) return fail("attention_decode: %d groups of key shares", ngroups);
+    if (ngroups > 1 && (!part_acc || !part_ml)) return fail("attention_decode: groups of key shares need the partial buffers");
     if (nkv <= 0 || nq % nkv) return fail("attention: %d query heads over %d KV heads", nq, nkv);
     if (!mhb_attention_decode_supports(d, P, nq / nkv, nsplit, rotary_dim))
         return fail("attention_decode: head_dim %d, pages of %d keys, %d heads per KV head, %d key splits, %d rotated "
@@ -611,5 +637,6 @@ MHB_EXPORT int mhb_attention_decode(const float* qkv, int qkv_nsplit, long long 
     a.positions = positions; a.block_table = block_table; a.status = status; a.qkv_split_stride = qkv_split_stride;
     a.qkv_nsplit = qkv_nsplit; a.rdim = rotary_dim; a.interleaved = interleaved ? 1 : 0; a.T = T; a.width = width;
     a.nq = nq; a.nkv = nkv; a.P = P; a.num_pages = num_pages; a.window = window; a.nsplit = nsplit; a.scale = scale;
+    a.ngroups = ngroups; a.part_acc = part_acc; a.part_ml = part_ml;
     return d == 128 ? launch<128>(map, a, stream) : launch<64>(map, a, stream);
 }

@@ -184,13 +184,14 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
                                          const float* __restrict__ part_ml,
                                          const int* __restrict__ tok_part_row,
                                          const int* __restrict__ tok_nsplit, OT* __restrict__ out,
-                                         int nq, int d) {
+                                         int nq, int d, int every) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y;
-    const int ns = tok_nsplit[t];
+    // every > 0: each token has exactly that many parts, in the rows t * every ...
+    const int ns = every > 0 ? every : tok_nsplit[t];
     if (ns <= 0) return;  // written directly by the attention kernel
-    const size_t row0 = tok_part_row[t];
+    const size_t row0 = every > 0 ? (size_t)t * every : tok_part_row[t];
     float M = -INFINITY;
     for (int s = 0; s < ns; ++s) M = fmaxf(M, part_ml[((row0 + s) * nq + h) * 2]);
     float L = 0.f;
@@ -255,14 +256,17 @@ MHB_EXPORT int mhb_attention_simt(const void* q, const void* cache, void* out, i
     return 0;
 }
 
+// every > 0: token t has `every` parts in the rows t * every ... of the partial buffers (tok_part_row and
+// tok_nsplit are not read); else token t has tok_nsplit[t] parts from row tok_part_row[t].
 MHB_EXPORT int mhb_attention_combine(const float* part_acc, const float* part_ml,
                                      const int* tok_part_row, const int* tok_nsplit, void* out,
-                                     int dtype, int T, int nq, int d, cudaStream_t stream) {
+                                     int dtype, int T, int nq, int d, int every, cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (every <= 0 && (!tok_part_row || !tok_nsplit)) return fail("attention_combine: no list of parts");
     dim3 grid(T, nq);
     const int threads = d >= 128 ? 128 : 32 * ((d + 31) / 32);
     MHB_DISPATCH_DTYPE(dtype, OT,
         launch_kernel(attention_combine_kernel<OT>, grid, dim3(threads), 0, stream, part_acc, part_ml,
-                      tok_part_row, tok_nsplit, (OT*)out, nq, d));
+                      tok_part_row, tok_nsplit, (OT*)out, nq, d, every));
     return check_launch("attention_combine");
 }

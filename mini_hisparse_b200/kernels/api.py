@@ -373,12 +373,16 @@ def attention_decode_max_clusters(d: int, nsplit: int) -> int:
 
 def attention_decode(qkv, bias, inv_freq, cache, out, positions, block_table, *, nq, nkv, d, page_size, nsplit,
                      qkv_nsplit=1, qkv_split_stride=0, rotary_dim=None, interleaved=False, window=0, scale=None,
-                     status=None):
+                     status=None, ngroups=1, part_acc=None, part_ml=None):
     """A batch of single new tokens in one kernel: the q/k/v product's float32 partials ``qkv``
     ([qkv_nsplit, T, (nq + 2 nkv) d], ``qkv_split_stride`` elements apart) are summed, biased and
     rotated, k and v are appended to ``cache`` (one layer's pool), every token attends over its
     ``nsplit`` equal shares of keys and the shares are merged inside a thread-block cluster.
-    Token i is segment i: ``block_table`` [T, width], ``positions`` [T]; ``out`` [T, nq d] bfloat16."""
+    Token i is segment i: ``block_table`` [T, width], ``positions`` [T]; ``out`` [T, nq d] bfloat16.
+
+    ``ngroups`` > 1 cuts every token's keys into ngroups * nsplit shares, ngroups clusters per token and
+    KV head: each cluster leaves its part in ``part_acc`` [T * ngroups, nq, d] and ``part_ml``
+    [T * ngroups, nq, 2], and ``out`` is written by attention_combine(..., every=ngroups)."""
     lib = build.load("attention_decode")
     T = out.shape[0]
     if qkv.dtype != torch.float32 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
@@ -395,8 +399,11 @@ def attention_decode(qkv, bias, inv_freq, cache, out, positions, block_table, *,
         _ptr(qkv), c_int(qkv_nsplit), c_longlong(qkv_split_stride), _ptr(bias), _ptr(inv_freq), c_int(rotary_dim),
         c_int(1 if interleaved else 0), _ptr(cache), _ptr(out), _ptr(positions), _ptr(block_table),
         c_int(block_table.shape[-1]), c_int(T), c_int(nq), c_int(nkv), c_int(d), c_int(page_size),
-        c_int(cache.shape[0]), c_int(window or 0), c_int(nsplit), c_float(scale), _ptr(status), _stream()),
+        c_int(cache.shape[0]), c_int(window or 0), c_int(nsplit), c_int(ngroups), _ptr(part_acc), _ptr(part_ml),
+        c_float(scale), _ptr(status), _stream()),
         "attention_decode")
+    if ngroups > 1:
+        attention_combine(part_acc, part_ml, None, None, out, nq=nq, d=d, every=ngroups)
 
 
 def attention_tc(q, cache, out, items, num_items, positions, block_table, *, nq, nkv, d, page_size,
@@ -417,12 +424,14 @@ def attention_tc(q, cache, out, items, num_items, positions, block_table, *, nq,
         c_int(cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(status), _stream()), "attention_tc")
 
 
-def attention_combine(part_acc, part_ml, tok_part_row, tok_nsplit, out, *, nq, d):
+def attention_combine(part_acc, part_ml, tok_part_row, tok_nsplit, out, *, nq, d, every=0):
+    """Merge the parts of every token's attention.  ``every`` > 0: each token has exactly that many parts,
+    in the rows t * every ... of the partial buffers (the two index arrays may be None)."""
     lib = build.load("attention_simt")
     T = out.shape[0]
     _check(lib, lib.mhb_attention_combine(_ptr(part_acc), _ptr(part_ml), _ptr(tok_part_row),
                                           _ptr(tok_nsplit), _ptr(out), c_int(dtype_code(out.dtype)),
-                                          c_int(T), c_int(nq), c_int(d), _stream()),
+                                          c_int(T), c_int(nq), c_int(d), c_int(every), _stream()),
            "attention_combine")
 
 

@@ -231,18 +231,20 @@ class AttentionPlanner(StepPlanner):
 
     def capacity(self, max_tokens, max_segments, fixed=None):
         if fixed is not None:            # a captured graph of single tokens: exactly these many
-            return {"items": max_segments * fixed * self.chunks * ITEM_INTS, "tok_part_row": max_tokens,
+            return {"items": max_segments * fixed[0] * fixed[1] * self.chunks * ITEM_INTS, "tok_part_row": max_tokens,
                     "tok_nsplit": max_tokens}
         items, _ = plan_capacity(self.shape, max_tokens, max_segments)
         return {"items": items * ITEM_INTS, "tok_part_row": max_tokens, "tok_nsplit": max_tokens}
 
     @staticmethod
-    def _out(plan: AttentionPlan, decode_nsplit: int = 0):
+    def _out(plan: AttentionPlan, decode_nsplit: int = 0, decode_groups: int = 1):
         arrays = {"items": plan.items.reshape(-1), "tok_part_row": plan.tok_part_row, "tok_nsplit": plan.tok_nsplit}
         # decode_nsplit > 0: the step is single tokens only (token i = segment i), every one with
-        # exactly that many equal shares of keys: what a kernel that plans for itself needs to know
+        # decode_groups x decode_nsplit equal shares of keys, decode_nsplit of them to a cluster: what a
+        # kernel that plans for itself needs to know
         facts = {"n_small": plan.n_small, "n_big": plan.n_big, "part_rows_cap": plan.part_rows,
-                 "any_split": bool(plan.part_rows), "big_split": plan.big_split, "decode_nsplit": decode_nsplit}
+                 "any_split": bool(plan.part_rows), "big_split": plan.big_split, "decode_nsplit": decode_nsplit,
+                 "decode_groups": decode_groups}
         return arrays, facts
 
     def plan(self, segments, T, fixed=None):
@@ -251,33 +253,62 @@ class AttentionPlanner(StepPlanner):
             # depend on whether it is replayed or launched
             starts = np.fromiter((s.start for s in segments), np.int64, T)
             return self.plan_decode(starts, self.decode_fixed_for(starts, int(starts.max()) + 1))
-        return self._out(plan_attention(self.shape, segments, T, self.sm_count, fixed_nsplit=fixed))
+        every = None if fixed is None else fixed[0] * fixed[1]
+        return self._out(plan_attention(self.shape, segments, T, self.sm_count, fixed_nsplit=every))
+
+    # what a CTA costs beside its keys (the query and the merge) and what a launch of attention_combine
+    # costs the step, in key tiles of streaming time
+    CTA_FIXED_TILES = 3.5
+    COMBINE_TILES = 8.0
+    STREAMS = 240.0          # CTAs streaming at a lone CTA's rate that the memory can feed
 
     def decode_fixed(self, segments_count, max_positions):
-        """Key splits per decoded token for a batch of B with at most ``max_positions`` cached keys: as
-        many CTAs as are resident at once (two per SM), never more, so that no CTA waits for a
-        second wave, and no split shorter than MIN_KEYS_PER_SPLIT keys."""
+        """Key shares per decoded token for a batch of B with at most ``max_positions`` cached keys, as
+        (shares in a cluster, clusters per token and KV head): as many CTAs as are resident at once (two per
+        SM), never more, so that no CTA waits for a second wave, and no share shorter than
+        MIN_KEYS_PER_SPLIT keys.  Without a cluster kernel: (shares, 1)."""
         ctas = segments_count * self.shape.kv_heads * self.chunks
         n = max(1, min(MAX_SPLITS, (2 * self.sm_count) // ctas, max_positions // MIN_KEYS_PER_SPLIT))
-        if self.clusters_of is not None and self.chunks == 1 and n > 1:
-            # The splits of a token form a cluster, and a cluster is placed inside one GPC: take the
-            # largest size of which all the step's clusters run at once (a second round of clusters costs
-            # more than shorter shares gain).  The driver's count of resident clusters holds when nothing
-            # else is on the GPU; the kernel before this one is still leaving, so large clusters, of which
-            # a GPC holds two or three and has no room left, get two clusters of margin (measured at the
-            # 7B shape: 16 clusters of 13, of which 17 should fit, and 20 of 12, of which 21 should, took
-            # as long as two rounds; 16 of 12, 20 and 24 of 10 and 32 of 8, of which 33 should fit, did not).
-            # More splits than the largest cluster would go through four launches (rotary and append,
-            # attention, merge); the one fused launch wins as long as its shares are not four times longer.
-            m = min(n, self.max_cluster)
-            while m > 1 and self.clusters_of(m) < ctas + (2 if m > 10 else 0):
-                m -= 1
-            if m > 1 and 4 * m >= n:
-                n = m
-        return n
+        if self.clusters_of is None or self.chunks != 1 or n == 1:
+            return n, 1
+        # The shares of a cluster are merged in its shared memory, and a cluster is placed inside one
+        # GPC: all the step's clusters must run at once (a second round of clusters costs more than
+        # shorter shares gain).  The driver's count of resident clusters holds when nothing else is on
+        # the GPU; the kernel before this one is still leaving, so large clusters, of which a GPC holds
+        # two or three and has no room left, get two clusters of margin (measured at the 7B shape: 16
+        # clusters of 13, of which 17 should fit, and 20 of 12, of which 21 should, took as long as two
+        # rounds; 16 of 12, 20 and 24 of 10 and 32 of 8, of which 33 should fit, did not).  One or two
+        # requests far into a long context have too few clusters of the largest size to keep the memory
+        # busy: they get several clusters per token and KV head, whose parts attention_combine merges.
+        # A launch is timed in the key tiles its longest CTA walks at the rate of a CTA that streams
+        # alone; all CTAs together cannot walk more than some 240 tiles in that time (the memory's rate
+        # over one CTA's), a CTA has a fixed cost, and parts left for attention_combine cost a launch and
+        # a pass over them: several clusters per token must be a tenth faster by this count to be taken
+        # (measured, 7B shape: one request at 32,000 keys 3.48 -> 3.18 ms a step with 8 clusters of 8;
+        # two requests at 16,000 keys were no faster with 4 clusters of 8 than with one of 16).
+        tiles = -(-max_positions // KEY_TILE)
+        floor = ctas * tiles / self.STREAMS
 
-    # a CTA's start and end (the query and the merge), in key tiles of streaming time
-    CTA_FIXED_TILES = 3.5
+        def cost(c, g):
+            return max(-(-tiles // (c * g)), floor) + self.CTA_FIXED_TILES + (self.COMBINE_TILES if g > 1 else 0.0)
+
+        def room(c):
+            return self.clusters_of(c) - (2 if c > 10 else 0)
+
+        best = None
+        for c in range(min(n, self.max_cluster), 1, -1):
+            if room(c) >= ctas:
+                best = (c, 1)
+                break
+        if best is not None:
+            best_cost = 0.9 * cost(*best)
+            for c in range(min(n, self.max_cluster), 3, -1):
+                for g in range(2, min(n // c, room(c) // ctas) + 1):
+                    if cost(c, g) < best_cost:
+                        best, best_cost = (c, g), cost(c, g)
+        # no cluster fits: the shares go through the kernels that merge through global memory
+        return best if best is not None else (n, 1)
+
     UNEVEN_CANDIDATES = (2, 3, 4, 6, 8, 12, 16)
 
     def decode_fixed_for(self, starts, max_positions):
@@ -287,11 +318,12 @@ class AttentionPlanner(StepPlanner):
         plus a fixed cost) to the resident slots in launch order, for decode_fixed's splits and for a
         few larger numbers; a larger number is only taken when it is a sixth faster, and the answer is
         remembered per rounded histories, so a captured graph is replaced seldom."""
-        n0 = self.decode_fixed(len(starts), max_positions)
+        fixed = self.decode_fixed(len(starts), max_positions)
+        n0 = fixed[0] * fixed[1]
         B = len(starts)
         limit = min(max_positions // MIN_KEYS_PER_SPLIT, self.max_cluster or MAX_SPLITS)
         if n0 > 1 or B < 2 or limit < 2:       # fewer requests: their splits are sized for one round of CTAs
-            return n0
+            return fixed
         tiles = (np.asarray(starts, np.int64) + KEY_TILE) // KEY_TILE
         key = (n0, limit) + tuple(((tiles + 7) // 8).tolist())
         hit = self._uneven.get(key)
@@ -307,8 +339,8 @@ class AttentionPlanner(StepPlanner):
                 best, best_time = n, t
         if len(self._uneven) > 512:
             self._uneven.clear()
-        self._uneven[key] = best
-        return best
+        self._uneven[key] = (best, 1)
+        return best, 1
 
     def _launch_time(self, tiles, n: int) -> float:
         """Key tiles of time until the last CTA of a decode launch with n key splits is done: CTAs start
@@ -328,7 +360,8 @@ class AttentionPlanner(StepPlanner):
         return max(busy)
 
     def plan_decode(self, starts, fixed):
-        return self._out(plan_decode(self.shape, starts, fixed), fixed if self.chunks == 1 else 0)
+        cluster, groups = fixed
+        return self._out(plan_decode(self.shape, starts, cluster * groups), cluster if self.chunks == 1 else 0, groups)
 
 
 @register_mixer("gq_attention")
@@ -428,18 +461,23 @@ class GQAttention(Mixer):
         family = self.kernel_family(cache.page_size)
         rdim = int(getattr(self.position, "rotary_dim", 0) or 0)
         interleaved = bool(getattr(self.position, "interleaved", False))
-        nsplit = meta.get("decode_nsplit", 0)
+        nsplit, ngroups = meta.get("decode_nsplit", 0), meta.get("decode_groups", 1)
         if (family == "tc" and nsplit and cache.writable
                 and K.attention_decode_supports(self.d, cache.page_size, self.nq // self.nkv, nsplit, rdim)):
             # single new tokens only: sum of the product's parts, bias, rotation, append, attention and
             # the merge of the key splits are one kernel
             qkv = rt.linear(h, self.qkv_weight, ws, "qkv", out_dtype=torch.float32)
             attn = ws.get("attn", (T, self.nq * self.d), rt.dtype)
+            parts = {}
+            if ngroups > 1:         # several clusters per token and KV head leave a part each
+                parts = dict(ngroups=ngroups,
+                             part_acc=ws.get("attn_part_acc", (T * ngroups, self.nq, self.d), torch.float32),
+                             part_ml=ws.get("attn_part_ml", (T * ngroups, self.nq, 2), torch.float32))
             K.attention_decode(qkv.tensor, self.qkv_bias_vec, self.position.inv_freq, cache.storage, attn,
                                ctx.positions, meta["block_table"], nq=self.nq, nkv=self.nkv, d=self.d,
                                page_size=cache.page_size, nsplit=nsplit, qkv_nsplit=qkv.nsplit,
                                qkv_split_stride=qkv.split_stride, rotary_dim=rdim, interleaved=interleaved,
-                               window=self.window or 0, scale=self.scale, status=ctx.status)
+                               window=self.window or 0, scale=self.scale, status=ctx.status, **parts)
             return rt.linear(attn, self.o_weight, ws, "mix_out")
         q = ws.get("q", (T, self.nq * self.d), rt.dtype)
         fused = rt.qkv_rope_append(h, self.qkv_weight, self.qkv_bias_vec, ctx, self.position, meta["block_table"],

@@ -126,12 +126,12 @@ def test_uneven_histories_get_more_key_splits_than_even_ones():
     uneven = np.random.default_rng(1).integers(128, 4224, 29)
     base = planner.decode_fixed(29, 8192)
     more = planner.decode_fixed_for(uneven, 8192)
-    assert base == 1 and 2 <= more <= 16
-    assert planner._launch_time((uneven + 64) // 64, more) < planner._launch_time((uneven + 64) // 64, base) / 1.2
+    assert base == (1, 1) and 2 <= more[0] <= 16 and more[1] == 1
+    assert planner._launch_time((uneven + 64) // 64, more[0]) < planner._launch_time((uneven + 64) // 64, 1) / 1.2
     assert all(planner.decode_fixed_for(uneven + step, 8192) == more for step in range(1, 40))
     arrays, facts = planner.plan_decode(uneven, more)
-    assert facts["decode_nsplit"] == more
-    check_cover(need, [(int(s), 1) for s in uneven], plan_decode(need, uneven, more))
+    assert facts["decode_nsplit"] == more[0] and facts["decode_groups"] == 1
+    check_cover(need, [(int(s), 1) for s in uneven], plan_decode(need, uneven, more[0]))
     for B in (1, 2, 8, 16, 32, 64):        # even histories: nothing to gain
         even = np.full(B, 4095)
         small = AttentionPlanner(AttentionShape(28, 4, None, 128), 148, lambda n: resident[n], 16)
@@ -148,9 +148,18 @@ def test_cluster_sizes_of_a_decode_step():
     reported = {1: 296, 2: 148, 3: 93, 4: 71, 5: 56, 6: 45, 7: 37, 8: 33, 9: 30, 10: 26, 11: 21, 12: 21, 13: 17,
                 14: 14, 15: 14, 16: 14}
     planner = AttentionPlanner(AttentionShape(28, 4, None, 128), 148, lambda n: reported[n], 16)
-    assert [planner.decode_fixed(B, 4096) for B in (1, 2, 3, 4, 5, 6, 8, 16, 32, 64)] == [16, 16, 16, 12, 10, 10, 8, 4, 2, 1]
-    assert planner.decode_fixed(1, 32768) == 16          # 64 shorter shares would need the unfused launches
-    assert planner.decode_fixed(4, 32768) == 12
-    assert planner.decode_fixed(8, 512) == 2             # no share shorter than 256 keys
+    assert [planner.decode_fixed(B, 4096) for B in (1, 2, 3, 4, 5, 6, 8, 16, 32, 64)] == [
+        (16, 1), (16, 1), (16, 1), (12, 1), (10, 1), (10, 1), (8, 1), (4, 1), (2, 1), (1, 1)]
+    # one request far into a long context: several clusters per KV head, all resident at once
+    cluster, groups = planner.decode_fixed(1, 32768)
+    assert groups > 1 and 48 <= cluster * groups <= 64 and reported[cluster] >= 4 * groups + (2 if cluster > 10 else 0)
+    assert planner.decode_fixed(1, 8192) == (16, 1)      # a second launch to merge parts would cost more than it saves
+    cluster, groups = planner.decode_fixed(4, 32768)
+    assert cluster * groups <= 18 and reported[cluster] >= 16 * groups + (2 if cluster > 10 else 0)
+    assert planner.decode_fixed(8, 512) == (2, 1)        # no share shorter than 256 keys
+    arrays, facts = planner.plan_decode(np.array([32000]), planner.decode_fixed(1, 32768))
+    cluster, groups = planner.decode_fixed(1, 32768)
+    assert facts["decode_nsplit"] == cluster and facts["decode_groups"] == groups
+    assert len(arrays["items"]) == cluster * groups * ITEM_INTS
     plain = AttentionPlanner(AttentionShape(28, 4, None, 128), 148)      # a kernel without clusters
-    assert plain.decode_fixed(1, 32768) == 64 and plain.decode_fixed(4, 4096) == 16
+    assert plain.decode_fixed(1, 32768) == (64, 1) and plain.decode_fixed(4, 4096) == (16, 1)

@@ -549,20 +549,25 @@ def test_attention_tensor_core_splits_window_and_far_key(kernel):
     torch.testing.assert_close(out2, ref2, **tol(bf, 2))
 
 
-@pytest.mark.parametrize("nq,nkv,d,P_,nsplit,qkv_nsplit,rdim,interleaved,window", [
-    (28, 4, 128, 16, 8, 8, 128, False, None),       # the benchmark's shape: 7 heads per KV head, clusters of 8
-    (28, 4, 128, 16, 16, 3, 128, False, None),      # clusters of 16
-    (3, 1, 64, 32, 1, 1, 64, False, None),          # one share: nothing to merge
-    (32, 2, 128, 8, 4, 2, 64, True, None),          # 16 heads per KV head, interleaved pairs on half the head
-    (8, 8, 64, 64, 3, 4, 0, False, None),           # no rotation, one head per KV head, pages of a whole tile
-    (12, 4, 128, 4, 6, 1, 96, False, 300),          # a window, tiny pages; 3 heads over 6 shares: some CTAs own no row
-    (20, 4, 64, 16, 3, 5, 64, False, None),         # 5 heads over 3 shares: a CTA owns two rows
+@pytest.mark.parametrize("nq,nkv,d,P_,nsplit,qkv_nsplit,rdim,interleaved,window,ngroups", [
+    (28, 4, 128, 16, 8, 8, 128, False, None, 1),       # the benchmark's shape: 7 heads per KV head, clusters of 8
+    (28, 4, 128, 16, 16, 3, 128, False, None, 1),      # clusters of 16
+    (3, 1, 64, 32, 1, 1, 64, False, None, 1),          # one share: nothing to merge
+    (32, 2, 128, 8, 4, 2, 64, True, None, 1),          # 16 heads per KV head, interleaved pairs on half the head
+    (8, 8, 64, 64, 3, 4, 0, False, None, 1),           # no rotation, one head per KV head, pages of a whole tile
+    (12, 4, 128, 4, 6, 1, 96, False, 300, 1),          # a window, tiny pages; 3 heads over 6 shares: some CTAs own no row
+    (20, 4, 64, 16, 3, 5, 64, False, None, 1),         # 5 heads over 3 shares: a CTA owns two rows
+    (28, 4, 128, 16, 4, 2, 128, False, None, 3),       # three clusters of 4 per token and KV head, merged by attention_combine
+    (12, 4, 128, 4, 2, 1, 96, False, 300, 5),          # five clusters of 2, a window: most groups of short histories are empty
+    (20, 4, 64, 16, 3, 5, 64, True, None, 2),          # two clusters of 3, a CTA owns two rows
+    (3, 1, 64, 32, 1, 1, 64, False, None, 4),          # four clusters of one CTA
 ])
-def test_attention_decode_fused(nq, nkv, d, P_, nsplit, qkv_nsplit, rdim, interleaved, window):
+def test_attention_decode_fused(nq, nkv, d, P_, nsplit, qkv_nsplit, rdim, interleaved, window, ngroups):
     """The decode kernel that does everything between the q/k/v product and the output projection:
     sums the product's parts, adds the bias, rotates, appends k and v to their pages, attends over
-    the cache and merges the key shares in its cluster.  Histories of 0, a few, one tile, and many
-    keys, some ending at a page's or a tile's edge; one far key among hundreds stands out."""
+    the cache and merges the key shares in its cluster (with several clusters per token and KV head,
+    every cluster leaves a part and attention_combine merges them).  Histories of 0, a few, one tile,
+    and many keys, some ending at a page's or a tile's edge; one far key among hundreds stands out."""
     bf = torch.bfloat16
     histories = [0, 5, 63, 64, 127, 700, 1023, 333]
     T = len(histories)
@@ -597,9 +602,13 @@ def test_attention_decode_fused(nq, nkv, d, P_, nsplit, qkv_nsplit, rdim, interl
     out = torch.full((T, nq * d), float("nan"), dtype=bf, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     assert K().attention_decode_supports(d, P_, nq // nkv, nsplit, rdim)
+    extra = {}
+    if ngroups > 1:
+        extra = dict(ngroups=ngroups, part_acc=torch.full((T * ngroups, nq, d), float("nan"), device=DEV),
+                     part_ml=torch.full((T * ngroups, nq, 2), float("nan"), device=DEV))
     K().attention_decode(parts, bias, inv, cache, out, positions, table, nq=nq, nkv=nkv, d=d, page_size=P_,
                          nsplit=nsplit, qkv_nsplit=qkv_nsplit, qkv_split_stride=parts.stride(0), rotary_dim=rdim,
-                         interleaved=interleaved, window=window or 0, status=status)
+                         interleaved=interleaved, window=window or 0, status=status, **extra)
     assert int(status) == 0
     k_new = plain_rotation(full[:, nq * d: (nq + nkv) * d].view(T, nkv, d), positions.cpu(), theta, rdim, interleaved).to(bf)
     v_new = full[:, (nq + nkv) * d:].view(T, nkv, d).to(bf)
