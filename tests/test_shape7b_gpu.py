@@ -152,3 +152,43 @@ def test_7b_layer_sizes_decode_tokens_beside_a_long_portion(folder):
         rows.append((got.argmax(-1) == ref.argmax(-1)).float())
     assert torch.cat(rows).mean() > 0.8
     cache.assert_invariants()
+
+
+def test_7b_layer_sizes_one_request_far_into_a_long_context(folder, tmp_path):
+    """One request 9,000 tokens into its context, bfloat16: a decode step then cuts its keys into several
+    clusters per KV head (four KV heads alone would keep 64 CTAs busy), each cluster leaves a part and
+    attention_combine merges them.  Twelve tokens decoded one by one through the captured graph are
+    compared with the same twelve positions run as the end of a prompt portion by the tcgen05 kernel:
+    two paths of the engine over the same cache content (the fixture's weights make attention far from
+    uniform)."""
+    from mini_hisparse_b200 import CacheConfig, CacheManager, load_model
+    from mini_hisparse_b200.engine import ModelRunner, StepEntry
+
+    long_folder = tmp_path / "long"
+    long_folder.mkdir()
+    (long_folder / "config.json").write_text(json.dumps(dict(CONFIG, max_position_embeddings=12000)))
+    (long_folder / "model.safetensors").symlink_to(folder / "model.safetensors")
+    model = load_model(long_folder, dtype="bfloat16")
+    cache = CacheManager(model.cache_needs, CacheConfig(num_pages=1200, page_size=16, max_requests=2,
+                                                        dtype=model.rt.dtype))
+    runner = ModelRunner(model, cache)
+    cluster, groups = runner.batch.slots[0].planner.decode_fixed(1, 16384)
+    assert groups > 1 and cluster * groups >= 32
+    N, tail = 9000, 12
+    tokens = random_tokens(CONFIG["vocab_size"], N + tail, seed=21)
+    cache.open("decoded")
+    for a in range(0, N, 3000):
+        runner.step([StepEntry("decoded", tokens[a:a + 3000], [])])
+    one_by_one = [runner.step([StepEntry("decoded", [t], [0])]).float().cpu().clone() for t in tokens[N:]]
+    runner.check_status()
+    assert runner.stats["graph_steps"] == tail
+    cache.open("portion")
+    for a in range(0, 8000, 4000):
+        runner.step([StepEntry("portion", tokens[a:a + 4000], [])])
+    whole = runner.step([StepEntry("portion", tokens[8000:], list(range(1000, 1000 + tail)))]).float().cpu()
+    runner.check_status()
+    got = torch.cat(one_by_one)
+    scale = float(whole.abs().max())
+    assert float((got - whole).abs().max()) < 0.02 * scale, float((got - whole).abs().max()) / scale
+    assert (got.argmax(-1) == whole.argmax(-1)).float().mean() >= 0.9
+    cache.assert_invariants()
