@@ -180,6 +180,66 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const DT* __restri
     }
 }
 
+// Many rows (a prompt portion), every row in place, one matrix of deltas: a CTA walks rows
+// blockIdx.x, blockIdx.x + gridDim.x, ... and asks for the next row before it reduces and stores
+// the current one.  With a CTA per row the GPU's CTAs all load, then all reduce, then all store,
+// wave after wave; walking keeps loads and stores of different rows in flight together (2,048 rows
+// of 3,584 with a bfloat16 delta, caches cold: 22 -> 20.5 us; the registers of two rows leave three
+// CTAs per SM, which is what limits it now).
+template <typename DT, typename OT>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_rows_kernel(float* __restrict__ x, const DT* __restrict__ delta, const float* __restrict__ weight,
+                        float eps, OT* __restrict__ out, int R, int H) {
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    const int nvec = H >> 2;
+    pdl_wait();
+    float4 cur[VEC_CACHE], dcur[VEC_CACHE], nxt[VEC_CACHE], dnxt[VEC_CACHE];
+    auto fetch = [&](int r, float4 (&a)[VEC_CACHE], float4 (&d)[VEC_CACHE]) {
+#pragma unroll
+        for (int c = 0; c < VEC_CACHE; ++c) {
+            const int i = threadIdx.x + c * blockDim.x;
+            if (i < nvec) {
+                a[c] = *(const float4*)(x + (size_t)r * H + 4 * i);
+                d[c] = delta ? load4<DT>(delta + (size_t)r * H + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+    };
+    int r = blockIdx.x;
+    if (r < R) fetch(r, cur, dcur);
+    for (; r < R; r += gridDim.x) {
+        const int rn = r + gridDim.x;
+        if (rn < R) fetch(rn, nxt, dnxt);
+        float ss = 0.f;
+#pragma unroll
+        for (int c = 0; c < VEC_CACHE; ++c) {
+            const int i = threadIdx.x + c * blockDim.x;
+            if (i < nvec) {
+                float4 a = cur[c];
+                a.x += dcur[c].x; a.y += dcur[c].y; a.z += dcur[c].z; a.w += dcur[c].w;
+                if (delta) *(float4*)(x + (size_t)r * H + 4 * i) = a;
+                cur[c] = a;
+                ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+            }
+        }
+        const float total = block_sum(ss, scratch);
+        const float rstd = rsqrtf(total / (float)H + eps);
+#pragma unroll
+        for (int c = 0; c < VEC_CACHE; ++c) {
+            const int i = threadIdx.x + c * blockDim.x;
+            if (i < nvec) {
+                const float4 w = *(const float4*)(weight + 4 * i);
+                float4 a = cur[c];
+                a.x = (a.x * rstd) * w.x; a.y = (a.y * rstd) * w.y;
+                a.z = (a.z * rstd) * w.z; a.w = (a.w * rstd) * w.w;
+                store4<OT>(out + (size_t)r * H + 4 * i, a);
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < VEC_CACHE; ++c) { cur[c] = nxt[c]; dcur[c] = dnxt[c]; }
+    }
+}
+
 // Residual add alone (the last feed-forward's output when no norm follows on all rows).
 template <typename DT>
 __global__ void residual_add_kernel(float* __restrict__ x, const DT* __restrict__ delta, int nsplit,
@@ -205,6 +265,26 @@ MHB_EXPORT int mhb_add_rmsnorm(float* x, const void* delta, int delta_dtype, int
         MHB_DISPATCH_DTYPE(delta_dtype, DT, MHB_DISPATCH_DTYPE(out_dtype, OT,
             launch_kernel((add_rmsnorm_vec_kernel<DT, OT, 1>), dim3(R), dim3(wide), 0, stream,
                 x, (const DT*)delta, nsplit, (size_t)split_stride, weight, eps, rows, (OT*)out, H)));
+        return check_launch("add_rmsnorm");
+    }
+    if (aligned && vthreads <= 256 && R >= 512 && rows == nullptr && nsplit == 1) {
+        // a prompt portion: a few CTAs per SM walk the rows
+        static int sms = 0;
+        if (!sms) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (sms <= 0) sms = 148;
+        }
+        MHB_DISPATCH_DTYPE(delta_dtype, DT, MHB_DISPATCH_DTYPE(out_dtype, OT, {
+            int per_sm = 0;       // as many CTAs as are resident at once
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, add_rmsnorm_rows_kernel<DT, OT>, vthreads, 0) !=
+                    cudaSuccess || per_sm < 1)
+                per_sm = 2;
+            const int grid = R < per_sm * sms ? R : per_sm * sms;
+            launch_kernel((add_rmsnorm_rows_kernel<DT, OT>), dim3(grid), dim3(vthreads), 0, stream,
+                x, (const DT*)delta, weight, eps, (OT*)out, R, H);
+        }));
         return check_launch("add_rmsnorm");
     }
     if (aligned && vthreads <= 1024) {

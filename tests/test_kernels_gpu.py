@@ -80,6 +80,28 @@ def test_rmsnorm_plain_add_rows_and_splits(dtype, H):
     torch.testing.assert_close(out3.float(), P.rms_norm((x + delta.float())[rows.long()], w, eps), **tol(dtype, 4))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("R,H", [(512, 3584), (1531, 1000), (2048, 72), (700, 4096)])
+def test_rmsnorm_many_rows(dtype, R, H):
+    """The row-walking kernel of prompt portions (512 rows and more, rows of up to 4,096 elements): more rows
+    than CTAs, a last round that not every CTA has, with and without a delta."""
+    eps = 1e-5
+    x = rnd(R, H, seed=1, scale=2.0)
+    x[5] *= 40.0                                # one row far larger than the others: rows do not mix
+    w = rnd(H, seed=2) * 0.1 + 1
+    delta = rnd(R, H, dtype=dtype, seed=3)
+    out = torch.full((R, H), float("nan"), dtype=dtype, device=DEV)
+    xr = x.clone()
+    K().add_rmsnorm(xr, w, eps, out, delta=delta)
+    torch.testing.assert_close(xr, x + delta.float(), atol=1e-6, rtol=1e-6)
+    torch.testing.assert_close(out.float(), P.rms_norm(x + delta.float(), w, eps), **tol(dtype, 4))
+    out.fill_(float("nan"))
+    xr = x.clone()
+    K().add_rmsnorm(xr, w, eps, out)
+    assert torch.equal(xr, x)
+    torch.testing.assert_close(out.float(), P.rms_norm(x, w, eps), **tol(dtype, 4))
+
+
 def test_residual_add():
     x = rnd(5, 33, seed=1)
     parts = rnd(2, 5, 33, seed=2)
