@@ -34,7 +34,7 @@ def _run(config: dict, context: int, args) -> dict:
     from mini_hisparse.model import MiniModel, ModelConfig
     from reference.cache import PagedConfig, PagedKVCache
 
-    from mini_hisparse_b200.measure import ClockSampler
+    from mini_hisparse_b200.measure import ClockSampler, headline_config
 
     steps, warmup, batch = args.steps, max(args.warmup, 3), args.batch
     layers = args.layers or config["num_hidden_layers"]
@@ -86,10 +86,9 @@ def _run(config: dict, context: int, args) -> dict:
         "metric": "decode tokens/s (Qwen2.5-7B shape, batch 8, context 4096)",
         "value": done / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic: torch default init, uniform-random token ids",
-        "config": {"model": "Qwen2.5-7B shape", "global_batch": batch, "seq_len": context,
-                   "parallelism": "single GPU", "layers": layers,
-                   "layers_of_config": config["num_hidden_layers"], "cache": "reference.cache.PagedKVCache, all pages resident"},
+        "dtype": "bf16",
+        "data": "synthetic: torch default init, uniform-random token ids; reference.cache.PagedKVCache, all pages resident",
+        "config": headline_config(config, batch=batch, context=context, layers=layers, page_size=page),
         "clocks": clocks.result,
         "e2e": {"value": done / wall, "unit": "tokens/s", "h2d_bytes_per_step": 8 * batch,
                 "d2h_bytes_per_step": 8 * batch},

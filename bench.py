@@ -204,14 +204,7 @@ def main() -> int:
         "dtype": "bf16",
         "data": "synthetic: seeded random weights, uniform-random token ids, random KV for the device-timed context",
         "impl": "ours",
-        "config": {
-            "model": "Qwen2.5-7B shape", "global_batch": args.batch, "seq_len": CONTEXT,
-            "parallelism": "single GPU", "layers": layers, "layers_of_config": CONFIG_7B["num_hidden_layers"],
-            "hidden": cfg.hidden_size, "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
-            "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-            "page_size": PAGE, "l2": "inputs larger than L2 (all weights are read every step)",
-            "peaks": f"of {peaks['source']}",
-        },
+        "config": measure.headline_config(CONFIG_7B, batch=args.batch, context=CONTEXT, layers=layers, page_size=PAGE),
         "clocks": main_pt["clocks"],
         "e2e": e2e,
         "gpu_launches": main_pt["launches"],

@@ -89,6 +89,20 @@ class ClockSampler:
 
 
 # ---- counts -------------------------------------------------------------------------------------
+def headline_config(config: dict, *, batch: int, context: int, layers: int, page_size: int) -> dict:
+    """The ``config`` of the headline bench line, from the model's config.json keys: both arms of the
+    benchmark print the same dictionary for the same shape."""
+    heads = config["num_attention_heads"]
+    return {
+        "model": "Qwen2.5-7B shape", "global_batch": batch, "seq_len": context, "parallelism": "single GPU",
+        "layers": layers, "layers_of_config": config["num_hidden_layers"], "hidden": config["hidden_size"],
+        "q_heads": heads, "kv_heads": config["num_key_value_heads"],
+        "head_dim": config.get("head_dim") or config["hidden_size"] // heads,
+        "intermediate": config["intermediate_size"], "vocab": config["vocab_size"], "page_size": page_size,
+        "l2": "inputs larger than L2 (all weights are read every step)", "peaks": f"of {peaks()['source']}",
+    }
+
+
 def decode_bytes(model, cache, live_tokens: int) -> int:
     """Bytes a decode step has to read: every weight it uses once (the embedding table is only
     gathered, so it does not count unless it is also the tied head) and the cache of the live
