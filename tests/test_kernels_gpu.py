@@ -590,8 +590,22 @@ def test_attention_decode_fused(nq, nkv, d, P_, nsplit, qkv_nsplit, rdim, interl
     the cache and merges the key shares in its cluster (with several clusters per token and KV head,
     every cluster leaves a part and attention_combine merges them).  Histories of 0, a few, one tile,
     and many keys, some ending at a page's or a tile's edge; one far key among hundreds stands out."""
+    check_attention_decode([0, 5, 63, 64, 127, 700, 1023, 333], nq, nkv, d, P_, nsplit, qkv_nsplit, rdim, interleaved,
+                           window, ngroups)
+
+
+def test_attention_decode_fused_more_clusters_than_fit():
+    """A batch of 90 tokens with uneven histories and three shares each: 1,080 CTAs in 360 clusters, several
+    rounds of them (what the planner chooses for a large batch that would else wait for its longest
+    history)."""
+    g = torch.Generator().manual_seed(11)
+    histories = torch.randint(0, 900, (90,), generator=g).tolist()
+    histories[7], histories[50] = 2300, 1999
+    check_attention_decode(histories, 28, 4, 128, 16, 3, 2, 128, False, None, 1)
+
+
+def check_attention_decode(histories, nq, nkv, d, P_, nsplit, qkv_nsplit, rdim, interleaved, window, ngroups):
     bf = torch.bfloat16
-    histories = [0, 5, 63, 64, 127, 700, 1023, 333]
     T = len(histories)
     theta = 10000.0
     g = torch.Generator().manual_seed(3)
