@@ -4,6 +4,7 @@ at the sizes they are tuned for, in float32 and in bfloat16, whole prompt, porti
 against the plain implementation run in float32 on the device."""
 import json
 
+import numpy as np
 import pytest
 import torch
 
@@ -191,4 +192,41 @@ def test_7b_layer_sizes_one_request_far_into_a_long_context(folder, tmp_path):
     scale = float(whole.abs().max())
     assert float((got - whole).abs().max()) < 0.02 * scale, float((got - whole).abs().max()) / scale
     assert (got.argmax(-1) == whole.argmax(-1)).float().mean() >= 0.9
+    cache.assert_invariants()
+
+
+def test_7b_layer_sizes_forty_requests_of_uneven_length_decode_together(folder):
+    """Forty requests with 20 to 900 cached tokens decode one token each in one captured step, bfloat16:
+    one CTA per token and KV head would wait for the longest history, so the planner cuts every token's
+    keys into a few shares (more clusters than are resident at once); every row is compared with the
+    plain implementation of its own request."""
+    from mini_hisparse_b200 import CacheConfig, CacheManager, load_model
+    from mini_hisparse_b200.engine import ModelRunner, StepEntry
+
+    torch.backends.cuda.matmul.allow_tf32 = False
+    cfg, w = P.load_folder(folder, dtype=torch.float32, device="cuda:0")
+    model = load_model(folder, dtype="bfloat16")
+    cache = CacheManager(model.cache_needs, CacheConfig(num_pages=1400, page_size=16, max_requests=40,
+                                                        dtype=model.rt.dtype))
+    runner = ModelRunner(model, cache)
+    g = torch.Generator().manual_seed(4)
+    lengths = torch.randint(20, 500, (40,), generator=g).tolist()
+    lengths[3], lengths[17], lengths[31] = 900, 860, 777
+    prompts = [random_tokens(CONFIG["vocab_size"], n, seed=100 + i) for i, n in enumerate(lengths)]
+    for i, toks in enumerate(prompts):
+        cache.open(f"r{i}")
+    for a in range(0, 40, 8):                                 # prefill all but the last token, eight requests a step
+        runner.step([StepEntry(f"r{i}", prompts[i][:-1], []) for i in range(a, a + 8)])
+    planner = runner.batch.slots[0].planner
+    shares = planner.decode_fixed_for(np.asarray([n - 1 for n in lengths]), 1024)
+    assert planner.decode_fixed(40, 1024) == (1, 1) and shares[0] > 1
+    out = runner.step([StepEntry(f"r{i}", [prompts[i][-1]], [0]) for i in range(40)]).float().cpu()
+    runner.check_status()
+    assert runner.stats["graph_steps"] == 1
+    agree = []
+    for i, toks in enumerate(prompts):
+        ref = P.forward_logits(cfg, w, toks)[-1].cpu()
+        torch.testing.assert_close(out[i], ref, atol=0.03 * float(ref.abs().max()), rtol=0.03)
+        agree.append(float(out[i].argmax() == ref.argmax()))
+    assert sum(agree) / len(agree) > 0.8
     cache.assert_invariants()
